@@ -1,0 +1,228 @@
+// stablehlo.reduce kernels: the input is viewed as [A, R, B] and reduced over R, with the producing elementwise
+// chain evaluated on the fly (vm.cuh) so that the reduced tensor is read from HBM exactly once.
+//
+//   B == 1 (row reduction): a group of T threads (a warp or a whole CTA) owns one (row, split) piece, walks it with
+//     128-bit vector loads, folds lanes in registers, then warp shuffles and one shared-memory step.
+//   B  > 1 (column reduction): threads are laid out [ry][bx]; each owns V adjacent columns and strides over R, so a
+//     warp reads one contiguous span per row; the ry partials meet in shared memory.
+// Long reductions with few outputs are cut into S splits whose partials land in scratch and are folded by a second
+// launch of the same kernel.  HBM-bound: algorithmic bytes = one read of every operand of the prologue.
+#include "../../../include/b2x_kernels.h"
+#include "common.cuh"
+#include "vm.cuh"
+
+namespace b2x {
+
+__device__ __forceinline__ uint32_t red_combine(uint32_t a, uint32_t b, int monoid, int cls) {
+  switch (monoid) {
+    case 0: return cls == VM_F32 ? f2u(u2f(a) + u2f(b)) : a + b;
+    case 1: return cls == VM_F32 ? f2u(u2f(a) * u2f(b)) : a * b;
+    case 2: return cls == VM_F32 ? f2u(vm_fmax(u2f(a), u2f(b))) : (cls == VM_S32 ? (uint32_t)max((int)a, (int)b) : max(a, b));
+    case 3: return cls == VM_F32 ? f2u(vm_fmin(u2f(a), u2f(b))) : (cls == VM_S32 ? (uint32_t)min((int)a, (int)b) : min(a, b));
+    case 4: return a & b;
+    case 5: return a | b;
+    default: return a ^ b;
+  }
+}
+__host__ __device__ inline uint32_t red_identity(int monoid, int cls) {
+  switch (monoid) {
+    case 0: case 5: case 6: return 0u;
+    case 1: return cls == VM_F32 ? 0x3f800000u : 1u;
+    case 2: return cls == VM_F32 ? 0xff800000u : (cls == VM_S32 ? 0x80000000u : 0u);
+    case 3: return cls == VM_F32 ? 0x7f800000u : (cls == VM_S32 ? 0x7fffffffu : 0xffffffffu);
+    default: return 0xffffffffu;
+  }
+}
+
+struct ReduceKArgs {
+  int64_t A, R, B;
+  int64_t chunk;       // elements of R per split (multiple of the vector width for row reductions)
+  int32_t S;
+  int32_t monoid, cls;
+  int32_t out_elem, init_elem;
+  uint32_t init_imm;
+  const void* init_ptr;
+  void* out;           // final output (S == 1) or partials (S > 1, raw 32-bit)
+};
+
+__device__ __forceinline__ void red_write(const ReduceKArgs& K, int64_t index, uint32_t v) {
+  if (K.S > 1) { ((uint32_t*)K.out)[index] = v; return; }
+  uint32_t init = K.init_imm;
+  if (K.init_ptr) {
+    uint32_t raw;
+    const int es = vm_elem_size((uint8_t)K.init_elem);
+    if (es == 4) raw = *(const uint32_t*)K.init_ptr; else if (es == 2) raw = *(const uint16_t*)K.init_ptr; else raw = *(const uint8_t*)K.init_ptr;
+    init = vm_decode(raw, (uint8_t)K.init_elem);
+  }
+  v = red_combine(init, v, K.monoid, K.cls);
+  uint32_t enc = vm_encode(v, (uint8_t)K.out_elem);
+  const int es = vm_elem_size((uint8_t)K.out_elem);
+  if (es == 4) ((uint32_t*)K.out)[index] = enc; else if (es == 2) ((uint16_t*)K.out)[index] = (uint16_t)enc; else ((uint8_t*)K.out)[index] = (uint8_t)enc;
+}
+
+// Row reduction.  T = threads cooperating on one (row, split) piece: 32 or 256.
+template <int V, int T>
+__global__ void __launch_bounds__(256) k_reduce_rows(const __grid_constant__ B2xVmProgram P, const __grid_constant__ ReduceKArgs K) {
+  __shared__ uint32_t smem[8];
+  constexpr int PIECES_PER_CTA = 256 / T;
+  const int lane_in_piece = threadIdx.x % T;
+  const int64_t n_pieces = K.A * K.S;
+  uint32_t zero[V];
+#pragma unroll
+  for (int j = 0; j < V; j++) zero[j] = 0;
+  const uint32_t ident = red_identity(K.monoid, K.cls);
+  for (int64_t piece0 = (int64_t)blockIdx.x * PIECES_PER_CTA; piece0 < n_pieces; piece0 += (int64_t)gridDim.x * PIECES_PER_CTA) {
+    const int64_t piece = piece0 + threadIdx.x / T;
+    uint32_t total = ident;
+    if (piece < n_pieces) {
+      const int64_t a = piece / K.S, s = piece % K.S;
+      const int64_t r0 = s * K.chunk;
+      const int64_t r1 = min(K.R, r0 + K.chunk);
+      for (int64_t r = r0 + (int64_t)lane_in_piece * V; r < r1; r += (int64_t)T * V) {
+        uint32_t acc[V];
+        vm_run<V>(P, (uint64_t)(a * K.R + r), zero, acc);
+#pragma unroll
+        for (int j = 0; j < V; j++) total = red_combine(total, acc[j], K.monoid, K.cls);
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) total = red_combine(total, __shfl_xor_sync(0xffffffffu, total, off), K.monoid, K.cls);
+    if (T == 32) {
+      if (lane_in_piece == 0 && piece < n_pieces) red_write(K, piece, total);
+    } else {
+      __syncthreads();
+      if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = total;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        uint32_t t = smem[0];
+#pragma unroll
+        for (int w = 1; w < 8; w++) t = red_combine(t, smem[w], K.monoid, K.cls);
+        if (piece < n_pieces) red_write(K, piece, t);
+      }
+    }
+  }
+}
+
+// Column reduction.  blockDim = (BX, RY) with BX * RY = 256; thread (bx, ry) owns V adjacent columns.
+template <int V>
+__global__ void __launch_bounds__(256) k_reduce_cols(const __grid_constant__ B2xVmProgram P, const __grid_constant__ ReduceKArgs K, int n_bblocks) {
+  __shared__ uint32_t smem[256 * V];
+  const int BX = blockDim.x, RY = blockDim.y;
+  const int64_t n_work = K.A * K.S * (int64_t)n_bblocks;
+  uint32_t zero[V];
+#pragma unroll
+  for (int j = 0; j < V; j++) zero[j] = 0;
+  const uint32_t ident = red_identity(K.monoid, K.cls);
+  for (int64_t w = blockIdx.x; w < n_work; w += gridDim.x) {
+    const int bb = (int)(w % n_bblocks);
+    const int64_t as = w / n_bblocks;
+    const int64_t a = as / K.S, s = as % K.S;
+    const int64_t b0 = ((int64_t)bb * BX + threadIdx.x) * V;
+    const int64_t r0 = s * K.chunk, r1 = min(K.R, r0 + K.chunk);
+    uint32_t tot[V];
+#pragma unroll
+    for (int j = 0; j < V; j++) tot[j] = ident;
+    if (b0 < K.B) {
+      for (int64_t r = r0 + threadIdx.y; r < r1; r += RY) {
+        uint32_t acc[V];
+        vm_run<V>(P, (uint64_t)((a * K.R + r) * K.B + b0), zero, acc);
+#pragma unroll
+        for (int j = 0; j < V; j++) tot[j] = red_combine(tot[j], acc[j], K.monoid, K.cls);
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < V; j++) smem[(threadIdx.y * BX + threadIdx.x) * V + j] = tot[j];
+    __syncthreads();
+    if (threadIdx.y == 0 && b0 < K.B) {
+      for (int y = 1; y < RY; y++) {
+#pragma unroll
+        for (int j = 0; j < V; j++) tot[j] = red_combine(tot[j], smem[(y * BX + threadIdx.x) * V + j], K.monoid, K.cls);
+      }
+#pragma unroll
+      for (int j = 0; j < V; j++) red_write(K, (a * K.S + s) * K.B + b0 + j, tot[j]);
+    }
+  }
+}
+
+static int launch_one(const B2xVmProgram& P, ReduceKArgs K, int vec, cudaStream_t stream) {
+  const int64_t cap = (int64_t)kNumSms * 16;
+  if (K.B == 1) {
+    const int64_t pieces = K.A * K.S;
+    const int64_t len = (K.chunk < K.R ? K.chunk : K.R);
+    const bool warp_rows = (len / vec) <= 64;
+    const int per_cta = warp_rows ? 8 : 1;
+    int64_t blocks = (pieces + per_cta - 1) / per_cta;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    dim3 grid((unsigned)blocks), block(256);
+#define B2X_ROWS(VV)                                                                      \
+    if (warp_rows) k_reduce_rows<VV, 32><<<grid, block, 0, stream>>>(P, K);               \
+    else k_reduce_rows<VV, 256><<<grid, block, 0, stream>>>(P, K);
+    if (vec == 8) { B2X_ROWS(8) } else if (vec == 4) { B2X_ROWS(4) } else { B2X_ROWS(1) }
+#undef B2X_ROWS
+  } else {
+    int64_t bvecs = (K.B + vec - 1) / vec;
+    int bx = 1;
+    while (bx < 256 && bx < bvecs) bx <<= 1;
+    int ry = 256 / bx;
+    int n_bblocks = (int)((bvecs + bx - 1) / bx);
+    int64_t blocks = K.A * K.S * (int64_t)n_bblocks;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    dim3 grid((unsigned)blocks), block(bx, ry);
+    if (vec == 8) k_reduce_cols<8><<<grid, block, 0, stream>>>(P, K, n_bblocks);
+    else if (vec == 4) k_reduce_cols<4><<<grid, block, 0, stream>>>(P, K, n_bblocks);
+    else k_reduce_cols<1><<<grid, block, 0, stream>>>(P, K, n_bblocks);
+  }
+  count_launch();
+  return (int)cudaGetLastError();
+}
+
+}  // namespace b2x
+
+extern "C" int b2x_reduce_splits(int64_t A, int64_t R, int64_t B) {
+  // Enough independent pieces to fill 148 SMs without starving each piece of work.
+  int64_t outputs = A * ((B + 255) / 256 > 1 ? (B + 255) / 256 : 1);
+  if (outputs >= 296 || R < 4096) return 1;
+  int64_t s = (592 + outputs - 1) / outputs;
+  if (s > R / 2048) s = R / 2048;
+  if (s > 1024) s = 1024;
+  return (int)(s < 1 ? 1 : s);
+}
+
+extern "C" int b2x_launch_reduce(const B2xVmProgram* prologue, const B2xReduceArgs* a, b2x_stream_t stream_) {
+  using namespace b2x;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (a->A <= 0 || a->B <= 0) return 0;
+  const int vec = a->vec;
+  if (vec != 1 && vec != 4 && vec != 8) return (int)cudaErrorInvalidValue;
+  const int S = b2x_reduce_splits(a->A, a->R, a->B);
+  ReduceKArgs K{};
+  K.A = a->A; K.R = a->R; K.B = a->B;
+  K.monoid = a->monoid; K.cls = a->cls;
+  K.out_elem = a->out_elem; K.init_elem = a->init_elem;
+  K.init_imm = a->init_imm; K.init_ptr = a->init_ptr;
+  if (S <= 1 || a->R == 0) {
+    K.S = 1; K.chunk = a->R > 0 ? a->R : 1; K.out = a->out;
+    return launch_one(*prologue, K, vec, stream);
+  }
+  if (!a->scratch) return (int)cudaErrorInvalidValue;
+  int64_t chunk = (a->R + S - 1) / S;
+  chunk = (chunk + vec - 1) / vec * vec;
+  K.S = S; K.chunk = chunk; K.out = a->scratch;
+  int rc = launch_one(*prologue, K, vec, stream);
+  if (rc) return rc;
+  // fold the [A, S, B] partials
+  B2xVmProgram F{};
+  F.n_instr = 1; F.n_tensors = 1; F.n_dims = 1;
+  F.dim[0] = a->A * S * a->B;
+  F.tensors[0].ptr = a->scratch;
+  F.tensors[0].stride[0] = 1;
+  F.tensors[0].elem = a->cls == VM_F32 ? EL_F32 : (a->cls == VM_S32 ? EL_S32 : EL_U32);
+  F.code[0].op = VM_LOAD; F.code[0].src_kind = VM_SRC_TENSOR; F.code[0].src_idx = 0; F.code[0].tc = a->cls;
+  ReduceKArgs K2 = K;
+  K2.R = S; K2.S = 1; K2.chunk = S; K2.out = a->out;
+  int v2 = (a->B == 1) ? ((S % 8 == 0) ? 8 : (S % 4 == 0 ? 4 : 1)) : ((a->B % 8 == 0) ? 8 : (a->B % 4 == 0 ? 4 : 1));
+  return launch_one(F, K2, v2, stream);
+}
