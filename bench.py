@@ -1,0 +1,355 @@
+#!/usr/bin/env python
+"""Benchmark of the StableHLO hot path through the PJRT C ABI.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--config c5|c4|c2|c3|c1]
+
+Own arm.  A step is one execution of the data-parallel gradient program (config 5 of BASELINE.json: the MLP forward +
+hand-written backward of config 4 on an 8192-token shard per replica, then stablehlo.all_reduce over the f32
+gradients and a divide by the replica count) on synthetic seeded inputs.  One process per GPU (torchrun for N > 1):
+every rank creates a PJRT client over its GPU with `node_id`/`num_nodes`, and the plugin's NCCL communicator is
+bootstrapped through the PJRT key-value callbacks backed by the torch.distributed store.  `value` is whole-job TFLOP/s
+(algorithmic GEMM flops of all replicas / max-over-ranks device time, inputs resident in HBM, CUDA events on the
+plugin's compute stream).  `e2e` runs the same step through the same API from pinned host memory: the activations are
+copied host->device and the loss device->host inside the timed region.
+
+Reference arm (--impl reference).  The reference executes these programs in OpenXLA's CPU plugin, which cannot be built
+here, so this arm times the CPU oracle (oracle/stablehlo_eval.py, a NumPy restatement; BLAS on all host cores) on a
+bounded token sample of the same program.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+T_FULL, D_FULL, F_FULL = 8192, 4096, 16384
+METRIC = "DP step TFLOP/s (dot_general GEMM flops of the config-4 gradient step, all replicas)"
+
+
+def _peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+            "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0])); mx = float(r[1])
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        busy = sorted(sm)[len(sm) // 2:] if sm else []
+        return {"sm_mhz": float(np.median(busy)) if busy else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def _dist():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def _max_over_ranks(x: float, world: int) -> float:
+    if world == 1:
+        return x
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _barrier(world: int):
+    import torch
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def program_for(config: str, n_replicas: int):
+    from ryft_b200 import configs
+    if config in ("c5", "c4"):
+        text = configs.c4_program(T_FULL, D_FULL, F_FULL, replicas=n_replicas if config == "c5" else 0)
+        flops = configs.C4_GEMM_FLOPS(T_FULL, D_FULL, F_FULL)
+        return text, flops
+    if config == "c2":
+        return configs.c2_program(), 2.0 * 32 * 2048 * 128 * 2048
+    if config == "c3":
+        return configs.c3_program(), 2.0 * 4 * 32 * 128 * 4096 * 4097
+    if config == "c1":
+        return configs.c1_program(), 2.0 * 512 * 768 * 512
+    raise SystemExit(f"unknown config {config}")
+
+
+def inputs_for(config: str, replica: int):
+    from ryft_b200 import configs
+    if config == "c5":
+        return configs.c4_inputs(T_FULL, D_FULL, F_FULL, seed=4, replica=replica)
+    if config == "c4":
+        return configs.c4_inputs(T_FULL, D_FULL, F_FULL)
+    return {"c2": configs.c2_inputs, "c3": configs.c3_inputs, "c1": configs.c1_inputs}[config]()
+
+
+def time_device(client, exe, bufs, steps: int, warmup: int, world: int, stream_handle: int, local: int):
+    """W untimed + K timed executions; CUDA events on the plugin's compute stream; returns (ms_total, step timings)."""
+    import torch
+    from ryft_b200 import pjrt
+    s = torch.cuda.ExternalStream(stream_handle, device=local)
+    last = None
+    for _ in range(warmup):
+        last = exe.execute([pjrt.ExecutionDeviceInputs(bufs)])
+    if last:
+        last[0].done.await_()
+    _barrier(world)
+    exe.step_timing(enable=1)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record(s)
+    for _ in range(steps):
+        last = exe.execute([pjrt.ExecutionDeviceInputs(bufs)])
+    t1.record(s)
+    last[0].done.await_()
+    t1.synchronize()
+    _barrier(world)
+    ms = float(t0.elapsed_time(t1))
+    timings = exe.step_timing(enable=0, collect=True)
+    return ms, timings, last
+
+
+def run_own(args) -> dict:
+    import torch
+    from ryft_b200 import configs, pjrt
+    rank, world, local = _dist()
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with: python -m torch.distributed.run --nproc-per-node N bench.py --gpus N ...")
+    torch.cuda.set_device(local)
+    kv = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local))
+        from torch.distributed.distributed_c10d import _get_default_store
+        kv = pjrt.TorchStoreKeyValueStore(torch.distributed.PrefixStore("b2x", _get_default_store()))
+    plugin = pjrt.load_cuda_13_plugin()
+    client = plugin.client({"visible_devices": [local], "node_id": rank, "num_nodes": world}, kv_store=kv)
+    config = args.config
+    n_rep = world if config == "c5" else 1
+    text, flops_per_replica = program_for(config, n_rep)
+    exe = client.compile(pjrt.Program.mlir(text), pjrt.CompilationOptions(replica_count=n_rep))
+    dev = exe.addressable_devices()[0]
+    stream = dev.compute_stream()
+    host_inputs = inputs_for(config, rank)
+    bufs = [client.buffer(x, device=dev) for x in host_inputs]
+    launches_per_exec = int(exe.executable().cost_analysis()["kernel launches"])
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms, timings, last = time_device(client, exe, bufs, args.steps, args.warmup, world, stream, local)
+    clocks = sampler.stop()
+    ms = _max_over_ranks(ms, world)
+    total_flops = flops_per_replica * n_rep * args.steps
+    value = total_flops / (ms * 1e-3) / 1e12
+
+    # ---- end to end: activations from pinned host memory each step, loss read back each step ----
+    e2e = None
+    if config in ("c5", "c4"):
+        x = host_inputs[0]
+        pinned = torch.empty(x.size, dtype=torch.uint16).pin_memory()
+        pinned.numpy()[:] = x.reshape(-1).view(np.uint16)
+        loss_host = np.zeros(4, dtype=np.uint8)
+        e2e_steps = max(3, min(args.steps, 10))
+
+        def one_step():
+            xb = client.buffer(pinned.data_ptr(), pjrt.BufferType.BF16, list(x.shape), device=dev, semantics=1)
+            outs = exe.execute([pjrt.ExecutionDeviceInputs([xb, bufs[1], bufs[2]])])
+            outs[0].outputs[2].copy_to_host(loss_host).await_()
+            return outs
+        for _ in range(2):
+            one_step()
+        _barrier(world)
+        w0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            one_step()
+        _barrier(world)
+        wall = _max_over_ranks(time.perf_counter() - w0, world)
+        e2e = {"value": flops_per_replica * n_rep * e2e_steps / wall / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": int(x.nbytes) * n_rep,
+               "d2h_bytes_per_step": 4 * n_rep, "ms_per_step": wall / e2e_steps * 1e3, "loss": float(loss_host.view(np.float32)[0])}
+
+    # ---- roofline of the dominant kernel (tcgen05 GEMM) from the per-step CUDA events of the timed region ----
+    peaks = _peaks()
+    gemm_ms = sum(t["ms"] for t in timings if t["label"].startswith("gemm_tc"))
+    gemm_flops = sum(t["flops"] for t in timings if t["label"].startswith("gemm_tc")) * args.steps
+    gemm_launches = sum(1 for t in timings if t["label"].startswith("gemm_tc")) * args.steps
+    roofline = None
+    if gemm_ms > 0:
+        achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "kernel": "k_gemm_tc (tcgen05, 128xBN tiles)", "achieved": achieved, "peak": peaks["bf16_tflops_sustained"],
+                    "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": None,
+                    "peak_source": f"{peaks['source']} (sustained cuBLAS bf16)", "avg_launch_ms": gemm_ms / max(gemm_launches, 1)}
+    if config == "c2" and gemm_ms > 0:
+        algo_bytes = 301_998_080.0
+        gbs = algo_bytes * args.steps / (gemm_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": "k_gemm_tc + fused bias/tanh/convert epilogue", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": gbs / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"], "avg_launch_ms": gemm_ms / max(gemm_launches, 1)}
+
+    line = {
+        "metric": METRIC if config in ("c5", "c4") else f"{config} TFLOP/s",
+        "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "steps_per_s": args.steps / (ms * 1e-3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 operands, f32 accumulate", "data": "synthetic (seeded N(0,1) activations, N(0,0.02) weights)",
+        "config": {"workload": {"c5": f"config 5: MLP fwd+bwd gradient step, tokens {T_FULL} x d {D_FULL} x ff {F_FULL} per replica, all_reduce(sum) of "
+                                      f"f32 dW1+dW2 ({2 * D_FULL * F_FULL * 4} B) over {n_rep} replica(s), divide by replica count",
+                                "c4": "config 4: MLP fwd+bwd gradient step on one GPU", "c2": "config 2: batched bf16 dot_general + bias + tanh + convert",
+                                "c3": "config 3: causal attention written out in StableHLO", "c1": "config 1: f32 dot_general 512x768x512"}[config],
+                   "replicas": n_rep, "parallelism": f"dp{n_rep}", "l2": "inputs (>= 320 MiB per step) exceed the 126 MB L2; no flush needed"},
+        "gpu_launches": launches_per_exec * args.steps, "clocks": clocks,
+        "steps_breakdown": [{"label": t["label"], "ms_per_step": t["ms"] / max(t["executions"], 1)} for t in timings],
+    }
+    if e2e:
+        line["e2e"] = e2e
+    if roofline:
+        line["roofline"] = roofline
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(config)
+    if rank == 0 and world == 1 and config == "c5" and not args.no_extras:
+        line["extra"] = extras(client, peaks, local)
+    client.close()
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+    return line if rank == 0 else None
+
+
+def extras(client, peaks, local) -> dict:
+    """dot_general (config 2) and attention (config 3) at full size, timed briefly on the same GPU."""
+    from ryft_b200 import pjrt
+    out = {}
+    for cfg, steps in (("c2", 20), ("c3", 3), ("c1", 20)):
+        try:
+            text, flops = program_for(cfg, 1)
+            exe = client.compile(pjrt.Program.mlir(text))
+            dev = exe.addressable_devices()[0]
+            bufs = [client.buffer(x, device=dev) for x in inputs_for(cfg, 0)]
+            ms, timings, _ = time_device(client, exe, bufs, steps, 3, 1, dev.compute_stream(), local)
+            out[cfg] = {"ms_per_step": ms / steps, "tflops": flops * steps / (ms * 1e-3) / 1e12,
+                        "steps_breakdown": [{"label": t["label"], "ms_per_step": t["ms"] / max(t["executions"], 1)} for t in timings]}
+            if cfg == "c2":
+                out[cfg]["hbm_gbs"] = 301_998_080.0 * steps / (ms * 1e-3) / 1e9
+                out[cfg]["hbm_frac"] = out[cfg]["hbm_gbs"] / peaks["hbm_gbs"]
+            del bufs, exe
+        except Exception as e:  # report, never hide
+            out[cfg] = {"error": str(e)}
+    return out
+
+
+def cpu_baseline(config: str, sample_tokens: int = 512) -> dict:
+    """The oracle timed on the host cores on a bounded sample of the workload (tokens cut to `sample_tokens`)."""
+    from oracle import stablehlo_eval as ev
+    from ryft_b200 import configs
+    if config not in ("c5", "c4"):
+        return {"value": None, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port", "sample": "not timed for this config"}
+    text = configs.c4_program(sample_tokens, D_FULL, F_FULL)
+    ins = configs.c4_inputs(sample_tokens, D_FULL, F_FULL, seed=4)
+    mod = ev.parse(text)
+    t0 = time.perf_counter()
+    ev.evaluate(mod, [ins], fast_dot=True)
+    dt = time.perf_counter() - t0
+    flops = configs.C4_GEMM_FLOPS(sample_tokens, D_FULL, F_FULL)
+    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port", "seconds": dt,
+            "sample": f"{sample_tokens} of {T_FULL} tokens, full d={D_FULL} ff={F_FULL}; NumPy oracle, f32 BLAS GEMMs on all host threads"}
+
+
+def run_reference(args) -> dict:
+    rank, world, _ = _dist()
+    if rank != 0:
+        return None
+    from oracle import stablehlo_eval as ev
+    from ryft_b200 import configs
+    sample = 256
+    text = configs.c4_program(sample, D_FULL, F_FULL)
+    ins = configs.c4_inputs(sample, D_FULL, F_FULL, seed=4)
+    mod = ev.parse(text)
+    flops = configs.C4_GEMM_FLOPS(sample, D_FULL, F_FULL)
+    for _ in range(args.warmup):
+        ev.evaluate(mod, [ins], fast_dot=True)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        ev.evaluate(mod, [ins], fast_dot=True)
+    dt = time.perf_counter() - t0
+    value = flops * args.steps / dt / 1e12
+    sample_txt = f"{sample} of {T_FULL} tokens per step, full d={D_FULL} ff={F_FULL}; NumPy oracle (port of StableHLO semantics), f32 BLAS on all host threads"
+    return {"impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 operands, f32 accumulate",
+            "data": "synthetic", "config": {"workload": "config 5 / config 4 gradient step (CPU, bounded token sample)", "replicas": 1},
+            "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port", "sample": sample_txt},
+            "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "the reference runs this path inside OpenXLA's CPU PJRT plugin, which cannot be built or fetched in this environment; the CPU oracle is timed instead"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    ap.add_argument("--config", default="c5", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "own":
+        args.warmup = 3
+    line = run_reference(args) if args.impl == "reference" else run_own(args)
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

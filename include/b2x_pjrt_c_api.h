@@ -672,6 +672,45 @@ typedef struct PJRT_Api {
   B2X_PJRT_FN(PJRT_Executable_ParameterMemoryKinds);
 } PJRT_Api;
 
+/* ---- extensions reachable from PJRT_Api::extension_start (linked list of PJRT_Extension_Base) ---------------------- */
+
+/* Stream extension, type id 3 (crates/ryft-pjrt/src/extensions/stream.rs:123-160; ids: crates/ryft-pjrt/src/lib.rs:179-203).
+ * `PJRT_Get_Stream_For_External_Ready_Events` returns the device's compute stream, the stream every kernel of an
+ * execution is launched on, so that a caller can order its own work, or CUDA timing events, against executions.
+ * `PJRT_Wait_Until_Buffer_Ready_On_Stream` makes `stream` wait for the buffer's definition event. */
+#define PJRT_Extension_Type_Stream 3
+typedef struct { size_t struct_size; PJRT_Device* device; intptr_t stream; /* out */ } PJRT_Get_Stream_For_External_Ready_Events_Args;
+typedef struct { size_t struct_size; intptr_t stream; PJRT_Buffer* buffer; } PJRT_Wait_Until_Buffer_Ready_On_Stream_Args;
+typedef struct PJRT_Stream_Extension {
+  PJRT_Extension_Base base;
+  PJRT_Error* (*get_stream)(PJRT_Get_Stream_For_External_Ready_Events_Args*);
+  PJRT_Error* (*wait_stream)(PJRT_Wait_Until_Buffer_Ready_On_Stream_Args*);
+} PJRT_Stream_Extension;
+
+/* Step-timing extension (no counterpart in the reference; private type id).  When enabled for a loaded executable,
+ * every later execution brackets each plan step with CUDA events on the stream the step runs on.  `collect` waits
+ * for the recorded executions, sums the device time per step and resets the record.  Arrays are borrowed from the
+ * executable and stay valid until the next call. */
+#define B2X_Extension_Type_StepTiming 0x62327801u
+typedef struct {
+  size_t struct_size;
+  PJRT_LoadedExecutable* executable;
+  size_t device_index;        /* index into the executable's addressable devices */
+  int enable;                 /* in: 1 = start recording, 0 = stop, -1 = leave as is */
+  int collect;                /* in: non-zero = gather the timings recorded so far */
+  size_t num_steps;           /* out */
+  size_t num_executions;      /* out: executions summed in step_ms */
+  const float* step_ms;       /* out: total device milliseconds per step over those executions */
+  const char* const* labels;  /* out: one NUL-terminated label per step ("gemm ...", "reduce ...") */
+  const double* flops;        /* out: algorithmic FLOPs of one launch of the step */
+  const double* bytes;        /* out: algorithmic bytes of one launch of the step */
+  const int* kernel_launches; /* out: kernels this library launches per step (0 for NCCL collectives and copies) */
+} B2X_StepTiming_Args;
+typedef struct B2X_StepTiming_Extension {
+  PJRT_Extension_Base base;
+  PJRT_Error* (*step_timing)(B2X_StepTiming_Args*);
+} B2X_StepTiming_Extension;
+
 /* The one exported symbol of the plugin (crates/ryft-pjrt/src/plugins.rs:67-79). */
 const PJRT_Api* GetPjrtApi(void);
 

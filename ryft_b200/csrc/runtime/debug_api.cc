@@ -29,3 +29,21 @@ extern "C" __attribute__((visibility("default"))) int b2x_plan_dump(const char* 
   }
   return code;
 }
+
+#include "objects.h"
+
+// Parses a serialized CompileOptionsProto the way PJRT_Client_Compile does and reports the fields the executor
+// honours: out[0] = replica_count, out[1] = partition_count, out[2] = device_ordinal, out[3] = precision,
+// out[4] = number of device-assignment entries, out[5..] = the assignment (replica -> device id), up to cap entries.
+extern "C" __attribute__((visibility("default"))) int b2x_debug_parse_compile_options(const char* data, size_t size, int64_t* out, size_t cap) {
+  b2x::CompileOptions co;
+  std::string err;
+  if (!b2x::parse_compile_options(data, size, &co, &err)) return 3;
+  if (cap < 5) return 3;
+  out[0] = co.num_replicas; out[1] = co.num_partitions; out[2] = co.device_ordinal; out[3] = co.precision;
+  size_t n = 0;
+  if (co.has_device_assignment && !co.da_devices.empty())
+    for (auto d : co.da_devices[0]) { if (5 + n < cap) out[5 + n] = d; n++; }
+  out[4] = (int64_t)n;
+  return 0;
+}

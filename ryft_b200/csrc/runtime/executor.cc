@@ -46,8 +46,13 @@ PJRT_Error* run_plan(PJRT_LoadedExecutable* le, int local_index, int replica, co
   cudaStream_t cs = dev->compute;
   B2xVmProgram prog;
   std::vector<int> outstanding;
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>>* timed = nullptr;
+  if (pd.timing) { pd.timed.emplace_back(); timed = &pd.timed.back(); }
   for (const Step& s : plan.steps) {
     for (int w : s.wait_colls) B2X_CUDA(cudaStreamWaitEvent(cs, pd.coll_done[w], 0));
+    const bool on_comm = s.kind == StepKind::ALL_REDUCE || s.kind == StepKind::ALL_GATHER;
+    cudaEvent_t t0 = nullptr, t1 = nullptr;
+    if (timed && !on_comm) { B2X_CUDA(cudaEventCreate(&t0)); B2X_CUDA(cudaEventCreate(&t1)); B2X_CUDA(cudaEventRecord(t0, cs)); }
     switch (s.kind) {
       case StepKind::ELEMENTWISE: {
         bind_program(s.vm, bind, &prog);
@@ -120,6 +125,7 @@ PJRT_Error* run_plan(PJRT_LoadedExecutable* le, int local_index, int replica, co
         if (group.empty()) return make_error(PJRT_Error_Code_INTERNAL, "replica is in no replica group");
         B2X_CUDA(cudaEventRecord(pd.fork, cs));
         B2X_CUDA(cudaStreamWaitEvent(dev->comm, pd.fork, 0));
+        if (timed) { B2X_CUDA(cudaEventCreate(&t0)); B2X_CUDA(cudaEventCreate(&t1)); B2X_CUDA(cudaEventRecord(t0, dev->comm)); }
         for (auto& c : s.colls) {
           void* src = bind(c.src);
           void* dst = bind(c.dst);
@@ -134,6 +140,7 @@ PJRT_Error* run_plan(PJRT_LoadedExecutable* le, int local_index, int replica, co
                               : le->client->nccl->all_gather(comm, src, dst, (size_t)c.count, (int)c.dtype, dev->comm);
           if (e) return e;
         }
+        if (timed) B2X_CUDA(cudaEventRecord(t1, dev->comm));
         B2X_CUDA(cudaEventRecord(pd.coll_done[s.coll_id], dev->comm));
         outstanding.push_back(s.coll_id);
         break;
@@ -141,6 +148,10 @@ PJRT_Error* run_plan(PJRT_LoadedExecutable* le, int local_index, int replica, co
       case StepKind::COPY:
         B2X_CUDA(cudaMemcpyAsync(bind(s.c_dst), bind(s.c_src), (size_t)s.c_bytes, cudaMemcpyDeviceToDevice, cs));
         break;
+    }
+    if (timed) {
+      if (!on_comm) B2X_CUDA(cudaEventRecord(t1, cs));
+      timed->push_back({t0, t1});
     }
   }
   for (int id : outstanding) B2X_CUDA(cudaStreamWaitEvent(cs, pd.coll_done[id], 0));

@@ -146,7 +146,15 @@ struct PJRT_LoadedExecutable {
     void* consts = nullptr;
     std::vector<cudaEvent_t> coll_done;   // one per collective step
     cudaEvent_t fork = nullptr;
+    // step timing (B2X_StepTiming_Extension)
+    bool timing = false;
+    std::vector<std::vector<std::pair<cudaEvent_t, cudaEvent_t>>> timed;  // [execution][step]
+    std::vector<float> step_ms;
   };
+  std::vector<std::string> step_labels;
+  std::vector<const char*> step_label_ptrs;
+  std::vector<double> step_flops, step_bytes;
+  std::vector<int> step_launches;
   std::vector<PerDevice> per_device;
   std::mutex mu;
   ~PJRT_LoadedExecutable();

@@ -131,6 +131,7 @@ PJRT_LoadedExecutable::~PJRT_LoadedExecutable() {
     if (pd.consts) cudaFree(pd.consts);
     for (auto e : pd.coll_done) cudaEventDestroy(e);
     if (pd.fork) cudaEventDestroy(pd.fork);
+    for (auto& exec : pd.timed) for (auto& ev : exec) { if (ev.first) cudaEventDestroy(ev.first); if (ev.second) cudaEventDestroy(ev.second); }
   }
 }
 
@@ -760,6 +761,7 @@ static PJRT_Error* Buffer_Bitcast(PJRT_Buffer_Bitcast_Args*) { return make_error
 
 // ---- compile / executables ----------------------------------------------------------------------------------------------
 
+static int step_kernel_launches(const Step& s);
 static uint64_t fnv1a(const std::string& s, uint64_t h = 1469598103934665603ull) {
   for (unsigned char c : s) { h ^= c; h *= 1099511628211ull; }
   return h;
@@ -823,9 +825,9 @@ static PJRT_Error* build_core(PJRT_Client* client, const std::string& code, cons
   char fp[40];
   snprintf(fp, sizeof(fp), "%016llx", (unsigned long long)fnv1a(options, fnv1a(code)));
   core->fingerprint = fp;
-  core->cost_names = {"flops", "bytes accessed"};
-  core->cost_props.resize(2);
-  for (int i = 0; i < 2; i++) {
+  core->cost_names = {"flops", "bytes accessed", "kernel launches"};
+  core->cost_props.resize(3);
+  for (int i = 0; i < 3; i++) {
     memset(&core->cost_props[i], 0, sizeof(PJRT_NamedValue));
     core->cost_props[i].struct_size = sizeof(PJRT_NamedValue);
     core->cost_props[i].name = core->cost_names[i].data(); core->cost_props[i].name_size = core->cost_names[i].size();
@@ -833,6 +835,11 @@ static PJRT_Error* build_core(PJRT_Client* client, const std::string& code, cons
   }
   core->cost_props[0].float_value = (float)p.total_flops;
   core->cost_props[1].float_value = (float)p.total_bytes;
+  {
+    int launches = 0;
+    for (auto& st : p.steps) launches += step_kernel_launches(st);
+    core->cost_props[2].float_value = (float)launches;
+  }
   *out = core;
   return nullptr;
 }
@@ -1171,12 +1178,98 @@ static PJRT_Error* LoadedExecutable_Execute(PJRT_LoadedExecutable_Execute_Args* 
   return ret;
 }
 
+// ---- extensions -----------------------------------------------------------------------------------------------------------
+
+static PJRT_Error* Ext_GetStream(PJRT_Get_Stream_For_External_Ready_Events_Args* a) {
+  B2X_CHECK_ARG(a->device && a->device->addressable, "the device is not addressable");
+  a->stream = (intptr_t)a->device->compute;
+  return nullptr;
+}
+static PJRT_Error* Ext_WaitStream(PJRT_Wait_Until_Buffer_Ready_On_Stream_Args* a) {
+  PJRT_Buffer* b = a->buffer;
+  std::lock_guard<std::mutex> lk(b->mu);
+  B2X_RETURN_IF_ERROR(check_live(b));
+  B2X_CUDA(cudaSetDevice(b->device->cuda_ordinal));
+  if (b->ready) B2X_CUDA(cudaStreamWaitEvent((cudaStream_t)a->stream, b->ready, 0));
+  return nullptr;
+}
+
+static int step_kernel_launches(const Step& s) {
+  switch (s.kind) {
+    case StepKind::ELEMENTWISE: return 1;
+    case StepKind::REDUCE: return reduce_splits(s.rA, s.rR, s.rB) > 1 ? 2 : 1;
+    case StepKind::GEMM: return s.g_split_f32 ? 3 : 1;
+    case StepKind::ATTENTION: return 1;
+    default: return 0;
+  }
+}
+
+static PJRT_Error* Ext_StepTiming(B2X_StepTiming_Args* a) {
+  PJRT_LoadedExecutable* le = a->executable;
+  B2X_CHECK_ARG(le && a->device_index < le->per_device.size(), "bad executable or device index");
+  std::lock_guard<std::mutex> lk(le->mu);
+  PJRT_LoadedExecutable::PerDevice& pd = le->per_device[a->device_index];
+  const Plan& plan = le->core->plans[0];
+  if (le->step_labels.empty()) {
+    for (auto& s : plan.steps) {
+      const char* kind = s.kind == StepKind::GEMM ? (s.g_tensor_core ? "gemm_tc " : "gemm_simt ") : s.kind == StepKind::REDUCE ? "reduce " :
+                         s.kind == StepKind::ELEMENTWISE ? "elementwise " : s.kind == StepKind::ATTENTION ? "attention " :
+                         s.kind == StepKind::COPY ? "copy " : "collective ";
+      le->step_labels.push_back(std::string(kind) + s.label);
+      le->step_flops.push_back(s.flops);
+      le->step_bytes.push_back(s.bytes);
+      le->step_launches.push_back(step_kernel_launches(s));
+    }
+    for (auto& l : le->step_labels) le->step_label_ptrs.push_back(l.c_str());
+  }
+  if (a->enable >= 0) pd.timing = a->enable != 0;
+  a->num_steps = plan.steps.size();
+  a->labels = le->step_label_ptrs.data();
+  a->flops = le->step_flops.data();
+  a->bytes = le->step_bytes.data();
+  a->kernel_launches = le->step_launches.data();
+  a->num_executions = 0;
+  pd.step_ms.assign(plan.steps.size(), 0.f);
+  if (a->collect) {
+    B2X_CUDA(cudaSetDevice(le->addressable[a->device_index]->cuda_ordinal));
+    for (auto& exec : pd.timed) {
+      for (size_t i = 0; i < exec.size() && i < pd.step_ms.size(); i++) {
+        float ms = 0.f;
+        cudaError_t e = cudaEventSynchronize(exec[i].second);
+        if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, exec[i].first, exec[i].second);
+        if (e != cudaSuccess) return cuda_error(e, "reading step timing events");
+        pd.step_ms[i] += ms;
+        cudaEventDestroy(exec[i].first);
+        cudaEventDestroy(exec[i].second);
+      }
+      a->num_executions++;
+    }
+    pd.timed.clear();
+  }
+  a->step_ms = pd.step_ms.data();
+  return nullptr;
+}
+
 // ---- table ----------------------------------------------------------------------------------------------------------------
 
 static PJRT_Api make_api() {
+  static PJRT_Stream_Extension stream_ext;
+  static B2X_StepTiming_Extension timing_ext;
+  memset(&stream_ext, 0, sizeof(stream_ext));
+  memset(&timing_ext, 0, sizeof(timing_ext));
+  timing_ext.base.struct_size = sizeof(timing_ext);
+  timing_ext.base.extension_type = B2X_Extension_Type_StepTiming;
+  timing_ext.base.next = nullptr;
+  timing_ext.step_timing = Ext_StepTiming;
+  stream_ext.base.struct_size = sizeof(stream_ext);
+  stream_ext.base.extension_type = PJRT_Extension_Type_Stream;
+  stream_ext.base.next = &timing_ext.base;
+  stream_ext.get_stream = Ext_GetStream;
+  stream_ext.wait_stream = Ext_WaitStream;
   PJRT_Api api;
   memset(&api, 0, sizeof(api));
   api.struct_size = sizeof(PJRT_Api);
+  api.extension_start = &stream_ext.base;
   api.pjrt_api_version.struct_size = sizeof(PJRT_Api_Version);
   api.pjrt_api_version.major_version = PJRT_API_MAJOR;
   api.pjrt_api_version.minor_version = PJRT_API_MINOR;

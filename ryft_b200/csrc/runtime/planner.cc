@@ -953,6 +953,8 @@ void Planner::emit_collective(const Op& op) {
     }
   }
   if ((int)seen.size() != opt_.num_replicas) unimplemented("replica_groups that do not cover every replica");
+  struct PendingCopy { Layout src; BufRef dst; DType dt; std::vector<int64_t> dims; };
+  std::vector<PendingCopy> pending_copies;
   for (size_t i = 0; i < op.operands.size(); i++) {
     const Value* x = op.operands[i];
     const Value* r = op.results[i];
@@ -969,8 +971,15 @@ void Planner::emit_collective(const Op& op) {
     if (op.kind == OpKind::ALL_GATHER) {
       for (int d = 0; d < x->type.rank(); d++) { if (d < op.iota_dim) c.outer *= x->type.dims[d]; else c.inner *= x->type.dims[d]; }
       if (c.outer != 1) {
-        // NCCL gathers along the outermost dimension; other dims go through a staging buffer + strided copy
-        unimplemented("all_gather along a dimension that is not the outermost non-unit dimension");
+        // NCCL concatenates whole operands (a new outermost group dim); for an inner all_gather_dim the gathered
+        // [G, outer, inner] staging buffer is rearranged into [outer, G, inner] by a strided copy afterwards
+        const int64_t G = (int64_t)s.replica_groups[0].size();
+        BufRef final_dst = c.dst;
+        c.dst = new_temp(r->type.byte_size());
+        Layout src;
+        src.buf = c.dst;
+        src.strides = {c.inner, c.outer * c.inner, 1};
+        pending_copies.push_back({src, final_dst, x->type.dtype, {c.outer, G, c.inner}});
       }
     } else {
       if (dtype_size(c.dtype) == 8 && c.dtype != DType::F64 && c.dtype != DType::S64 && c.dtype != DType::U64) internal("bad dtype");
@@ -980,6 +989,21 @@ void Planner::emit_collective(const Op& op) {
     s.colls.push_back(c);
   }
   plan_.steps.push_back(std::move(s));
+  for (auto& pc : pending_copies) {
+    if (dtype_size(pc.dt) == 8) unimplemented("all_gather of 64-bit elements along an inner dimension");
+    GroupBuilder gb;
+    gb.P = this;
+    gb.root_dims = pc.dims;
+    GNode nd;
+    nd.k = GNode::TENSOR;
+    nd.dtype = pc.dt;
+    nd.tensor = gb.add_tensor(pc.src.buf, pc.dt, pc.src.strides);
+    gb.nodes.push_back(nd);
+    int t = gb.add_tensor(pc.dst, pc.dt, row_major_strides(pc.dims));
+    gb.outs.push_back({0, t});
+    VmBinding vb = gb.finish(-1);
+    push_vm_step(std::move(vb), "copy:all_gather_interleave");
+  }
 }
 
 void Planner::emit_outputs() {

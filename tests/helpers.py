@@ -1,0 +1,62 @@
+"""Shared helpers of the parity tests: run a StableHLO program through the PJRT C ABI on the GPU and through the CPU
+oracle on the same inputs, and compare with the build's tolerances: integer / predicate / index results bit-exact;
+f32 <= 1e-4 relative Frobenius error; bf16 and f16 <= 1e-2 max-abs error normalised by the RMS of the expected output."""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import numpy as np
+
+from oracle import stablehlo_eval as ev
+from ryft_b200 import pjrt
+
+F32_REL_FROBENIUS = 1e-4
+BF16_MAX_ABS_OVER_RMS = 1e-2
+
+
+def run_gpu(client, text: str, inputs: Sequence[np.ndarray], options: pjrt.CompilationOptions | None = None) -> List[np.ndarray]:
+    exe = client.compile(pjrt.Program.mlir(text), options or pjrt.CompilationOptions())
+    device = exe.addressable_devices()[0]
+    bufs = [client.buffer(np.ascontiguousarray(x), device=device) for x in inputs]
+    outs = exe.execute([pjrt.ExecutionDeviceInputs(bufs)])
+    outs[0].done.await_()
+    return [o.to_numpy() for o in outs[0].outputs]
+
+
+def run_oracle(text: str, inputs: Sequence[np.ndarray]) -> List[np.ndarray]:
+    return ev.evaluate(text, [list(inputs)])[0]
+
+
+def assert_close(actual: np.ndarray, expected: np.ndarray, what: str = "", f32_tol: float = F32_REL_FROBENIUS,
+                 narrow_tol: float = BF16_MAX_ABS_OVER_RMS) -> None:
+    assert actual.shape == expected.shape, (what, actual.shape, expected.shape)
+    assert actual.dtype == expected.dtype, (what, actual.dtype, expected.dtype)
+    kind = expected.dtype.kind
+    name = expected.dtype.name
+    if kind in "iub":
+        if not np.array_equal(actual, expected):
+            bad = np.argwhere(actual != expected)
+            raise AssertionError(f"{what}: {len(bad)} of {expected.size} integer elements differ; first at {bad[0].tolist()}: "
+                                 f"{actual[tuple(bad[0])]} != {expected[tuple(bad[0])]}")
+        return
+    a64, e64 = actual.astype(np.float64), expected.astype(np.float64)
+    fin = np.isfinite(e64)
+    assert np.array_equal(np.isfinite(a64), fin), f"{what}: non-finite pattern differs"
+    if not fin.all():
+        assert np.array_equal(a64[~fin], e64[~fin], equal_nan=True), f"{what}: inf/nan values differ"
+        a64, e64 = np.where(fin, a64, 0.0), np.where(fin, e64, 0.0)
+    if name in ("bfloat16", "float16"):
+        err = ev.max_abs_over_rms(a64, e64)
+        assert err <= narrow_tol, f"{what}: max-abs/RMS error {err:.3e} exceeds {narrow_tol}"
+    else:
+        err = ev.rel_frobenius(a64, e64)
+        assert err <= f32_tol, f"{what}: relative Frobenius error {err:.3e} exceeds {f32_tol}"
+
+
+def check_program(client, text: str, inputs: Sequence[np.ndarray], what: str = "", **tol) -> List[np.ndarray]:
+    got = run_gpu(client, text, inputs)
+    want = run_oracle(text, inputs)
+    assert len(got) == len(want)
+    for i, (g, w) in enumerate(zip(got, want)):
+        assert_close(g, w, f"{what} output {i}", **tol)
+    return got

@@ -1,0 +1,136 @@
+"""The C-ABI boundary, checked without a GPU: the libraries load, export what include/*.h declares, the PJRT_Api
+table has the reference's layout and version, and the host-only entry points (errors, events, plugin attributes)
+behave as ryft-pjrt's tests expect (crates/ryft-pjrt/src/lib.rs:548-591, events.rs:566-648)."""
+import ctypes as C
+import re
+import subprocess
+import threading
+from pathlib import Path
+
+import pytest
+
+import ryft_b200
+from ryft_b200 import pjrt
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _exports(path):
+    out = subprocess.run(["nm", "-D", "--defined-only", str(path)], capture_output=True, text=True, check=True).stdout
+    return {line.split()[-1] for line in out.splitlines() if line.strip()}
+
+
+def test_libraries_exist_and_load():
+    assert ryft_b200.PLUGIN_PATH.exists(), "build the native library: python -m ryft_b200.build"
+    assert ryft_b200.KERNELS_PATH.exists()
+    C.CDLL(str(ryft_b200.PLUGIN_PATH))
+    C.CDLL(str(ryft_b200.KERNELS_PATH))
+
+
+def test_plugin_exports_only_get_pjrt_api():
+    # the reference's plugins export exactly this symbol (crates/ryft-xla-sys/pjrt_plugin_version_script.lds:1-7)
+    assert _exports(ryft_b200.PLUGIN_PATH) == {"GetPjrtApi"}
+
+
+def test_kernel_library_exports_every_declared_entry_point():
+    header = (ROOT / "include" / "b2x_kernels.h").read_text()
+    declared = set(re.findall(r"B2X_API\s+\w+\s+(b2x_\w+)\(", header))
+    assert len(declared) >= 8
+    assert declared <= _exports(ryft_b200.KERNELS_PATH)
+
+
+def test_api_table_layout_and_version(plugin):
+    names = pjrt.api_function_names()
+    assert len(names) == 135                      # crates/ryft-pjrt/src/lib.rs:222-363
+    assert names[0] == "PJRT_Error_Destroy" and names[-1] == "PJRT_Executable_ParameterMemoryKinds"
+    assert plugin.version() == (0, 104)           # crates/ryft-pjrt/src/versions.rs:33-34
+    assert plugin.api.struct_size == 16 + 24 + 8 * 135
+    must = ["Client_Destroy", "Buffer_Destroy", "Event_Destroy", "Executable_Destroy", "LoadedExecutable_Destroy", "ExecuteContext_Destroy",
+            "Error_Destroy", "Error_Message", "Error_GetCode", "Plugin_Initialize", "Client_Compile", "LoadedExecutable_Execute",
+            "Client_BufferFromHostBuffer", "Buffer_ToHostBuffer", "Event_Await", "Event_OnReady"]
+    for m in must:
+        assert plugin.api.has(m), m
+    # optional subsystems stay NULL, which ryft maps to Unimplemented (crates/ryft-pjrt/src/macros.rs:36-44)
+    assert not plugin.api.has("TopologyDescription_Create")
+    with pytest.raises(pjrt.PjrtError) as e:
+        plugin.api.call("TopologyDescription_Create", pjrt.A["Plugin_Initialize"]())
+    assert e.value.code == 12
+
+
+def test_plugin_attributes(plugin):
+    # crates/ryft-pjrt/src/lib.rs:575-577
+    assert plugin.attribute("stablehlo_current_version") == [1, 16, 0]
+    assert plugin.attribute("stablehlo_minimum_version") == [0, 9, 0]
+    assert plugin.attribute("xla_version") == 2
+    with pytest.raises(pjrt.PjrtError) as e:
+        plugin.attribute("__missing__")
+    assert e.value.code == 5 and "__missing__" in e.value.message
+
+
+def test_load_plugin_is_cached():
+    assert pjrt.load_plugin(ryft_b200.PLUGIN_PATH) is pjrt.load_plugin(ryft_b200.PLUGIN_PATH)
+
+
+def test_missing_library_fails_loudly(tmp_path):
+    with pytest.raises(FileNotFoundError):
+        pjrt.Plugin(tmp_path / "libpjrt-plugin-cuda-13.so")
+
+
+def test_event_set_await_on_ready(plugin):
+    # crates/ryft-pjrt/src/events.rs:566-648
+    ev = pjrt.Event.create(plugin.api)
+    assert not ev.ready()
+    seen = []
+    ev.on_ready(lambda err: seen.append(("before", err)))
+    ev.set()
+    assert ev.ready() and ev.error() is None
+    ev.on_ready(lambda err: seen.append(("after", err)))
+    assert seen == [("before", None), ("after", None)]
+    ev.await_()
+    with pytest.raises(pjrt.PjrtError):
+        ev.set()                                   # an event can be set only once
+
+
+def test_event_error_propagates_code_and_message(plugin):
+    ev = pjrt.Event.create(plugin.api)
+    got = []
+    ev.on_ready(lambda err: got.append(err))
+    ev.set(10, "replica 1 never joined")
+    assert got[0].code == 10 and got[0].message == "replica 1 never joined"
+    err = ev.error()
+    assert err.code == 10
+    with pytest.raises(pjrt.PjrtError) as e:
+        ev.await_()
+    assert e.value.code_name == "ABORTED"
+
+
+def test_event_await_from_another_thread(plugin):
+    ev = pjrt.Event.create(plugin.api)
+    t = threading.Timer(0.05, ev.set)
+    t.start()
+    ev.await_()
+    t.join()
+    assert ev.ready()
+
+
+def test_compile_options_wire_format():
+    # field numbers of crates/ryft-xla-sys/src/protos.rs:3298-3346, 2391-2417, 2340-2354
+    lib = C.CDLL(str(ryft_b200.KERNELS_PATH))
+    lib.b2x_debug_parse_compile_options.argtypes = [C.c_char_p, C.c_size_t, C.POINTER(C.c_int64), C.c_size_t]
+    out = (C.c_int64 * 16)()
+    blob = pjrt.CompilationOptions(replica_count=4, partition_count=1, device_assignment=[3, 2, 1, 0], precision=2).encode()
+    assert lib.b2x_debug_parse_compile_options(blob, len(blob), out, 16) == 0
+    assert list(out[:5]) == [4, 1, -1, 2, 4] and list(out[5:9]) == [3, 2, 1, 0]
+    blob = pjrt.CompilationOptions().encode()
+    assert lib.b2x_debug_parse_compile_options(blob, len(blob), out, 16) == 0
+    assert list(out[:5]) == [1, 1, -1, 0, 0]
+    assert lib.b2x_debug_parse_compile_options(b"\x1a\x7f", 2, out, 16) == 3   # truncated message is rejected
+
+
+def test_client_create_without_gpu_fails_without_fallback(plugin):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    with pytest.raises(pjrt.PjrtError) as e:
+        plugin.client()
+    assert e.value.code_name == "FAILED_PRECONDITION" and "no CPU execution path" in e.value.message

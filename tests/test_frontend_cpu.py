@@ -1,0 +1,159 @@
+"""Front end and planner, checked on the host through `b2x_plan_dump`: every printed form the reference pins parses,
+fusion decisions are the intended ones, and unsupported input is rejected at compile time with the reference's error
+codes (never executed on the CPU)."""
+import pytest
+
+import ryft_b200
+from ryft_b200 import configs, pjrt
+from ryft_b200.stablehlo import Builder
+
+
+def wrap(body: str, args: str, ret: str, names: str) -> str:
+    return f"module {{\n  func.func @main({args}) -> {ret} {{\n{body}\n    return {names} : {ret.strip('()')}\n  }}\n}}\n"
+
+
+# one entry per printed form pinned by a reference test (file:line of that test in crates/ryft-mlir/src/dialects/stable_hlo/operations/)
+PRINTED_FORMS = [
+    ("arithmetic.rs:695", "%0 = stablehlo.add %arg0, %arg1 : tensor<2x2xi32>", "%arg0: tensor<2x2xi32>, %arg1: tensor<2x2xi32>", "tensor<2x2xi32>"),
+    ("arithmetic.rs:740", "%0 = stablehlo.subtract %arg0, %arg1 : tensor<2x2xi32>", "%arg0: tensor<2x2xi32>, %arg1: tensor<2x2xi32>", "tensor<2x2xi32>"),
+    ("arithmetic.rs:785", "%0 = stablehlo.multiply %arg0, %arg1 : tensor<2x2xi32>", "%arg0: tensor<2x2xi32>, %arg1: tensor<2x2xi32>", "tensor<2x2xi32>"),
+    ("arithmetic.rs:830", "%0 = stablehlo.divide %arg0, %arg1 : tensor<2x2xf32>", "%arg0: tensor<2x2xf32>, %arg1: tensor<2x2xf32>", "tensor<2x2xf32>"),
+    ("arithmetic.rs:650", "%0 = stablehlo.negate %arg0 : tensor<3xi32>", "%arg0: tensor<3xi32>", "tensor<3xi32>"),
+    ("comparison.rs:590", "%0 = stablehlo.maximum %arg0, %arg1 : tensor<3xf32>", "%arg0: tensor<3xf32>, %arg1: tensor<3xf32>", "tensor<3xf32>"),
+    ("comparison.rs:634", "%0 = stablehlo.minimum %arg0, %arg1 : tensor<3xf32>", "%arg0: tensor<3xf32>, %arg1: tensor<3xf32>", "tensor<3xf32>"),
+    ("trigonometric.rs:442", "%0 = stablehlo.tanh %arg0 : tensor<3xf32>", "%arg0: tensor<3xf32>", "tensor<3xf32>"),
+    ("exponential.rs:673", "%0 = stablehlo.exponential %arg0 : tensor<2x2xf32>", "%arg0: tensor<2x2xf32>", "tensor<2x2xf32>"),
+    ("exponential.rs:540-544", "%0 = stablehlo.sqrt %arg0 {result_accuracy = #stablehlo.result_accuracy<mode = #stablehlo.result_accuracy_mode<HIGHEST>>} : tensor<2x2xf32>",
+     "%arg0: tensor<2x2xf32>", "tensor<2x2xf32>"),
+    ("casting.rs:456", "%0 = stablehlo.convert %arg0 : (tensor<3xi32>) -> tensor<3xf32>", "%arg0: tensor<3xi32>", "tensor<3xf32>"),
+    ("comparison.rs:500", "%0 = stablehlo.compare GE, %arg0, %arg1, TOTALORDER : (tensor<3xf32>, tensor<3xf32>) -> tensor<3xi1>",
+     "%arg0: tensor<3xf32>, %arg1: tensor<3xf32>", "tensor<3xi1>"),
+    ("control_flow.rs:596", "%0 = stablehlo.select %arg0, %arg1, %arg2 : tensor<3x4xi1>, tensor<3x4xi32>",
+     "%arg0: tensor<3x4xi1>, %arg1: tensor<3x4xi32>, %arg2: tensor<3x4xi32>", "tensor<3x4xi32>"),
+    ("control_flow.rs:361", "%0 = stablehlo.constant dense<0> : tensor<2xi32>", "", "tensor<2xi32>"),
+    ("miscellaneous.rs:1144", "%0 = stablehlo.constant dense<[[0, 1, 2, 3], [4, 5, 6, 7]]> : tensor<2x4xi32>", "", "tensor<2x4xi32>"),
+    ("elements.rs:1335", "%0 = stablehlo.constant dense<[1.500000e+00, -2.500000e+00]> : tensor<2xf32>", "", "tensor<2xf32>"),
+    ("float.rs:12-24", "%0 = stablehlo.constant dense<0xFF800000> : tensor<2xf32>", "", "tensor<2xf32>"),
+    ("miscellaneous.rs:1181", "%0 = stablehlo.iota dim = 1 : tensor<4x5xi32>", "", "tensor<4x5xi32>"),
+    ("manipulation.rs:2154", "%0 = stablehlo.broadcast_in_dim %arg0, dims = [2, 1] : (tensor<1x3xi32>) -> tensor<2x3x2xi32>", "%arg0: tensor<1x3xi32>", "tensor<2x3x2xi32>"),
+    ("manipulation.rs:2022", "%0 = stablehlo.transpose %arg0, dims = [2, 0, 1] : (tensor<3x4x5xi32>) -> tensor<5x3x4xi32>", "%arg0: tensor<3x4x5xi32>", "tensor<5x3x4xi32>"),
+    ("manipulation.rs:2065", "%0 = stablehlo.reshape %arg0 : (tensor<1x6xi32>) -> tensor<2x3xi32>", "%arg0: tensor<1x6xi32>", "tensor<2x3xi32>"),
+    ("linear_algebra.rs:2245-2258",
+     "%0 = stablehlo.dot_general %arg0, %arg1, batching_dims = [0] x [0], contracting_dims = [2] x [1], algorithm = <lhs_precision_type = tf32, rhs_precision_type = tf32, "
+     "accumulation_type = f32, lhs_component_count = 1, rhs_component_count = 1, num_primitive_operations = 1, allow_imprecise_accumulation = false> "
+     ": (tensor<2x2x2xf32>, tensor<2x2x2xf32>) -> tensor<2x2x2xf32>", "%arg0: tensor<2x2x2xf32>, %arg1: tensor<2x2x2xf32>", "tensor<2x2x2xf32>"),
+    ("devices.rs:1265-1270", "%0 = stablehlo.dot_general %arg0, %arg1, batching_dims = [] x [], contracting_dims = [1] x [0] : (tensor<4x4xf32>, tensor<4x4xf32>) -> tensor<4x4xf32>",
+     "%arg0: tensor<4x4xf32>, %arg1: tensor<4x4xf32>", "tensor<4x4xf32>"),
+    ("functional.rs:534-536", "%0 = stablehlo.reduce(%arg0 init: %arg1) applies stablehlo.add across dimensions = [1] : (tensor<3x4xi32>, tensor<i32>) -> tensor<3xi32>",
+     "%arg0: tensor<3x4xi32>, %arg1: tensor<i32>", "tensor<3xi32>"),
+    ("communication.rs:168-173", "%0 = stablehlo.replica_id : tensor<ui32>", "", "tensor<ui32>"),
+]
+
+
+@pytest.mark.parametrize("where,line,args,ret", PRINTED_FORMS, ids=[p[0] for p in PRINTED_FORMS])
+def test_printed_forms_parse_and_plan(where, line, args, ret):
+    text = wrap("    " + line, args, ret, "%0")
+    dump = ryft_b200.plan_dump(text)
+    assert dump.startswith("plan main:")
+
+
+def test_generic_forms_of_collectives_parse():
+    # communication.rs:1759-1767 and :1692-1697
+    text = """
+module {
+  func.func @main(%arg0: tensor<2x2xf32>, %arg1: tensor<2x2xi32>) -> (tensor<2x2xf32>, tensor<2x4xi32>) {
+    %0 = "stablehlo.all_reduce"(%arg0) <{channel_handle = #stablehlo.channel_handle<handle = 1, type = 1>, replica_groups = dense<[[0, 2], [1, 3]]> : tensor<2x2xi64>, use_global_device_ids}> ({
+    ^bb0(%arg2: tensor<f32>, %arg3: tensor<f32>):
+      %2 = stablehlo.add %arg2, %arg3 : tensor<f32>
+      stablehlo.return %2 : tensor<f32>
+    }) : (tensor<2x2xf32>) -> tensor<2x2xf32>
+    %1 = "stablehlo.all_gather"(%arg1) <{all_gather_dim = 1 : i64, channel_handle = #stablehlo.channel_handle<handle = 1, type = 0>, replica_groups = dense<[[0, 2], [1, 3]]> : tensor<2x2xi64>, use_global_device_ids}> : (tensor<2x2xi32>) -> tensor<2x4xi32>
+    return %0, %1 : tensor<2x2xf32>, tensor<2x4xi32>
+  }
+}
+"""
+    dump = ryft_b200.plan_dump(text, num_replicas=4)
+    assert "all_reduce #0" in dump and "all_gather #1" in dump and "copy:all_gather_interleave" in dump
+
+
+def test_reference_add_program_plans_to_one_kernel():
+    text = wrap("    %0 = stablehlo.add %arg0, %arg1 : tensor<2x1xi32>", "%arg0: tensor<2x1xi32>, %arg1: tensor<2x1xi32>", "tensor<2x1xi32>", "%0")
+    dump = ryft_b200.plan_dump(text)
+    assert "1 steps" in dump and "load T0; add T1; store T2;" in dump
+
+
+def test_c2_epilogue_is_fused_into_the_gemm():
+    dump = ryft_b200.plan_dump(configs.c2_program())
+    assert "1 steps" in dump and "tcgen05" in dump
+    assert "load acc0; add T0; tanh aux=1; cvt rn1; store T1;" in dump      # bias add + tanh + convert, one store in bf16
+    assert "arena 0 B" in dump                                               # nothing is materialised
+
+
+def test_c3_mask_is_folded_and_never_materialised():
+    dump = ryft_b200.plan_dump(configs.c3_program(1, 2, 256, 64))
+    # iota / compare / select run inside the first GEMM's epilogue as index arithmetic
+    assert "load iota1; cmp iota2 aux=2;" in dump and "select #0xff800000" in dump
+    assert dump.count("gemm ") == 2 and dump.count("reduce ") == 2
+
+
+def test_c4_plan_shape():
+    dump = ryft_b200.plan_dump(configs.c4_program())
+    assert dump.count("gemm ") == 5 and dump.count("tcgen05") == 5
+    assert "7 steps" in dump                       # 5 GEMMs + loss reduce + scalar scale
+    # the forward GEMM stores H and gelu(H) in bf16 from one accumulator
+    first = dump.split("[1]")[0]
+    assert first.count("store") == 2 and ":bf16" in first and ":f32" not in first.split("vm:")[1].split("code:")[0]
+
+
+def test_c5_collectives_are_split_and_hoisted_behind_their_producers():
+    dump = ryft_b200.plan_dump(configs.c4_program(replicas=8), num_replicas=8)
+    lines = [l for l in dump.splitlines() if l.lstrip().startswith("[")]
+    kinds = [l.split("]")[1].split()[0 if "(wait" not in l else 2] for l in lines]
+    first_ar = next(i for i, l in enumerate(lines) if "all_reduce #0" in l)
+    last_gemm = max(i for i, l in enumerate(lines) if " gemm " in l)
+    assert first_ar < last_gemm, "the first gradient all-reduce must start before the last GEMM is issued"
+    assert sum("(wait #" in l for l in lines) == 2
+
+
+@pytest.mark.parametrize("body,needle", [
+    ("    %0 = stablehlo.custom_call @foo(%arg0) : (tensor<2xf32>) -> tensor<2xf32>", "custom_call"),
+    ("    %0 = stablehlo.sort %arg0 : tensor<2xf32>", "sort"),
+    ('    %0 = "stablehlo.rng_bit_generator"(%arg0) : (tensor<2xf32>) -> tensor<2xf32>', "rng_bit_generator"),
+])
+def test_unsupported_ops_are_rejected_by_name(body, needle):
+    text = wrap(body, "%arg0: tensor<2xf32>", "tensor<2xf32>", "%0")
+    with pytest.raises(pjrt.PjrtError) as e:
+        ryft_b200.plan_dump(text)
+    assert e.value.code_name == "UNIMPLEMENTED" and needle in e.value.message
+
+
+def test_bytecode_is_rejected_with_a_clear_message():
+    with pytest.raises(pjrt.PjrtError) as e:
+        ryft_b200.plan_dump(b"ML\xefR\x00\x01")
+    assert e.value.code_name == "UNIMPLEMENTED" and "bytecode" in e.value.message
+
+
+@pytest.mark.parametrize("body,args,ret", [
+    ("    %0 = stablehlo.add %arg0, %arg1 : tensor<2xf32>", "%arg0: tensor<2xf32>, %arg1: tensor<3xf32>", "tensor<2xf32>"),
+    ("    %0 = stablehlo.dot_general %arg0, %arg1, batching_dims = [] x [], contracting_dims = [1] x [0] : (tensor<2x3xf32>, tensor<4x2xf32>) -> tensor<2x2xf32>",
+     "%arg0: tensor<2x3xf32>, %arg1: tensor<4x2xf32>", "tensor<2x2xf32>"),
+    ("    %0 = stablehlo.broadcast_in_dim %arg0, dims = [0] : (tensor<3xf32>) -> tensor<2x3xf32>", "%arg0: tensor<3xf32>", "tensor<2x3xf32>"),
+])
+def test_malformed_programs_are_invalid_argument(body, args, ret):
+    with pytest.raises(pjrt.PjrtError) as e:
+        ryft_b200.plan_dump(wrap(body, args, ret, "%0"))
+    assert e.value.code_name == "INVALID_ARGUMENT"
+
+
+def test_partitioning_requests_are_unimplemented():
+    text = wrap("    %0 = stablehlo.add %arg0, %arg0 : tensor<2xf32>", '%arg0: tensor<2xf32> {sdy.sharding = #sdy.sharding<@mesh, [{"x"}]>}', "tensor<2xf32>", "%0")
+    assert ryft_b200.plan_dump(text).startswith("plan main")     # attributes alone are accepted
+
+
+def test_builder_matches_reference_program_text():
+    b = Builder()
+    x = b.arg([2, 1], "i32"); y = b.arg([2, 1], "i32")
+    text = b.build(b.add(x, y))
+    # crates/ryft-pjrt/src/programs.rs:2492-2498
+    assert text == ("module {\n  func.func @main(%arg0: tensor<2x1xi32>, %arg1: tensor<2x1xi32>) -> tensor<2x1xi32> {\n"
+                    "    %0 = stablehlo.add %arg0, %arg1 : tensor<2x1xi32>\n    return %0 : tensor<2x1xi32>\n  }\n}\n")

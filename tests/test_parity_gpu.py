@@ -1,0 +1,297 @@
+"""Parity of the CUDA path (through the PJRT C ABI) with the CPU oracle on the same seeded inputs."""
+import os
+
+import numpy as np
+import pytest
+
+from ryft_b200 import configs, pjrt
+from ryft_b200.stablehlo import Builder
+
+from helpers import assert_close, check_program, run_gpu, run_oracle
+
+pytestmark = pytest.mark.gpu
+BF16 = configs.BF16
+
+
+def rnd(shape, dtype, seed=0, scale=1.0):
+    r = np.random.default_rng(seed)
+    if np.dtype(dtype).kind in "iu":
+        info = np.iinfo(dtype)
+        return r.integers(max(info.min, -1000), min(info.max, 1000), size=shape).astype(dtype)
+    if np.dtype(dtype) == np.bool_:
+        return r.integers(0, 2, size=shape).astype(np.bool_)
+    return (r.standard_normal(shape, dtype=np.float32) * np.float32(scale)).astype(dtype)
+
+
+# ---- elementwise ------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["f32", "bf16", "f16"])
+@pytest.mark.parametrize("shape", [(7,), (33, 5), (4, 3, 64), (1024, 1024)])
+def test_float_arithmetic_chain(client, dtype, shape):
+    b = Builder()
+    x = b.arg(shape, dtype); y = b.arg(shape, dtype)
+    t = b.add(b.multiply(x, y), b.subtract(x, y))
+    t = b.maximum(b.minimum(t, b.splat(3.0, t)), b.negate(b.splat(3.0, t)))
+    t = b.divide(t, b.add(b.abs(y), b.splat(1.0, y)))
+    text = b.build(t, b.multiply(b.tanh(x), b.logistic(y)), b.exponential(b.minimum(x, b.splat(2.0, x))), b.sqrt(b.abs(x)), b.rsqrt(b.add(b.abs(y), b.splat(0.5, y))),
+                   b.log(b.add(b.abs(x), b.splat(0.1, x))))
+    npdt = configs.np_dtype(dtype)
+    check_program(client, text, [rnd(shape, npdt, 1), rnd(shape, npdt, 2)], f"chain {dtype} {shape}")
+
+
+@pytest.mark.parametrize("dtype,np_dt", [("i32", np.int32), ("ui32", np.uint32), ("i8", np.int8), ("i16", np.int16), ("ui8", np.uint8)])
+def test_integer_arithmetic_is_bit_exact(client, dtype, np_dt):
+    shape = (257, 9)
+    b = Builder()
+    x = b.arg(shape, dtype); y = b.arg(shape, dtype)
+    text = b.build(b.add(x, y), b.subtract(x, y), b.multiply(x, y), b.maximum(x, y), b.minimum(x, y),
+                   b.divide(x, b.maximum(b.abs(y) if dtype.startswith("i") else y, b.splat(1, y))))
+    check_program(client, text, [rnd(shape, np_dt, 3), rnd(shape, np_dt, 4)], dtype)
+
+
+def test_compare_select_iota_mask_is_bit_exact(client):
+    S = 96
+    b = Builder()
+    x = b.arg([2, 3, S, S], "f32")
+    row = b.iota(0, [S, S], "i32"); col = b.iota(1, [S, S], "i32")
+    mask = b.compare("GE", row, col, "SIGNED")
+    maskb = b.broadcast_in_dim(mask, [2, 3], [2, 3, S, S])
+    y = b.select(maskb, x, b.splat(float("-inf"), x))
+    text = b.build(y, mask, b.add(row, col), b.convert(mask, "i32"))
+    got = check_program(client, text, [rnd((2, 3, S, S), np.float32, 5)], "mask")
+    assert np.array_equal(got[1], np.tril(np.ones((S, S), bool)))
+    assert np.isneginf(got[0][0, 0, 0, 1]) and got[0][0, 0, 5, 5] != -np.inf
+
+
+@pytest.mark.parametrize("direction", ["EQ", "NE", "GE", "GT", "LE", "LT"])
+def test_compare_directions(client, direction):
+    b = Builder()
+    x = b.arg([64], "f32"); y = b.arg([64], "f32"); i = b.arg([64], "i32"); j = b.arg([64], "i32")
+    text = b.build(b.compare(direction, x, y, "FLOAT"), b.compare(direction, i, j, "SIGNED"))
+    xs = rnd((64,), np.float32, 6); ys = xs.copy(); ys[::3] += 1; ys[1::3] -= 1
+    iz = rnd((64,), np.int32, 7); jz = iz.copy(); jz[::2] += 1
+    check_program(client, text, [xs, ys, iz, jz], direction)
+
+
+def test_convert_matrix(client):
+    shape = (1000,)
+    b = Builder()
+    f = b.arg(shape, "f32"); i = b.arg(shape, "i32"); h = b.arg(shape, "bf16")
+    text = b.build(b.convert(f, "bf16"), b.convert(f, "f16"), b.convert(f, "i32"), b.convert(i, "f32"), b.convert(h, "f32"), b.convert(i, "i8"),
+                   b.convert(f, "i1"), b.convert(i, "bf16"), b.convert(b.convert(f, "bf16"), "f16"))
+    fs = rnd(shape, np.float32, 8, 100.0); fs[:4] = [0.0, -0.0, 1.00390625, 131008.0]
+    check_program(client, text, [fs, rnd(shape, np.int32, 9), rnd(shape, BF16, 10)], "convert")
+
+
+def test_f32_to_bf16_rounds_to_nearest_even(client):
+    b = Builder()
+    f = b.arg([4], "f32")
+    text = b.build(b.convert(f, "bf16"))
+    # exactly halfway between two bf16 values: ties go to the even mantissa
+    xs = np.array([1.00390625, 1.01171875, -1.00390625, 65280.0 + 128.0], np.float32)
+    (got,) = run_gpu(client, text, [xs])
+    assert got.astype(np.float32).tolist() == [1.0, 1.015625, -1.0, 65536.0]
+
+
+def test_broadcast_transpose_reshape(client):
+    b = Builder()
+    x = b.arg([6, 8, 10], "f32"); bias = b.arg([8], "f32"); s = b.arg([], "f32")
+    xt = b.transpose(x, [2, 0, 1])                                   # [10, 6, 8]
+    y = b.add(xt, b.broadcast_in_dim(bias, [2], [10, 6, 8]))
+    y = b.multiply(y, b.broadcast_in_dim(s, [], [10, 6, 8]))
+    z = b.reshape(b.transpose(y, [1, 0, 2]), [6, 80])                # needs a materialised copy
+    text = b.build(y, z, b.reshape(x, [48, 10]), b.transpose(x, [1, 2, 0]))
+    check_program(client, text, [rnd((6, 8, 10), np.float32, 11), rnd((8,), np.float32, 12), np.array(1.5, np.float32)], "views")
+
+
+def test_doc_comment_examples_on_gpu(client):
+    # manipulation.rs:303-310 and miscellaneous.rs:74-90, executed
+    b = Builder()
+    x = b.arg([1, 3], "i32")
+    text = b.build(b.broadcast_in_dim(x, [2, 1], [2, 3, 2]), b.iota(0, [4, 5], "i32"), b.iota(1, [4, 5], "i32"))
+    got = run_gpu(client, text, [np.array([[1, 2, 3]], np.int32)])
+    assert got[0].tolist() == [[[1, 1], [2, 2], [3, 3]], [[1, 1], [2, 2], [3, 3]]]
+    assert got[1].tolist() == [[i] * 5 for i in range(4)] and got[2].tolist() == [list(range(5))] * 4
+
+
+def test_constants(client):
+    b = Builder()
+    x = b.arg([2, 3], "f32")
+    c = b.constant_array([[1.5, -2.0, 0.25], [3.0, 4.0, -8.0]], "f32")
+    k = b.constant_array([[1, 2, 3], [4, 5, 6]], "i32")
+    text = b.build(b.add(x, c), k, b.constant(7, [4], "i32"), b.constant(float("inf"), [2], "bf16"))
+    check_program(client, text, [rnd((2, 3), np.float32, 13)], "constants")
+
+
+# ---- reduce -----------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("shape,dims", [((3, 4), [1]), ((1, 6), [1]), ((64, 4096), [1]), ((64, 4096), [0]), ((5, 7, 9), [1]), ((5, 7, 9), [0, 2]),
+                                         ((5, 7, 9), [0, 1, 2]), ((2048, 33), [0]), ((16, 100000), [1]), ((3000000,), [0]), ((8, 128, 72), [0, 1])])
+@pytest.mark.parametrize("body", ["add", "maximum"])
+def test_reduce_f32(client, shape, dims, body):
+    b = Builder()
+    x = b.arg(shape, "f32")
+    init = b.constant(0.0 if body == "add" else float("-inf"), [], "f32")
+    text = b.build(b.reduce(x, init, body, dims))
+    check_program(client, text, [rnd(shape, np.float32, 14)], f"reduce {body} {shape} {dims}")
+
+
+def test_reduce_integer_and_init_operand(client):
+    b = Builder()
+    x = b.arg([3, 4], "i32"); init = b.arg([], "i32")
+    text = b.build(b.reduce(x, init, "add", [1]), b.reduce(x, init, "minimum", [0]), b.reduce(x, init, "multiply", [0, 1]))
+    got = check_program(client, text, [np.arange(12, dtype=np.int32).reshape(3, 4) - 5, np.array(3, np.int32)], "int reduce")
+    assert got[0].tolist() == [-14 + 3, 2 + 3, 18 + 3]
+
+
+def test_reduce_with_fused_prologue_and_bf16(client):
+    b = Builder()
+    x = b.arg([128, 512], "bf16"); y = b.arg([128, 512], "bf16")
+    sq = b.multiply(b.convert(x, "f32"), b.convert(y, "f32"))
+    zero = b.constant(0.0, [], "f32")
+    zb = b.constant(0.0, [], "bf16")
+    text = b.build(b.reduce(sq, zero, "add", [0, 1]), b.reduce(sq, zero, "add", [1]), b.reduce(x, zb, "add", [0]))
+    check_program(client, text, [rnd((128, 512), BF16, 15), rnd((128, 512), BF16, 16)], "prologue")
+
+
+def test_softmax_written_out(client):
+    B, S = 6, 200
+    b = Builder()
+    x = b.arg([B, S], "f32")
+    m = b.reduce(x, b.constant(float("-inf"), [], "f32"), "maximum", [1])
+    e = b.exponential(b.subtract(x, b.broadcast_in_dim(m, [0], [B, S])))
+    l = b.reduce(e, b.constant(0.0, [], "f32"), "add", [1])
+    text = b.build(b.divide(e, b.broadcast_in_dim(l, [0], [B, S])))
+    (got,) = check_program(client, text, [rnd((B, S), np.float32, 17, 3.0)], "softmax")
+    np.testing.assert_allclose(got.sum(axis=1), 1.0, rtol=1e-5)
+
+
+# ---- dot_general --------------------------------------------------------------------------------------------------------
+DOT_CASES = [
+    # (lhs shape, rhs shape, batch dims, contracting dims)
+    ((2, 3), (3, 2), ([], []), ([1], [0])),
+    ((17, 33), (33, 5), ([], []), ([1], [0])),
+    ((33, 17), (33, 5), ([], []), ([0], [0])),
+    ((17, 33), (5, 33), ([], []), ([1], [1])),
+    ((3, 20, 12), (3, 12, 8), ([0], [0]), ([2], [1])),
+    ((4, 6, 5, 7), (6, 4, 7, 9), ([0, 1], [1, 0]), ([3], [2])),
+    ((5, 6, 7), (6, 7, 8), ([], []), ([1, 2], [0, 1])),
+    ((8,), (8,), ([], []), ([0], [0])),
+    ((4, 8), (8,), ([], []), ([1], [0])),
+]
+
+
+@pytest.mark.parametrize("ls,rs,batch,contract", DOT_CASES)
+@pytest.mark.parametrize("dtype", ["f32", "bf16", "i32"])
+def test_dot_general_dimension_numbers(client, ls, rs, batch, contract, dtype):
+    b = Builder()
+    x = b.arg(ls, dtype); y = b.arg(rs, dtype)
+    text = b.build(b.dot_general(x, y, batch, contract, out_dtype="f32" if dtype == "bf16" else None))
+    npdt = configs.np_dtype(dtype)
+    xs, ys = rnd(ls, npdt, 18), rnd(rs, npdt, 19)
+    if dtype == "i32":
+        xs, ys = xs % 50, ys % 50
+    check_program(client, text, [xs, ys], f"dot {ls}x{rs}")
+
+
+def test_dot_general_batched_identity_example(client):
+    # crates/ryft-mlir/src/dialects/stable_hlo/operations/linear_algebra.rs:671-701 (with i32 in place of i64)
+    b = Builder()
+    x = b.arg([2, 2, 2], "i32"); y = b.arg([2, 2, 2], "i32")
+    text = b.build(b.dot_general(x, y, ([0], [0]), ([2], [1])))
+    lhs = np.array([[[1, 2], [3, 4]], [[5, 6], [7, 8]]], np.int32)
+    rhs = np.array([[[1, 0], [0, 1]], [[1, 0], [0, 1]]], np.int32)
+    (got,) = run_gpu(client, text, [lhs, rhs])
+    assert np.array_equal(got, lhs)
+
+
+TC_CASES = [
+    # M, N, K, lhs contracting dim, rhs contracting dim  (NN, NT, TN, TT), sizes include ragged tails in every dim
+    (256, 256, 128, 1, 0), (256, 256, 128, 1, 1), (256, 256, 128, 0, 0), (256, 256, 128, 0, 1),
+    (384, 512, 320, 1, 0), (200, 264, 104, 1, 0), (200, 264, 104, 0, 0), (200, 264, 104, 1, 1), (1000, 72, 64, 1, 0),
+    (128, 64, 32, 1, 0), (136, 136, 2048, 1, 0), (520, 1032, 72, 0, 1),
+]
+
+
+@pytest.mark.parametrize("M,N,K,lc,rc", TC_CASES)
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+def test_tensor_core_gemm_forms(client, M, N, K, lc, rc, dtype):
+    ls = (M, K) if lc == 1 else (K, M)
+    rs = (K, N) if rc == 0 else (N, K)
+    b = Builder()
+    x = b.arg(ls, dtype); y = b.arg(rs, dtype)
+    text = b.build(b.dot_general(x, y, ([], []), ([lc], [rc]), out_dtype="f32"))
+    import ryft_b200
+    assert "tcgen05" in ryft_b200.plan_dump(text)
+    npdt = configs.np_dtype(dtype)
+    check_program(client, text, [rnd(ls, npdt, 20, 0.5), rnd(rs, npdt, 21, 0.5)], f"tc {M}x{N}x{K} lc={lc} rc={rc}", f32_tol=1e-5)
+
+
+def test_tensor_core_gemm_batched_with_fused_epilogue(client):
+    text = configs.c2_program(4, 256, 128, 320)
+    got = check_program(client, text, configs.c2_inputs(4, 256, 128, 320), "c2 small")
+    assert got[0].dtype == BF16
+
+
+def test_f32_gemm_runs_as_three_tf32_products(client):
+    import ryft_b200
+    text = configs.c1_program(512, 768, 512)
+    assert "3xtf32" in ryft_b200.plan_dump(text)
+    check_program(client, text, configs.c1_inputs(512, 768, 512), "c1")            # the 1e-4 bar of the build
+    check_program(client, configs.c1_program(264, 100, 136), configs.c1_inputs(264, 100, 136), "c1 ragged", f32_tol=2e-5)
+
+
+def test_tensor_core_and_cuda_core_paths_agree_at_full_c2_size(client):
+    """Size-independent check at the full benchmark size: two independent kernels, same program, same inputs."""
+    text = configs.c2_program()
+    ins = configs.c2_inputs()
+    (tc,) = run_gpu(client, text, ins)
+    os.environ["B2X_GEMM"] = "simt"
+    try:
+        (simt,) = run_gpu(client, text, ins)
+    finally:
+        del os.environ["B2X_GEMM"]
+    assert_close(tc, simt, "c2 tcgen05 vs simt")
+    # and a slice against the oracle
+    want = run_oracle(configs.c2_program(1, 2048, 128, 2048), [ins[0][:1], ins[1][:1], ins[2]])[0]
+    assert_close(tc[:1], want, "c2 batch 0 vs oracle")
+
+
+# ---- whole configurations at reduced sizes ------------------------------------------------------------------------------
+def test_c3_attention_unfused_path(client):
+    args = (2, 3, 256, 64)
+    check_program(client, configs.c3_program(*args), configs.c3_inputs(*args), "c3 small")
+    check_program(client, configs.c3_program(1, 2, 128, 128, causal=False), configs.c3_inputs(1, 2, 128, 128), "c3 non-causal")
+
+
+def test_c3_causal_property(client):
+    """Causality at a larger size without the oracle: output row t must not change when keys after t change."""
+    args = (1, 2, 512, 128)
+    q, k, v = configs.c3_inputs(*args)
+    text = configs.c3_program(*args)
+    (o1,) = run_gpu(client, text, [q, k, v])
+    k2, v2 = k.copy(), v.copy()
+    k2[:, :, 300:, :] = 0; v2[:, :, 300:, :] = 1
+    (o2,) = run_gpu(client, text, [q, k2, v2])
+    assert np.array_equal(o1[:, :, :300], o2[:, :, :300])
+    assert not np.array_equal(o1[:, :, 300:], o2[:, :, 300:])
+
+
+def test_c4_mlp_gradients(client):
+    T, D, F = 256, 128, 384
+    got = check_program(client, configs.c4_program(T, D, F), configs.c4_inputs(T, D, F), "c4 small")
+    assert got[0].shape == (D, F) and got[1].shape == (F, D) and got[2].shape == ()
+
+
+def test_c4_gradient_matches_finite_difference(client):
+    """Domain property: the hand-written backward pass is the derivative of the loss (checked on one weight)."""
+    T, D, F = 128, 128, 128
+    x, w1, w2 = configs.c4_inputs(T, D, F)
+    text = configs.c4_program(T, D, F)
+    dw1, dw2, loss = run_gpu(client, text, [x, w1, w2])
+    # oracle loss in f64 for a perturbed weight; bf16 storage limits the step, so compare direction and magnitude loosely
+    i, j = np.unravel_index(np.argmax(np.abs(dw2)), dw2.shape)
+    w2p = w2.astype(np.float32).copy(); w2p[i, j] *= 1.25
+    w2p = w2p.astype(BF16)
+    step = float(w2p[i, j].astype(np.float32) - w2[i, j].astype(np.float32))
+    lp = run_oracle(text, [x, w1, w2p])[2]
+    fd = (float(lp) - float(loss)) / step
+    assert np.sign(fd) == np.sign(dw2[i, j]) and abs(fd - dw2[i, j]) <= 0.35 * abs(dw2[i, j])
