@@ -105,6 +105,9 @@ struct PlanOptions {
   bool allow_fused_attention = true;
   bool allow_epilogue_fusion = true;
   int precision = 0;               // Precision::{Default,High,Highest}
+  bool fast_math = false;          // B2X_FAST_MATH=1: hardware-approximate tanh/exp/log where the value is rounded to a
+                                   // 16-bit float before it is stored (about 2^-11 relative error, i.e. frequent one-ulp
+                                   // differences in bf16 results); off by default so that results match a CPU evaluation
 };
 
 // Lowers a verified module to a plan.  `replica` is only used to fold stablehlo.replica_id (plans are otherwise

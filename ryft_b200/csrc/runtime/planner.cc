@@ -374,7 +374,7 @@ void Planner::GroupBuilder::gen(int ni) {
     }
   };
   auto un = [&](uint8_t vop, uint8_t aux) { gen(n.in[0]); emit(vop, nullptr, -1, aux, ci.cls, ci.rnd); };
-  const uint8_t fast = n.precise ? 0 : 1;
+  const uint8_t fast = (P->opt_.fast_math && !n.precise) ? 1 : 0;
   switch (op.kind) {
     case OpKind::ADD: bin(VM_ADD, VM_ADD, 0, ci.cls, ci.rnd); break;
     case OpKind::MULTIPLY: bin(VM_MUL, VM_MUL, 0, ci.cls, ci.rnd); break;

@@ -969,7 +969,7 @@ class Client:
         integer host address paired with `nbytes` semantics through a numpy/torch array's pointer."""
         keep = None
         if isinstance(data, np.ndarray):
-            arr = data if byte_strides is not None else np.ascontiguousarray(data)
+            arr = data if (byte_strides is not None or data.flags.c_contiguous) else data.copy(order="C")
             keep = arr
             ptr = arr.ctypes.data
             if buffer_type is None: buffer_type = _np_to_buffer_type(arr.dtype)
