@@ -47,6 +47,22 @@ typedef struct {
 B2X_API int b2x_reduce_splits(int64_t A, int64_t R, int64_t B);
 B2X_API int b2x_launch_reduce(const B2xVmProgram* host_prologue, const B2xReduceArgs* host_args, b2x_stream_t stream);
 
+/* The same reduction for callers that must not allocate device memory (an embedding runtime that owns the allocator,
+ * a serving loop that cannot afford an allocation stall, a process whose free memory is all pooled elsewhere).  This
+ * entry point has no counterpart in the reference.  `host_args->scratch` is ignored: partial results go to a fixed
+ * array of B2X_REDUCE_NOALLOC_MAX_PARTIALS 32-bit words that is part of the library image (each GPU that loads the
+ * library holds those 64 KiB until the process exits).  It calls no cudaMalloc/cudaFree and no allocating routine.
+ *   - A reduction that needs more partials (A * b2x_reduce_splits(A,R,B) * B, when the split count is > 1) is refused
+ *     with cudaErrorInvalidValue and a message in `err` (may be NULL).
+ *   - The first call on each device looks up the array's device address (with that device current); make that call
+ *     before starting any stream capture.
+ *   - All calls share the one array and it keeps the previous call's contents.  Nothing needs clearing (each call
+ *     overwrites every partial it later reads), but two calls whose kernels overlap on the GPU, on any streams, race
+ *     on it: order them on one stream or with events. */
+#define B2X_REDUCE_NOALLOC_MAX_PARTIALS 16384
+B2X_API int b2x_launch_reduce_noalloc(const B2xVmProgram* host_prologue, const B2xReduceArgs* host_args, b2x_stream_t stream, char* err,
+                                      size_t err_cap);
+
 /* stablehlo.dot_general (linear_algebra.rs:561-592, 756-797) after normalisation to a strided batched GEMM
  * C[b][m][n] = sum_k A[b][m][k] * B[b][k][n].  Strides are in elements.  The accumulator (f32, or s32 for integer
  * inputs) is handed to `epilogue` as VM_SRC_ACC0; the epilogue's root shape is [batch * M, N] linearised row-major

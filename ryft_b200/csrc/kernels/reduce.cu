@@ -7,6 +7,9 @@
 //     warp reads one contiguous span per row; the ry partials meet in shared memory.
 // Long reductions with few outputs are cut into S splits whose partials land in scratch and are folded by a second
 // launch of the same kernel.  HBM-bound: algorithmic bytes = one read of every operand of the prologue.
+#include <cstdio>
+#include <mutex>
+
 #include "../../../include/b2x_kernels.h"
 #include "common.cuh"
 #include "vm.cuh"
@@ -225,4 +228,54 @@ extern "C" int b2x_launch_reduce(const B2xVmProgram* prologue, const B2xReduceAr
   K2.R = S; K2.S = 1; K2.chunk = S; K2.out = a->out;
   int v2 = (a->B == 1) ? ((S % 8 == 0) ? 8 : (S % 4 == 0 ? 4 : 1)) : ((a->B % 8 == 0) ? 8 : (a->B % 4 == 0 ? 4 : 1));
   return launch_one(F, K2, v2, stream);
+}
+
+// ---- reduction entry point that allocates nothing ---------------------------------------------------------------------
+// Some callers of this library run where device memory cannot be requested: inside a framework that owns the whole
+// allocator and forbids foreign cudaMalloc calls, in a latency-critical serving loop where an allocation would stall
+// the device, or after the process has handed all free memory to a pool.  A long reduction with few outputs needs a
+// small buffer for its partial results; here that buffer is a fixed array inside the library image, so such callers
+// can still reduce.  The price is a size limit and no concurrency between calls (see include/b2x_kernels.h).
+namespace b2x {
+static __device__ __align__(256) uint32_t g_reduce_partials[B2X_REDUCE_NOALLOC_MAX_PARTIALS];
+static std::mutex g_partials_mu;
+static void* g_partials_addr[64] = {};
+
+// Device address of the partials array for the current device; looked up once per device.  The array's name is only a
+// host-side handle, never a device pointer, so the address must come from the runtime.
+static int partials_address(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lk(g_partials_mu);
+  if (!g_partials_addr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_reduce_partials);
+    if (e != cudaSuccess) return (int)e;
+    g_partials_addr[dev] = p;
+  }
+  *out = g_partials_addr[dev];
+  return 0;
+}
+}  // namespace b2x
+
+extern "C" int b2x_launch_reduce_noalloc(const B2xVmProgram* prologue, const B2xReduceArgs* a, b2x_stream_t stream, char* err, size_t err_cap) {
+  using namespace b2x;
+  auto fail = [&](int code, const char* fmt, long long x, long long y) {
+    if (err && err_cap) snprintf(err, err_cap, fmt, x, y);
+    return code;
+  };
+  if (err && err_cap) err[0] = 0;
+  const int S = b2x_reduce_splits(a->A, a->R, a->B);
+  const long long need = S > 1 ? (long long)a->A * S * a->B : 0;
+  if (need > B2X_REDUCE_NOALLOC_MAX_PARTIALS)
+    return fail((int)cudaErrorInvalidValue, "this reduction needs %lld partial results but the built-in buffer holds %lld; use b2x_launch_reduce with caller scratch",
+                need, (long long)B2X_REDUCE_NOALLOC_MAX_PARTIALS);
+  void* partials = nullptr;
+  int rc = partials_address(&partials);
+  if (rc) return fail(rc, "could not resolve the built-in partials buffer on this device (CUDA error %lld)%.0lld", (long long)rc, 0LL);
+  B2xReduceArgs b = *a;
+  b.scratch = partials;   // every partial is written by the first pass before the second pass reads it: nothing to clear
+  return b2x_launch_reduce(prologue, &b, stream);
 }
