@@ -11,7 +11,7 @@
 namespace b2x {
 std::atomic<int64_t> g_launch_count{0};
 
-template <int V>
+template <int V, int ID>
 __global__ void __launch_bounds__(256) k_elementwise(const __grid_constant__ B2xVmProgram P, uint64_t n_vec) {
   const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
   uint32_t zero[V];
@@ -19,7 +19,7 @@ __global__ void __launch_bounds__(256) k_elementwise(const __grid_constant__ B2x
   for (int j = 0; j < V; j++) zero[j] = 0;
   for (uint64_t v = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; v < n_vec; v += stride) {
     uint32_t acc[V];
-    vm_run<V>(P, v * V, zero, acc);
+    vm_run<V, ID>(P, v * V, zero, acc);
   }
 }
 }  // namespace b2x
@@ -36,9 +36,16 @@ extern "C" int b2x_launch_elementwise(const B2xVmProgram* prog, int64_t n_elemen
   uint64_t cap = (uint64_t)kNumSms * 8 * 4;
   if (blocks > cap) blocks = cap;
   dim3 grid((unsigned)blocks), block(256);
-  if (vec == 8) k_elementwise<8><<<grid, block, 0, stream>>>(*prog, n_vec);
-  else if (vec == 4) k_elementwise<4><<<grid, block, 0, stream>>>(*prog, n_vec);
-  else k_elementwise<1><<<grid, block, 0, stream>>>(*prog, n_vec);
+  if (vec == 8) {
+    // a program whose structure was known at build time runs as straight-line code, anything else is interpreted
+    switch (vm_static_lookup(vm_signature_hash(*prog))) {
+#define X(I) case I: k_elementwise<8, I><<<grid, block, 0, stream>>>(*prog, n_vec); break;
+      B2X_VM_STATIC_ELEMENTWISE(X)
+#undef X
+      default: k_elementwise<8, 0><<<grid, block, 0, stream>>>(*prog, n_vec); break;
+    }
+  } else if (vec == 4) k_elementwise<4, 0><<<grid, block, 0, stream>>>(*prog, n_vec);
+  else k_elementwise<1, 0><<<grid, block, 0, stream>>>(*prog, n_vec);
   count_launch();
   return (int)cudaGetLastError();
 }

@@ -1,212 +1,7 @@
-// stablehlo.dot_general on the 5th-generation tensor cores: a persistent, warp-specialised tcgen05 GEMM.
-//
-//   C[b][m][n] = sum_k A[b][m][k] * B[b][k][n],  A and B bf16 / f16 (kind::f16) or f32 read as TF32 (kind::tf32),
-//   f32 accumulation in TMEM, result handed to the fused elementwise epilogue program (vm.cuh) which does the stores.
-//
-// One CTA per SM (grid = min(tiles, 148)), 192 threads:
-//   warp 0     TMA producer: per k-block one 128 x BK tile of A and one BN x BK tile of B into a STAGES-deep ring of
-//              128-byte-swizzled shared-memory buffers (cp.async.bulk.tensor, per CTA, no multicast);
-//   warp 1     MMA issuer: one elected lane issues tcgen05.mma (128 x BN x 16) over the ring, commits each stage back
-//              to the producer and each finished accumulator to the epilogue; also owns TMEM allocation;
-//   warps 2-5  epilogue: tcgen05.ld the 128 x BN f32 accumulator (each warp its 32 lanes), run the epilogue program on
-//              8-wide row vectors and store.  Two accumulators (2 x BN TMEM columns) let tile i's epilogue overlap
-//              tile i+1's main loop.
-// Either operand may be K-major (k contiguous) or MN-major (m or n contiguous); the second form covers the
-// transposed contractions of a backward pass without materialising a transpose.
-// Bound: tensor pipe for K >= ~1024 (algorithmic FLOPs = 2*B*M*N*K); HBM (output bytes) for short K.
-// Every mbarrier wait is bounded (sm100.cuh); on expiry the CTA unwinds, frees TMEM and reports through `status`.
-#include "../../../include/b2x_kernels.h"
-#include "common.cuh"
-#include "sm100.cuh"
-#include "vm.cuh"
+// Entry points of the tcgen05 GEMM (kernel: gemm_tc.cuh) and the f32 hi/lo split used by the 3xTF32 scheme.
+#include "gemm_tc.cuh"
 
 namespace b2x {
-
-struct TcParams {
-  int64_t batch, M, N, K;
-  int32_t a_mn_major, b_mn_major;
-  int32_t num_m_tiles, num_n_tiles;
-  int64_t num_tiles;
-  int32_t k_blocks;
-  uint32_t idesc;
-};
-
-constexpr int TC_BM = 128;
-
-template <int BN, int STAGES, bool TF32>
-struct TcSmem {
-  static constexpr int A_BYTES = TC_BM * 128;   // 128 rows (or k-lines x chunks) of 128 bytes
-  static constexpr int B_BYTES = BN * 128;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + slack for 1024-byte alignment
-};
-
-template <int BN, int STAGES, bool TF32>
-__global__ void __launch_bounds__(192, 1)
-k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ TcParams p,
-          const __grid_constant__ B2xVmProgram epi, int32_t* status) {
-  using namespace sm100;
-  using SM = TcSmem<BN, STAGES, TF32>;
-  constexpr int ES = TF32 ? 4 : 2;
-  constexpr int BK = 128 / ES;            // elements per 128-byte line: 64 (16-bit) or 32 (tf32)
-  constexpr int UMMA_K = 32 / ES;         // 16 or 8
-  constexpr int CHUNK = 128 / ES;         // MN-elements per 128-byte line in MN-major layout
-  constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
-
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  const uint32_t smem_base = smem_u32(smem);
-  uint64_t* bars = (uint64_t*)(smem + SM::BAR_OFFSET);
-  // barrier slots: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], drain
-  const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * STAGES, bar_tfull = bar_empty + 8 * STAGES,
-                 bar_tempty = bar_tfull + 16, bar_drain = bar_tempty + 16;
-  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 5);
-  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-    for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 4); }
-    mbar_init(bar_drain, 1);
-    *abort_flag = 0;
-    mbar_fence_init();
-    tma_prefetch_desc(&tmA);
-    tma_prefetch_desc(&tmB);
-  }
-  if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-
-  const int64_t tiles_per_batch = (int64_t)p.num_m_tiles * p.num_n_tiles;
-
-  if (warp == 0) {
-    // ------------------------------------------------ TMA producer ------------------------------------------------
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int64_t t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
-        const int b = (int)(t / tiles_per_batch);
-        const int64_t rem = t - (int64_t)b * tiles_per_batch;
-        const int m0 = (int)(rem % p.num_m_tiles) * TC_BM;
-        const int n0 = (int)(rem / p.num_m_tiles) * BN;
-        for (int kb = 0; kb < p.k_blocks; kb++) {
-          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, status, 1)) { ok = false; break; }
-          const uint32_t full = bar_full + 8 * stage;
-          mbar_expect_tx(full, SM::STAGE_BYTES);
-          const uint32_t sa = smem_base + stage * SM::STAGE_BYTES, sb = sa + SM::A_BYTES;
-          const int k0 = kb * BK;
-          if (!p.a_mn_major) tma_load_3d(sa, &tmA, full, k0, m0, b);
-          else {
-#pragma unroll
-            for (int c = 0; c < TC_BM / CHUNK; c++) tma_load_3d(sa + c * (BK * 128), &tmA, full, m0 + c * CHUNK, k0, b);
-          }
-          if (!p.b_mn_major) tma_load_3d(sb, &tmB, full, k0, n0, b);
-          else {
-#pragma unroll
-            for (int c = 0; c < BN / CHUNK; c++) tma_load_3d(sb + c * (BK * 128), &tmB, full, n0 + c * CHUNK, k0, b);
-          }
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
-        }
-      }
-      if (!ok) {
-        // unwind: let copies already in flight land before the CTA's shared memory goes away
-        for (int s = 0; s < STAGES; s++) {
-          for (uint32_t i = 0; i < (1u << 16); i++) { if (mbar_try_wait(bar_full + 8 * s, 0) || mbar_try_wait(bar_full + 8 * s, 1)) break; __nanosleep(64); }
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------ MMA issuer ----------------------------------------------------
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      int64_t local = 0;
-      for (int64_t t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x, local++) {
-        const int acc = (int)(local & 1);
-        const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
-        if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, status, 2)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = 0; kb < p.k_blocks; kb++) {
-          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, status, 3)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t sa = smem_base + stage * SM::STAGE_BYTES, sb = sa + SM::A_BYTES;
-          // K-major: 8-row groups 1024 B apart, k advances 32 B inside the swizzle atom.
-          // MN-major: 64/32-element chunks BK*128 B apart, 8 k-lines per 1024 B group, k advances UMMA_K lines.
-          const uint64_t a_desc0 = p.a_mn_major ? make_smem_desc(sa, BK * 128, 1024) : make_smem_desc(sa, 16, 1024);
-          const uint64_t b_desc0 = p.b_mn_major ? make_smem_desc(sb, BK * 128, 1024) : make_smem_desc(sb, 16, 1024);
-          const uint32_t a_adv = p.a_mn_major ? (UMMA_K * 128) >> 4 : 32 >> 4;
-          const uint32_t b_adv = p.b_mn_major ? (UMMA_K * 128) >> 4 : 32 >> 4;
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; k++) {
-            umma_ss<TF32>(d_tmem, a_desc0 + (uint64_t)(k * a_adv), b_desc0 + (uint64_t)(k * b_adv), p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
-          }
-          tc_commit(bar_empty + 8 * stage);   // frees the stage once the MMAs above have read it
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
-        }
-        if (ok) tc_commit(bar_tfull + 8 * acc);  // accumulator complete
-      }
-      // drain: everything issued must retire before TMEM is released
-      tc_commit(bar_drain);
-      mbar_wait(bar_drain, 0, abort_flag, nullptr, 0);
-    }
-  } else {
-    // ------------------------------------------------ epilogue ------------------------------------------------------
-    const int quad = warp & 3;              // TMEM lanes [32*quad, 32*quad + 32)
-    bool ok = true;
-    int64_t local = 0;
-    for (int64_t t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x, local++) {
-      const int acc = (int)(local & 1);
-      const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
-      const int b = (int)(t / tiles_per_batch);
-      const int64_t rem = t - (int64_t)b * tiles_per_batch;
-      const int m0 = (int)(rem % p.num_m_tiles) * TC_BM;
-      const int n0 = (int)(rem / p.num_m_tiles) * BN;
-      if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, status, 4)) { ok = false; break; }
-      tc_fence_after();
-      const int64_t row = (int64_t)m0 + quad * 32 + lane;
-      const bool row_ok = row < p.M;
-      const uint64_t row_lin = (uint64_t)(((int64_t)b * p.M + row) * p.N);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; c++) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32), r);
-        tc_wait_ld();
-        if (row_ok) {
-#pragma unroll
-          for (int v = 0; v < 4; v++) {
-            const int col = n0 + c * 32 + v * 8;
-            if (col < p.N) {
-              uint32_t a0[8], out[8];
-#pragma unroll
-              for (int j = 0; j < 8; j++) a0[j] = r[v * 8 + j];
-              vm_run<8>(epi, row_lin + (uint64_t)col, a0, out);
-            }
-          }
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
-  }
-}
 
 // ---- f32 -> hi/lo TF32 split for the 3xTF32 scheme ------------------------------------------------------------------
 // out rows are K-major with 3K elements: sel 0 -> [hi | hi | lo], sel 1 -> [hi | lo | hi].
@@ -226,22 +21,6 @@ __global__ void __launch_bounds__(256) k_split_f32(const float* __restrict__ src
     o[K + k] = sel == 0 ? hi : lo;
     o[2 * K + k] = sel == 0 ? lo : hi;
   }
-}
-
-template <int BN, int STAGES, bool TF32>
-static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, const B2xVmProgram& epi, int32_t* status, cudaStream_t stream) {
-  using SM = TcSmem<BN, STAGES, TF32>;
-  auto kern = k_gemm_tc<BN, STAGES, TF32>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
-  int64_t grid = p.num_tiles < kNumSms ? p.num_tiles : kNumSms;
-  kern<<<(unsigned)grid, 192, SM::TOTAL, stream>>>(tmA, tmB, p, epi, status);
-  count_launch();
-  return (int)cudaGetLastError();
 }
 
 }  // namespace b2x
@@ -292,11 +71,16 @@ extern "C" int b2x_launch_gemm_tc(const B2xGemmArgs* a, const B2xVmProgram* epil
   p.k_blocks = (int)((a->K + BK - 1) / BK);
   p.idesc = sm100::make_idesc(tf32 ? 2u : (a->elem == EL_BF16 ? 1u : 0u), a_mn, b_mn, TC_BM, (uint32_t)BN);
   if (tf32) {
-    if (BN == 256) return launch_tc<256, 4, true>(tmA, tmB, p, *epilogue, status, stream);
-    if (BN == 128) return launch_tc<128, 6, true>(tmA, tmB, p, *epilogue, status, stream);
-    return launch_tc<64, 8, true>(tmA, tmB, p, *epilogue, status, stream);
+    if (BN == 256) return launch_tc<256, 4, true, 0>(tmA, tmB, p, *epilogue, status, stream);
+    if (BN == 128) return launch_tc<128, 6, true, 0>(tmA, tmB, p, *epilogue, status, stream);
+    return launch_tc<64, 8, true, 0>(tmA, tmB, p, *epilogue, status, stream);
   }
-  if (BN == 256) return launch_tc<256, 4, false>(tmA, tmB, p, *epilogue, status, stream);
-  if (BN == 128) return launch_tc<128, 6, false>(tmA, tmB, p, *epilogue, status, stream);
-  return launch_tc<64, 8, false>(tmA, tmB, p, *epilogue, status, stream);
+  const int id = vm_static_lookup(vm_signature_hash(*epilogue));
+  if (id) {
+    int rc = launch_tc_static(id, BN, tmA, tmB, p, *epilogue, status, stream);
+    if (rc >= 0) return rc;
+  }
+  if (BN == 256) return launch_tc<256, 4, false, 0>(tmA, tmB, p, *epilogue, status, stream);
+  if (BN == 128) return launch_tc<128, 6, false, 0>(tmA, tmB, p, *epilogue, status, stream);
+  return launch_tc<64, 8, false, 0>(tmA, tmB, p, *epilogue, status, stream);
 }

@@ -64,7 +64,7 @@ __device__ __forceinline__ void red_write(const ReduceKArgs& K, int64_t index, u
 }
 
 // Row reduction.  T = threads cooperating on one (row, split) piece: 32 or 256.
-template <int V, int T>
+template <int V, int T, int ID>
 __global__ void __launch_bounds__(256) k_reduce_rows(const __grid_constant__ B2xVmProgram P, const __grid_constant__ ReduceKArgs K) {
   __shared__ uint32_t smem[8];
   constexpr int PIECES_PER_CTA = 256 / T;
@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(256) k_reduce_rows(const __grid_constant__ B2x
       const int64_t r1 = min(K.R, r0 + K.chunk);
       for (int64_t r = r0 + (int64_t)lane_in_piece * V; r < r1; r += (int64_t)T * V) {
         uint32_t acc[V];
-        vm_run<V>(P, (uint64_t)(a * K.R + r), zero, acc);
+        vm_run<V, ID>(P, (uint64_t)(a * K.R + r), zero, acc);
 #pragma unroll
         for (int j = 0; j < V; j++) total = red_combine(total, acc[j], K.monoid, K.cls);
       }
@@ -159,10 +159,17 @@ static int launch_one(const B2xVmProgram& P, ReduceKArgs K, int vec, cudaStream_
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     dim3 grid((unsigned)blocks), block(256);
-#define B2X_ROWS(VV)                                                                      \
-    if (warp_rows) k_reduce_rows<VV, 32><<<grid, block, 0, stream>>>(P, K);               \
-    else k_reduce_rows<VV, 256><<<grid, block, 0, stream>>>(P, K);
-    if (vec == 8) { B2X_ROWS(8) } else if (vec == 4) { B2X_ROWS(4) } else { B2X_ROWS(1) }
+#define B2X_ROWS(VV, II)                                                                  \
+    if (warp_rows) k_reduce_rows<VV, 32, II><<<grid, block, 0, stream>>>(P, K);           \
+    else k_reduce_rows<VV, 256, II><<<grid, block, 0, stream>>>(P, K);
+    if (vec == 8) {
+      switch (vm_static_lookup(vm_signature_hash(P))) {
+#define X(I) case I: B2X_ROWS(8, I) break;
+        B2X_VM_STATIC_REDUCE(X)
+#undef X
+        default: B2X_ROWS(8, 0) break;
+      }
+    } else if (vec == 4) { B2X_ROWS(4, 0) } else { B2X_ROWS(1, 0) }
 #undef B2X_ROWS
   } else {
     int64_t bvecs = (K.B + vec - 1) / vec;

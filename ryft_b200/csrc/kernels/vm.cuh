@@ -97,13 +97,13 @@ __device__ __forceinline__ uint32_t vm_encode(uint32_t v, uint8_t elem) {
 
 // Fetch V elements of tensor T starting at element offset `off`, consecutive elements `istride` apart.
 template <int V>
-__device__ __forceinline__ void vm_fetch(const B2xVmTensor& T, int64_t off, int64_t istride, uint32_t (&b)[V]) {
-  const int es = vm_elem_size(T.elem);
-  const char* base = (const char*)T.ptr + off * es;
+__device__ __forceinline__ void vm_fetch(const void* ptr, const uint8_t elem, int64_t off, int64_t istride, uint32_t (&b)[V]) {
+  const int es = vm_elem_size(elem);
+  const char* base = (const char*)ptr + off * es;
   if (istride == 0 || V == 1) {
     uint32_t raw;
     if (es == 4) vm_ld_bytes<4>(base, &raw); else if (es == 2) vm_ld_bytes<2>(base, &raw); else vm_ld_bytes<1>(base, &raw);
-    raw = vm_decode(raw, T.elem);
+    raw = vm_decode(raw, elem);
 #pragma unroll
     for (int j = 0; j < V; j++) b[j] = raw;
     return;
@@ -122,7 +122,7 @@ __device__ __forceinline__ void vm_fetch(const B2xVmTensor& T, int64_t off, int6
         uint32_t raw[(V + 1) / 2];
         vm_ld_bytes<V * 2>(base, raw);
 #pragma unroll
-        for (int j = 0; j < V; j++) b[j] = vm_decode((raw[j / 2] >> ((j & 1) * 16)) & 0xffffu, T.elem);
+        for (int j = 0; j < V; j++) b[j] = vm_decode((raw[j / 2] >> ((j & 1) * 16)) & 0xffffu, elem);
         return;
       }
     } else if (es == 1) {
@@ -130,7 +130,7 @@ __device__ __forceinline__ void vm_fetch(const B2xVmTensor& T, int64_t off, int6
         uint32_t raw[(V + 3) / 4];
         vm_ld_bytes<V>(base, raw);
 #pragma unroll
-        for (int j = 0; j < V; j++) b[j] = vm_decode((raw[j / 4] >> ((j & 3) * 8)) & 0xffu, T.elem);
+        for (int j = 0; j < V; j++) b[j] = vm_decode((raw[j / 4] >> ((j & 3) * 8)) & 0xffu, elem);
         return;
       }
     }
@@ -140,19 +140,19 @@ __device__ __forceinline__ void vm_fetch(const B2xVmTensor& T, int64_t off, int6
     uint32_t raw;
     const char* p = base + (int64_t)j * istride * es;
     if (es == 4) vm_ld_bytes<4>(p, &raw); else if (es == 2) vm_ld_bytes<2>(p, &raw); else vm_ld_bytes<1>(p, &raw);
-    b[j] = vm_decode(raw, T.elem);
+    b[j] = vm_decode(raw, elem);
   }
 }
 
 template <int V>
-__device__ __forceinline__ void vm_put(const B2xVmTensor& T, int64_t off, int64_t istride, const uint32_t (&a)[V]) {
-  const int es = vm_elem_size(T.elem);
-  char* base = (char*)T.ptr + off * es;
+__device__ __forceinline__ void vm_put(void* ptr, const uint8_t elem, int64_t off, int64_t istride, const uint32_t (&a)[V]) {
+  const int es = vm_elem_size(elem);
+  char* base = (char*)ptr + off * es;
   if (istride == 1 && V > 1) {
     if (es == 4 && ((uintptr_t)base & (V * 4 >= 16 ? 15 : V * 4 - 1)) == 0) {
       uint32_t raw[V];
 #pragma unroll
-      for (int j = 0; j < V; j++) raw[j] = vm_encode(a[j], T.elem);
+      for (int j = 0; j < V; j++) raw[j] = vm_encode(a[j], elem);
       vm_st_bytes<V * 4>(base, raw);
       return;
     }
@@ -161,7 +161,7 @@ __device__ __forceinline__ void vm_put(const B2xVmTensor& T, int64_t off, int64_
 #pragma unroll
       for (int j = 0; j < (V + 1) / 2; j++) raw[j] = 0;
 #pragma unroll
-      for (int j = 0; j < V; j++) raw[j / 2] |= vm_encode(a[j], T.elem) << ((j & 1) * 16);
+      for (int j = 0; j < V; j++) raw[j / 2] |= vm_encode(a[j], elem) << ((j & 1) * 16);
       vm_st_bytes<V * 2>(base, raw);
       return;
     }
@@ -170,14 +170,14 @@ __device__ __forceinline__ void vm_put(const B2xVmTensor& T, int64_t off, int64_
 #pragma unroll
       for (int j = 0; j < (V + 3) / 4; j++) raw[j] = 0;
 #pragma unroll
-      for (int j = 0; j < V; j++) raw[j / 4] |= vm_encode(a[j], T.elem) << ((j & 3) * 8);
+      for (int j = 0; j < V; j++) raw[j / 4] |= vm_encode(a[j], elem) << ((j & 3) * 8);
       vm_st_bytes<V>(base, raw);
       return;
     }
   }
 #pragma unroll
   for (int j = 0; j < V; j++) {
-    uint32_t raw = vm_encode(a[j], T.elem);
+    uint32_t raw = vm_encode(a[j], elem);
     char* p = base + (int64_t)j * istride * es;
     if (es == 4) vm_st_bytes<4>(p, &raw); else if (es == 2) vm_st_bytes<2>(p, &raw); else vm_st_bytes<1>(p, &raw);
   }
@@ -213,34 +213,78 @@ __device__ __forceinline__ bool vm_cmp(T x, T y, uint8_t dir) {
   }
 }
 
+// ---- out-of-line helpers for rarely used ops: keeps the interpreter's hot code small enough for the instruction cache
+static __device__ __noinline__ float vm_rare_f32(uint8_t op, float x, float y) {
+  switch (op) {
+    case VM_POW: return powf(x, y);
+    case VM_REM: return fmodf(x, y);
+    case VM_EXPM1: return expm1f(x);
+    case VM_LOG1P: return log1pf(x);
+    case VM_SIN: return sinf(x);
+    case VM_COS: return cosf(x);
+    case VM_SIGN: return (x != x) ? x : (x > 0.f ? 1.f : (x < 0.f ? -1.f : x));
+    case VM_FLOOR: return floorf(x);
+    case VM_CEIL: return ceilf(x);
+    case VM_LOG: return logf(x);
+    case VM_LOGISTIC: return __fdiv_rn(1.0f, 1.0f + expf(-x));
+    case VM_RSQRT: return __fdiv_rn(1.0f, sqrtf(x));
+    default: return x;
+  }
+}
+static __device__ __noinline__ uint32_t vm_rare_int(uint8_t op, uint8_t tc, uint32_t x, uint32_t y) {
+  const bool s = tc == VM_S32;
+  switch (op) {
+    case VM_DIV: return s ? (uint32_t)vm_sdiv((int)x, (int)y) : vm_udiv(x, y);
+    case VM_REM: return s ? (uint32_t)vm_srem((int)x, (int)y) : vm_urem(x, y);
+    case VM_POW: return (uint32_t)vm_ipow((int)x, (int)y);
+    case VM_SIGN: return s ? (uint32_t)(((int)x > 0) - ((int)x < 0)) : (x != 0u);
+    default: return x;
+  }
+}
+
+// Register state of one program run: accumulator, operand, temporaries.  Always indexed with compile-time constants
+// after inlining, so it lives in registers.
+template <int V>
+struct VmState {
+  uint32_t acc[V], b[V], t0[V], t1[V], t2[V], t3[V], t4[V], t5[V];
+};
+
 #define B2X_VM_TEMP_SWITCH(idx, T, stmt)                 \
   switch (idx) {                                          \
-    case 0: { auto& T = t0; stmt; } break;                \
-    case 1: { auto& T = t1; stmt; } break;                \
-    case 2: { auto& T = t2; stmt; } break;                \
-    case 3: { auto& T = t3; stmt; } break;                \
-    case 4: { auto& T = t4; stmt; } break;                \
-    default: { auto& T = t5; stmt; } break;               \
+    case 0: { auto& T = S.t0; stmt; } break;              \
+    case 1: { auto& T = S.t1; stmt; } break;              \
+    case 2: { auto& T = S.t2; stmt; } break;              \
+    case 3: { auto& T = S.t3; stmt; } break;              \
+    case 4: { auto& T = S.t4; stmt; } break;              \
+    default: { auto& T = S.t5; stmt; } break;             \
   }
 
-#define B2X_VM_BIN(EF, ES, EU)                                                                              \
-  {                                                                                                         \
-    if (I.tc == VM_F32) {                                                                                   \
-      _Pragma("unroll") for (int j = 0; j < V; j++) { float x = u2f(X[j]), y = u2f(Y[j]); acc[j] = f2u(EF); } \
-    } else if (I.tc == VM_S32) {                                                                            \
-      _Pragma("unroll") for (int j = 0; j < V; j++) { int x = (int)X[j], y = (int)Y[j]; acc[j] = (uint32_t)(ES); } \
-    } else {                                                                                                \
-      _Pragma("unroll") for (int j = 0; j < V; j++) { uint32_t x = X[j], y = Y[j]; acc[j] = (uint32_t)(EU); } \
-    }                                                                                                       \
+#define B2X_VM_BIN(EF, ES, EU)                                                                                \
+  {                                                                                                           \
+    if (tc == VM_F32) {                                                                                       \
+      _Pragma("unroll") for (int j = 0; j < V; j++) { float x = u2f(X[j]), y = u2f(Y[j]); S.acc[j] = f2u(EF); } \
+    } else if (tc == VM_S32) {                                                                                \
+      _Pragma("unroll") for (int j = 0; j < V; j++) { int x = (int)X[j], y = (int)Y[j]; S.acc[j] = (uint32_t)(ES); } \
+    } else {                                                                                                  \
+      _Pragma("unroll") for (int j = 0; j < V; j++) { uint32_t x = X[j], y = Y[j]; S.acc[j] = (uint32_t)(EU); } \
+    }                                                                                                         \
   }
-
-#define B2X_VM_UN(EF, ES)                                                                     \
-  {                                                                                           \
-    if (I.tc == VM_F32) {                                                                     \
-      _Pragma("unroll") for (int j = 0; j < V; j++) { float x = u2f(acc[j]); acc[j] = f2u(EF); } \
-    } else {                                                                                  \
-      _Pragma("unroll") for (int j = 0; j < V; j++) { int x = (int)acc[j]; acc[j] = (uint32_t)(ES); } \
-    }                                                                                         \
+#define B2X_VM_BIN_RARE(OPC)                                                                                  \
+  {                                                                                                           \
+    if (tc == VM_F32) {                                                                                       \
+      _Pragma("unroll") for (int j = 0; j < V; j++) S.acc[j] = f2u(vm_rare_f32(OPC, u2f(X[j]), u2f(Y[j])));    \
+    } else {                                                                                                  \
+      _Pragma("unroll") for (int j = 0; j < V; j++) S.acc[j] = vm_rare_int(OPC, tc, X[j], Y[j]);               \
+    }                                                                                                         \
+  }
+#define B2X_VM_UN_F(EF) { _Pragma("unroll") for (int j = 0; j < V; j++) { float x = u2f(S.acc[j]); S.acc[j] = f2u(EF); } }
+#define B2X_VM_UN_RARE(OPC)                                                                                   \
+  {                                                                                                           \
+    if (tc == VM_F32) {                                                                                       \
+      _Pragma("unroll") for (int j = 0; j < V; j++) S.acc[j] = f2u(vm_rare_f32(OPC, u2f(S.acc[j]), 0.f));      \
+    } else {                                                                                                  \
+      _Pragma("unroll") for (int j = 0; j < V; j++) S.acc[j] = vm_rare_int(OPC, tc, S.acc[j], 0u);             \
+    }                                                                                                         \
   }
 
 // Decomposes the linear index of a vector's first element into coordinates of the merged root dims.
@@ -265,148 +309,207 @@ __device__ __forceinline__ void vm_coords(const B2xVmProgram& P, uint64_t lin, i
   }
 }
 
+__device__ __forceinline__ int64_t vm_offset(const B2xVmTensor& T, const int64_t (&coord)[B2X_VM_MAX_DIMS], int nd) {
+  int64_t off = 0;
+#pragma unroll
+  for (int d = 0; d < B2X_VM_MAX_DIMS; d++) if (d < nd) off += coord[d] * T.stride[d];
+  return off;
+}
+
+// One instruction.  Every argument except the state is uniform across the grid; when the caller passes compile-time
+// constants (specialised programs) the switches below fold away and only the selected op's code remains.
+template <int V>
+__device__ __forceinline__ void vm_exec(const B2xVmProgram& P, const int64_t (&coord)[B2X_VM_MAX_DIMS], const int nd, const uint8_t op,
+                                        const uint8_t src_kind, const uint8_t src_idx, const uint8_t aux, const uint8_t tc, const uint8_t rnd,
+                                        const uint32_t imm, const uint8_t elem, const uint32_t (&acc0)[V], VmState<V>& S) {
+  // ---- operand fetch ----
+  switch (src_kind) {
+    case VM_SRC_TEMP:
+      B2X_VM_TEMP_SWITCH(src_idx, T, _Pragma("unroll") for (int j = 0; j < V; j++) S.b[j] = T[j]);
+      break;
+    case VM_SRC_TENSOR:
+      if (op != VM_STORE) {
+        const B2xVmTensor& T = P.tensors[src_idx];
+        vm_fetch<V>(T.ptr, elem, vm_offset(T, coord, nd), T.stride[nd - 1], S.b);
+      }
+      break;
+    case VM_SRC_IMM:
+#pragma unroll
+      for (int j = 0; j < V; j++) S.b[j] = imm;
+      break;
+    case VM_SRC_IOTA: {
+      const bool inner = (src_idx == nd - 1);
+      int32_t c0 = 0;
+#pragma unroll
+      for (int d = 0; d < B2X_VM_MAX_DIMS; d++) if (d == src_idx) c0 = (int32_t)coord[d];
+#pragma unroll
+      for (int j = 0; j < V; j++) {
+        int32_t c = c0 + (inner ? j : 0);
+        S.b[j] = (tc == VM_F32) ? f2u((float)c) : (uint32_t)c;
+      }
+      break;
+    }
+    case VM_SRC_ACC0:
+#pragma unroll
+      for (int j = 0; j < V; j++) S.b[j] = acc0[j];
+      break;
+    default: break;
+  }
+  // ---- execute ----
+  bool narrow = true;
+  switch (op) {
+    case VM_LOAD:
+#pragma unroll
+      for (int j = 0; j < V; j++) S.acc[j] = S.b[j];
+      break;
+    case VM_SAVE:
+      B2X_VM_TEMP_SWITCH(aux, T, _Pragma("unroll") for (int j = 0; j < V; j++) T[j] = S.acc[j]);
+      narrow = false;
+      break;
+    case VM_STORE: {
+      const B2xVmTensor& T = P.tensors[src_idx];
+      vm_put<V>(T.ptr, elem, vm_offset(T, coord, nd), T.stride[nd - 1], S.acc);
+      narrow = false;
+      break;
+    }
+#define X S.acc
+#define Y S.b
+    case VM_ADD: B2X_VM_BIN(x + y, x + y, x + y) break;
+    case VM_SUB: B2X_VM_BIN(x - y, x - y, x - y) break;
+    case VM_MUL: B2X_VM_BIN(x * y, x * y, x * y) break;
+    case VM_DIV: if (tc == VM_F32) B2X_VM_BIN(__fdiv_rn(x, y), 0, 0) else B2X_VM_BIN_RARE(VM_DIV) break;
+    case VM_MAX: B2X_VM_BIN(vm_fmax(x, y), max(x, y), max(x, y)) break;
+    case VM_MIN: B2X_VM_BIN(vm_fmin(x, y), min(x, y), min(x, y)) break;
+    case VM_POW: B2X_VM_BIN_RARE(VM_POW) break;
+    case VM_REM: B2X_VM_BIN_RARE(VM_REM) break;
+    case VM_AND: B2X_VM_BIN(u2f(f2u(x) & f2u(y)), x & y, x & y) break;
+    case VM_OR: B2X_VM_BIN(u2f(f2u(x) | f2u(y)), x | y, x | y) break;
+    case VM_XOR: B2X_VM_BIN(u2f(f2u(x) ^ f2u(y)), x ^ y, x ^ y) break;
+    case VM_CMP: B2X_VM_BIN(u2f(vm_cmp<float>(x, y, aux) ? 1u : 0u), vm_cmp<int>(x, y, aux) ? 1 : 0, vm_cmp<uint32_t>(x, y, aux) ? 1u : 0u) break;
+#undef X
+#undef Y
+#define X S.b
+#define Y S.acc
+    case VM_RSUB: B2X_VM_BIN(x - y, x - y, x - y) break;
+    case VM_RDIV: if (tc == VM_F32) B2X_VM_BIN(__fdiv_rn(x, y), 0, 0) else B2X_VM_BIN_RARE(VM_DIV) break;
+    case VM_RPOW: B2X_VM_BIN_RARE(VM_POW) break;
+    case VM_RREM: B2X_VM_BIN_RARE(VM_REM) break;
+    case VM_RCMP: B2X_VM_BIN(u2f(vm_cmp<float>(x, y, aux) ? 1u : 0u), vm_cmp<int>(x, y, aux) ? 1 : 0, vm_cmp<uint32_t>(x, y, aux) ? 1u : 0u) break;
+#undef X
+#undef Y
+    case VM_NEG:
+      if (tc == VM_F32) B2X_VM_UN_F(-x) else { _Pragma("unroll") for (int j = 0; j < V; j++) S.acc[j] = 0u - S.acc[j]; }
+      break;
+    case VM_ABS:
+      if (tc == VM_F32) B2X_VM_UN_F(fabsf(x))
+      else if (tc == VM_S32) { _Pragma("unroll") for (int j = 0; j < V; j++) { int x = (int)S.acc[j]; S.acc[j] = (uint32_t)(x < 0 ? -x : x); } }
+      break;
+    case VM_TANH: if (aux) B2X_VM_UN_F(vm_tanh_fast(x)) else B2X_VM_UN_F(tanhf(x)) break;
+    case VM_EXP: if (aux) B2X_VM_UN_F(__expf(x)) else B2X_VM_UN_F(expf(x)) break;
+    case VM_SQRT: B2X_VM_UN_F(sqrtf(x)) break;
+    case VM_LOG: if (aux) B2X_VM_UN_F(__logf(x)) else B2X_VM_UN_RARE(VM_LOG) break;
+    case VM_LOGISTIC: if (aux) B2X_VM_UN_F(__fdividef(1.0f, 1.0f + __expf(-x))) else B2X_VM_UN_RARE(VM_LOGISTIC) break;
+    case VM_RSQRT: B2X_VM_UN_RARE(VM_RSQRT) break;
+    case VM_SIGN: B2X_VM_UN_RARE(VM_SIGN) break;
+    case VM_FLOOR: B2X_VM_UN_RARE(VM_FLOOR) break;
+    case VM_CEIL: B2X_VM_UN_RARE(VM_CEIL) break;
+    case VM_EXPM1: B2X_VM_UN_RARE(VM_EXPM1) break;
+    case VM_LOG1P: B2X_VM_UN_RARE(VM_LOG1P) break;
+    case VM_SIN: B2X_VM_UN_RARE(VM_SIN) break;
+    case VM_COS: B2X_VM_UN_RARE(VM_COS) break;
+    case VM_NOT:
+#pragma unroll
+      for (int j = 0; j < V; j++) S.acc[j] = (rnd == VM_RN_PRED) ? (S.acc[j] == 0u ? 1u : 0u) : ~S.acc[j];
+      break;
+    case VM_CVT: {
+      const uint8_t from = aux, to = tc;
+#pragma unroll
+      for (int j = 0; j < V; j++) {
+        uint32_t v = S.acc[j];
+        if (rnd == VM_RN_PRED) { v = (from == VM_F32) ? (u2f(v) != 0.0f ? 1u : 0u) : (v != 0u ? 1u : 0u); }
+        else if (from == VM_F32 && to == VM_S32) v = (uint32_t)__float2int_rz(u2f(v));
+        else if (from == VM_F32 && to == VM_U32) v = __float2uint_rz(u2f(v));
+        else if (from == VM_S32 && to == VM_F32) v = f2u(__int2float_rn((int)v));
+        else if (from == VM_U32 && to == VM_F32) v = f2u(__uint2float_rn(v));
+        S.acc[j] = v;
+      }
+      break;
+    }
+    case VM_SELECT:
+      B2X_VM_TEMP_SWITCH(aux, T, _Pragma("unroll") for (int j = 0; j < V; j++) S.acc[j] = T[j] ? S.acc[j] : S.b[j]);
+      narrow = false;
+      break;
+    case VM_RSELECT:
+      B2X_VM_TEMP_SWITCH(aux, T, _Pragma("unroll") for (int j = 0; j < V; j++) S.acc[j] = T[j] ? S.b[j] : S.acc[j]);
+      narrow = false;
+      break;
+    default: break;
+  }
+  if (narrow && rnd != VM_RN_NONE && !(op == VM_CVT && rnd == VM_RN_PRED)) {
+#pragma unroll
+    for (int j = 0; j < V; j++) S.acc[j] = vm_narrow(S.acc[j], rnd);
+  }
+}
+
+// ---- specialised programs ---------------------------------------------------------------------------------------------
+// VmStatic<ID> describes a program whose structure is known when the library is built (generated table below); ID 0
+// is the interpreter.  A specialised run unrolls the program at compile time, so each instruction's opcode, operand
+// kind, register class, rounding and tensor element types are constants and the op switches disappear; immediates,
+// pointers, strides and dims still come from the B2xVmProgram passed at launch.
+struct VmSig { uint8_t op, src_kind, src_idx, aux, tc, rnd; };
+template <int ID> struct VmStatic { static constexpr int n = 0; };
+
+}  // namespace b2x
+#include "vm_static_table.h"
+namespace b2x {
+
+template <int V, int ID, int PC>
+__device__ __forceinline__ void vm_unroll(const B2xVmProgram& P, const int64_t (&coord)[B2X_VM_MAX_DIMS], const int nd, const uint32_t (&acc0)[V],
+                                          VmState<V>& S) {
+  if constexpr (PC < VmStatic<ID>::n) {
+    constexpr VmSig G = VmStatic<ID>::at(PC);
+    constexpr uint8_t elem = (G.src_kind == VM_SRC_TENSOR) ? VmStatic<ID>::elem(G.src_idx) : (uint8_t)0;
+    vm_exec<V>(P, coord, nd, G.op, G.src_kind, G.src_idx, G.aux, G.tc, G.rnd, P.code[PC].imm, elem, acc0, S);
+    vm_unroll<V, ID, PC + 1>(P, coord, nd, acc0, S);
+  }
+}
+
 // Runs the program for the V elements whose first element has linear index `lin` in the root shape.
 // `acc0` feeds VM_SRC_ACC0 operands.  On return `acc` holds the final accumulator (used by reductions).
-template <int V>
+template <int V, int ID = 0>
 __device__ __forceinline__ void vm_run(const B2xVmProgram& P, uint64_t lin, const uint32_t (&acc0)[V], uint32_t (&acc)[V]) {
   int64_t coord[B2X_VM_MAX_DIMS];
   vm_coords(P, lin, coord);
   const int nd = P.n_dims;
-  uint32_t t0[V], t1[V], t2[V], t3[V], t4[V], t5[V];
-  uint32_t b[V];
+  VmState<V> S;
 #pragma unroll
-  for (int j = 0; j < V; j++) { acc[j] = 0; b[j] = 0; t0[j] = t1[j] = t2[j] = t3[j] = t4[j] = t5[j] = 0; }
-
+  for (int j = 0; j < V; j++) { S.acc[j] = 0; S.b[j] = 0; S.t0[j] = S.t1[j] = S.t2[j] = S.t3[j] = S.t4[j] = S.t5[j] = 0; }
+  if constexpr (ID == 0) {
 #pragma unroll 1
-  for (int pc = 0; pc < P.n_instr; pc++) {
-    const B2xVmInstr I = P.code[pc];
-    // ---- operand fetch ----
-    switch (I.src_kind) {
-      case VM_SRC_TEMP:
-        B2X_VM_TEMP_SWITCH(I.src_idx, T, _Pragma("unroll") for (int j = 0; j < V; j++) b[j] = T[j]);
-        break;
-      case VM_SRC_TENSOR:
-        if (I.op != VM_STORE) {
-          const B2xVmTensor& T = P.tensors[I.src_idx];
-          int64_t off = 0;
-#pragma unroll
-          for (int d = 0; d < B2X_VM_MAX_DIMS; d++) if (d < nd) off += coord[d] * T.stride[d];
-          vm_fetch<V>(T, off, T.stride[nd - 1], b);
-        }
-        break;
-      case VM_SRC_IMM:
-#pragma unroll
-        for (int j = 0; j < V; j++) b[j] = I.imm;
-        break;
-      case VM_SRC_IOTA: {
-        const bool inner = (I.src_idx == nd - 1);
-        int32_t c0 = 0;
-#pragma unroll
-        for (int d = 0; d < B2X_VM_MAX_DIMS; d++) if (d == I.src_idx) c0 = (int32_t)coord[d];
-#pragma unroll
-        for (int j = 0; j < V; j++) {
-          int32_t c = c0 + (inner ? j : 0);
-          b[j] = (I.tc == VM_F32) ? f2u((float)c) : (uint32_t)c;
-        }
-        break;
-      }
-      case VM_SRC_ACC0:
-#pragma unroll
-        for (int j = 0; j < V; j++) b[j] = acc0[j];
-        break;
-      default: break;
+    for (int pc = 0; pc < P.n_instr; pc++) {
+      const B2xVmInstr I = P.code[pc];
+      const uint8_t elem = (I.src_kind == VM_SRC_TENSOR) ? P.tensors[I.src_idx].elem : (uint8_t)0;
+      vm_exec<V>(P, coord, nd, I.op, I.src_kind, I.src_idx, I.aux, I.tc, I.rnd, I.imm, elem, acc0, S);
     }
-    // ---- execute ----
-    switch (I.op) {
-      case VM_LOAD:
-#pragma unroll
-        for (int j = 0; j < V; j++) acc[j] = b[j];
-        break;
-      case VM_SAVE:
-        B2X_VM_TEMP_SWITCH(I.aux, T, _Pragma("unroll") for (int j = 0; j < V; j++) T[j] = acc[j]);
-        continue;
-      case VM_STORE: {
-        const B2xVmTensor& T = P.tensors[I.src_idx];
-        int64_t off = 0;
-#pragma unroll
-        for (int d = 0; d < B2X_VM_MAX_DIMS; d++) if (d < nd) off += coord[d] * T.stride[d];
-        vm_put<V>(T, off, T.stride[nd - 1], acc);
-        continue;
-      }
-#define X acc
-#define Y b
-      case VM_ADD: B2X_VM_BIN(x + y, x + y, x + y) break;
-      case VM_SUB: B2X_VM_BIN(x - y, x - y, x - y) break;
-      case VM_MUL: B2X_VM_BIN(x * y, x * y, x * y) break;
-      case VM_DIV: B2X_VM_BIN(__fdiv_rn(x, y), vm_sdiv(x, y), vm_udiv(x, y)) break;
-      case VM_MAX: B2X_VM_BIN(vm_fmax(x, y), max(x, y), max(x, y)) break;
-      case VM_MIN: B2X_VM_BIN(vm_fmin(x, y), min(x, y), min(x, y)) break;
-      case VM_POW: B2X_VM_BIN(powf(x, y), vm_ipow(x, y), (uint32_t)vm_ipow((int)x, (int)y)) break;
-      case VM_REM: B2X_VM_BIN(fmodf(x, y), vm_srem(x, y), vm_urem(x, y)) break;
-      case VM_AND: B2X_VM_BIN(u2f(f2u(x) & f2u(y)), x & y, x & y) break;
-      case VM_OR: B2X_VM_BIN(u2f(f2u(x) | f2u(y)), x | y, x | y) break;
-      case VM_XOR: B2X_VM_BIN(u2f(f2u(x) ^ f2u(y)), x ^ y, x ^ y) break;
-      case VM_CMP: B2X_VM_BIN(u2f(vm_cmp<float>(x, y, I.aux) ? 1u : 0u), vm_cmp<int>(x, y, I.aux) ? 1 : 0, vm_cmp<uint32_t>(x, y, I.aux) ? 1u : 0u) break;
-#undef X
-#undef Y
-#define X b
-#define Y acc
-      case VM_RSUB: B2X_VM_BIN(x - y, x - y, x - y) break;
-      case VM_RDIV: B2X_VM_BIN(__fdiv_rn(x, y), vm_sdiv(x, y), vm_udiv(x, y)) break;
-      case VM_RPOW: B2X_VM_BIN(powf(x, y), vm_ipow(x, y), (uint32_t)vm_ipow((int)x, (int)y)) break;
-      case VM_RREM: B2X_VM_BIN(fmodf(x, y), vm_srem(x, y), vm_urem(x, y)) break;
-      case VM_RCMP: B2X_VM_BIN(u2f(vm_cmp<float>(x, y, I.aux) ? 1u : 0u), vm_cmp<int>(x, y, I.aux) ? 1 : 0, vm_cmp<uint32_t>(x, y, I.aux) ? 1u : 0u) break;
-#undef X
-#undef Y
-      case VM_NEG: B2X_VM_UN(-x, -x) break;
-      case VM_ABS: B2X_VM_UN(fabsf(x), (I.tc == VM_S32 ? (x < 0 ? -x : x) : x)) break;
-      case VM_TANH: if (I.aux) B2X_VM_UN(vm_tanh_fast(x), x) else B2X_VM_UN(tanhf(x), x) break;
-      case VM_EXP: if (I.aux) B2X_VM_UN(__expf(x), x) else B2X_VM_UN(expf(x), x) break;
-      case VM_LOG: if (I.aux) B2X_VM_UN(__logf(x), x) else B2X_VM_UN(logf(x), x) break;
-      case VM_SQRT: B2X_VM_UN(sqrtf(x), x) break;
-      case VM_RSQRT: B2X_VM_UN(__fdiv_rn(1.0f, sqrtf(x)), x) break;
-      case VM_LOGISTIC: if (I.aux) B2X_VM_UN(__fdividef(1.0f, 1.0f + __expf(-x)), x) else B2X_VM_UN(__fdiv_rn(1.0f, 1.0f + expf(-x)), x) break;
-      case VM_NOT:
-#pragma unroll
-        for (int j = 0; j < V; j++) acc[j] = (I.rnd == VM_RN_PRED) ? (acc[j] == 0u ? 1u : 0u) : ~acc[j];
-        break;
-      case VM_SIGN: B2X_VM_UN((x != x) ? x : (x > 0.f ? 1.f : (x < 0.f ? -1.f : x)), (x > 0) - (x < 0)) break;
-      case VM_FLOOR: B2X_VM_UN(floorf(x), x) break;
-      case VM_CEIL: B2X_VM_UN(ceilf(x), x) break;
-      case VM_EXPM1: B2X_VM_UN(expm1f(x), x) break;
-      case VM_LOG1P: B2X_VM_UN(log1pf(x), x) break;
-      case VM_SIN: B2X_VM_UN(sinf(x), x) break;
-      case VM_COS: B2X_VM_UN(cosf(x), x) break;
-      case VM_CVT: {
-        const uint8_t from = I.aux, to = I.tc;
-#pragma unroll
-        for (int j = 0; j < V; j++) {
-          uint32_t v = acc[j];
-          if (I.rnd == VM_RN_PRED) { v = (from == VM_F32) ? (u2f(v) != 0.0f ? 1u : 0u) : (v != 0u ? 1u : 0u); }
-          else if (from == VM_F32 && to == VM_S32) v = (uint32_t)__float2int_rz(u2f(v));
-          else if (from == VM_F32 && to == VM_U32) v = __float2uint_rz(u2f(v));
-          else if (from == VM_S32 && to == VM_F32) v = f2u(__int2float_rn((int)v));
-          else if (from == VM_U32 && to == VM_F32) v = f2u(__uint2float_rn(v));
-          acc[j] = v;
-        }
-        break;
-      }
-      case VM_SELECT:
-        B2X_VM_TEMP_SWITCH(I.aux, T, _Pragma("unroll") for (int j = 0; j < V; j++) acc[j] = T[j] ? acc[j] : b[j]);
-        break;
-      case VM_RSELECT:
-        B2X_VM_TEMP_SWITCH(I.aux, T, _Pragma("unroll") for (int j = 0; j < V; j++) acc[j] = T[j] ? b[j] : acc[j]);
-        break;
-      default: break;
-    }
-    if (I.rnd != VM_RN_NONE && I.op != VM_CVT) {
-#pragma unroll
-      for (int j = 0; j < V; j++) acc[j] = vm_narrow(acc[j], I.rnd);
-    } else if (I.op == VM_CVT && I.rnd != VM_RN_PRED && I.rnd != VM_RN_NONE) {
-#pragma unroll
-      for (int j = 0; j < V; j++) acc[j] = vm_narrow(acc[j], I.rnd);
-    }
+  } else {
+    vm_unroll<V, ID, 0>(P, coord, nd, acc0, S);
   }
+#pragma unroll
+  for (int j = 0; j < V; j++) acc[j] = S.acc[j];
+}
+
+// Signature hash of a program (structure only: ops, operand kinds, classes, rounding, tensor element types).
+__host__ inline uint64_t vm_signature_hash(const B2xVmProgram& P) {
+  uint64_t h = 1469598103934665603ull;
+  auto mix = [&](uint8_t b) { h ^= b; h *= 1099511628211ull; };
+  mix((uint8_t)P.n_instr);
+  for (int i = 0; i < P.n_instr; i++) {
+    const B2xVmInstr& I = P.code[i];
+    mix(I.op); mix(I.src_kind); mix(I.src_idx); mix(I.aux); mix(I.tc); mix(I.rnd);
+  }
+  mix((uint8_t)P.n_tensors);
+  for (int t = 0; t < P.n_tensors; t++) mix(P.tensors[t].elem);
+  return h;
 }
 
 }  // namespace b2x

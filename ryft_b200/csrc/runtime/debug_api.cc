@@ -47,3 +47,52 @@ extern "C" __attribute__((visibility("default"))) int b2x_debug_parse_compile_op
   out[4] = (int64_t)n;
   return 0;
 }
+
+// Lists the fused-elementwise programs of a module's launch plan, one per line:
+//   role|BN|vec|hash|n_instr|op.src_kind.src_idx.aux.tc.rnd,...|elem,elem,...|label
+// role is elementwise, reduce or gemm_tc.  Input of gen_vm_static.py, which builds the table of specialised programs.
+extern "C" __attribute__((visibility("default"))) int b2x_plan_signatures(const char* mlir, size_t mlir_size, int num_replicas, char* out, size_t out_cap,
+                                                                           size_t* out_size) {
+  std::string text;
+  int code = 0;
+  try {
+    auto m = b2x::parse_module(std::string(mlir, mlir_size));
+    b2x::PlanOptions o;
+    o.num_replicas = num_replicas > 0 ? num_replicas : 1;
+    b2x::Plan plan = b2x::build_plan(*m, o, 0);
+    for (auto& s : plan.steps) {
+      const char* role = nullptr;
+      int bn = 0;
+      if (s.kind == b2x::StepKind::ELEMENTWISE) role = "elementwise";
+      else if (s.kind == b2x::StepKind::REDUCE) role = "reduce";
+      else if (s.kind == b2x::StepKind::GEMM && s.g_tensor_core && !s.g_split_f32) { role = "gemm_tc"; bn = s.gN >= 256 ? 256 : (s.gN >= 128 ? 128 : 64); }
+      if (!role) continue;
+      const B2xVmProgram& P = s.vm.prog;
+      uint64_t h = 1469598103934665603ull;
+      auto mix = [&](uint8_t b) { h ^= b; h *= 1099511628211ull; };
+      mix((uint8_t)P.n_instr);
+      std::string code_s, elems;
+      for (int i = 0; i < P.n_instr; i++) {
+        const B2xVmInstr& I = P.code[i];
+        mix(I.op); mix(I.src_kind); mix(I.src_idx); mix(I.aux); mix(I.tc); mix(I.rnd);
+        if (i) code_s += ",";
+        code_s += std::to_string(I.op) + "." + std::to_string(I.src_kind) + "." + std::to_string(I.src_idx) + "." + std::to_string(I.aux) + "." +
+                  std::to_string(I.tc) + "." + std::to_string(I.rnd);
+      }
+      mix((uint8_t)P.n_tensors);
+      for (int t = 0; t < P.n_tensors; t++) { mix(P.tensors[t].elem); if (t) elems += ","; elems += std::to_string(P.tensors[t].elem); }
+      text += std::string(role) + "|" + std::to_string(bn) + "|" + std::to_string(s.vm.vec) + "|" + std::to_string(h) + "|" + std::to_string(P.n_instr) + "|" + code_s +
+              "|" + elems + "|" + s.label + "\n";
+    }
+  } catch (const b2x::CompileError& e) {
+    code = e.code;
+    text = e.what();
+  }
+  if (out_size) *out_size = text.size();
+  if (out && out_cap) {
+    size_t n = text.size() < out_cap - 1 ? text.size() : out_cap - 1;
+    memcpy(out, text.data(), n);
+    out[n] = 0;
+  }
+  return code;
+}
