@@ -227,6 +227,10 @@ class Planner {
   }
 
   void classify();
+  struct AttnMatch { const Value* q; const Value* k; const Value* v; float scale; bool causal; };
+  std::map<const Op*, AttnMatch> attn_;
+  void match_attention();
+  void emit_attention(const Op& op, const AttnMatch& m);
   void emit_group_for_root(const Value* v);
   void emit_reduce(const Op& op);
   void emit_dot(const Op& op);
@@ -540,6 +544,144 @@ VmBinding Planner::GroupBuilder::finish(int final_node) {
   int64_t inner = mdims.back();
   vb.vec = (inner % 8 == 0) ? 8 : (inner % 4 == 0 ? 4 : 1);
   return vb;
+}
+
+// ---- fused attention pattern ------------------------------------------------------------------------------------------
+// Recognises, ending at the second dot_general:
+//   S = dot_general(Q, K) over the last dim, leading dims batched;  [S = S * splat(c)];
+//   [S = select(broadcast(compare GE (iota rows, iota cols)), S, splat(-inf))];
+//   M = reduce max over the last dim; E = exp(S - broadcast(M)); L = reduce add(E); P = E / broadcast(L); [convert];
+//   O = dot_general(P, V) contracting P's last dim with V's key dim.
+// Every intermediate must have no user outside the pattern.
+void Planner::match_attention() {
+  if (!opt_.allow_fused_attention) return;
+  auto users_are = [&](const Value* v, std::initializer_list<const Op*> ops) {
+    for (auto o : m_.outputs) if (o == v) return false;
+    for (auto u : v->users) { bool in = false; for (auto o : ops) if (u == o) in = true; if (!in) return false; }
+    return !v->users.empty();
+  };
+  auto op_of = [&](const Value* v, OpKind k) -> const Op* { return (v->def && v->def->kind == k) ? v->def : nullptr; };
+  std::function<bool(const Value*, float*)> splat_f32 = [&](const Value* v, float* out) -> bool {
+    if (!v->def) return false;
+    if (v->def->kind == OpKind::CONSTANT && v->def->splat && v->type.dtype == DType::F32) { memcpy(out, v->def->const_data.data(), 4); return true; }
+    if (v->def->kind == OpKind::BROADCAST_IN_DIM && v->def->operands[0]->type.num_elements() == 1) return splat_f32(v->def->operands[0], out);
+    return false;
+  };
+  auto last_dim_bcast = [&](const Value* v) -> const Value* {   // broadcast of [..., S] to [..., S, T] along all leading dims
+    const Op* b = op_of(v, OpKind::BROADCAST_IN_DIM);
+    if (!b) return nullptr;
+    const Value* u = b->operands[0];
+    if (u->type.rank() != v->type.rank() - 1) return nullptr;
+    for (int i = 0; i < u->type.rank(); i++) if (b->dims[i] != i || u->type.dims[i] != v->type.dims[i]) return nullptr;
+    return u;
+  };
+  for (auto& up : m_.ops) {
+    const Op& d2 = *up;
+    if (d2.kind != OpKind::DOT_GENERAL) continue;
+    const Value* pv = d2.operands[0];
+    const Value* vv = d2.operands[1];
+    const int r = pv->type.rank();
+    if (r < 2 || vv->type.rank() != r || d2.results[0]->type.dtype != DType::BF16 || vv->type.dtype != DType::BF16) continue;
+    std::vector<int64_t> lead;
+    for (int i = 0; i < r - 2; i++) lead.push_back(i);
+    if (d2.lhs_batch != lead || d2.rhs_batch != lead || d2.lhs_contract != std::vector<int64_t>{r - 1} || d2.rhs_contract != std::vector<int64_t>{r - 2}) continue;
+    std::vector<const Op*> chain;
+    const Op* cvt = op_of(pv, OpKind::CONVERT);
+    const Value* pf = pv;
+    if (cvt) { if (!users_are(pv, {&d2}) || pv->type.dtype != DType::BF16) continue; chain.push_back(cvt); pf = cvt->operands[0]; }
+    else continue;   // P must reach the second product in bf16
+    const Op* div = op_of(pf, OpKind::DIVIDE);
+    if (!div || !users_are(pf, {cvt}) || pf->type.dtype != DType::F32) continue;
+    const Value* e = div->operands[0];
+    const Value* lsrc = last_dim_bcast(div->operands[1]);
+    if (!lsrc || !users_are(div->operands[1], {div})) continue;
+    const Op* lred = op_of(lsrc, OpKind::REDUCE);
+    if (!lred || lred->monoid != Monoid::ADD || lred->operands[0] != e || lred->dims != std::vector<int64_t>{r - 1} || !users_are(lsrc, {div->operands[1]->def})) continue;
+    float init = 1.f;
+    if (!splat_f32(lred->operands[1], &init) || init != 0.f) continue;
+    const Op* ex = op_of(e, OpKind::EXP);
+    if (!ex || !users_are(e, {div, lred})) continue;
+    const Op* sub = op_of(ex->operands[0], OpKind::SUBTRACT);
+    if (!sub || !users_are(ex->operands[0], {ex})) continue;
+    const Value* x = sub->operands[0];
+    const Value* msrc = last_dim_bcast(sub->operands[1]);
+    if (!msrc || !users_are(sub->operands[1], {sub})) continue;
+    const Op* mred = op_of(msrc, OpKind::REDUCE);
+    if (!mred || mred->monoid != Monoid::MAX || mred->operands[0] != x || mred->dims != std::vector<int64_t>{r - 1} || !users_are(msrc, {sub->operands[1]->def})) continue;
+    if (!splat_f32(mred->operands[1], &init) || !(init == -INFINITY)) continue;
+    if (!users_are(x, {sub, mred})) continue;
+    chain.insert(chain.end(), {div, div->operands[1]->def, lred, ex, sub, sub->operands[1]->def, mred});
+    // optional causal mask
+    bool causal = false;
+    const Value* y = x;
+    if (const Op* sel = op_of(x, OpKind::SELECT)) {
+      float ninf = 0.f;
+      if (!splat_f32(sel->operands[2], &ninf) || !(ninf == -INFINITY)) continue;
+      const Op* mb = op_of(sel->operands[0], OpKind::BROADCAST_IN_DIM);
+      if (!mb || mb->dims != std::vector<int64_t>{r - 2, r - 1}) continue;
+      const Op* cmp = op_of(mb->operands[0], OpKind::COMPARE);
+      if (!cmp || cmp->cmp_dir != CmpDir::GE) continue;
+      const Op* i0 = op_of(cmp->operands[0], OpKind::IOTA);
+      const Op* i1 = op_of(cmp->operands[1], OpKind::IOTA);
+      if (!i0 || !i1 || i0->iota_dim != 0 || i1->iota_dim != 1 || !dtype_is_signed_int(i0->results[0]->type.dtype)) continue;
+      causal = true;
+      y = sel->operands[1];
+      chain.push_back(sel);
+      if (!users_are(y, {sel})) continue;
+    }
+    float scale = 1.f;
+    const Value* sdot = y;
+    if (const Op* mul = op_of(y, OpKind::MULTIPLY)) {
+      float c = 0.f;
+      if (splat_f32(mul->operands[1], &c)) sdot = mul->operands[0];
+      else if (splat_f32(mul->operands[0], &c)) sdot = mul->operands[1];
+      else continue;
+      if (!(c > 0.f)) continue;
+      scale = c;
+      chain.push_back(mul);
+      if (!users_are(sdot, {mul})) continue;
+    }
+    const Op* d1 = op_of(sdot, OpKind::DOT_GENERAL);
+    if (!d1 || sdot->type.dtype != DType::F32) continue;
+    const Value* q = d1->operands[0];
+    const Value* k = d1->operands[1];
+    if (q->type.rank() != r || k->type.rank() != r || q->type.dtype != DType::BF16 || k->type.dtype != DType::BF16) continue;
+    if (d1->lhs_batch != lead || d1->rhs_batch != lead || d1->lhs_contract != std::vector<int64_t>{r - 1} || d1->rhs_contract != std::vector<int64_t>{r - 1}) continue;
+    const int64_t D = q->type.dims[r - 1];
+    if ((D != 64 && D != 128) || vv->type.dims[r - 1] != D || vv->type.dims[r - 2] != k->type.dims[r - 2]) continue;
+    chain.push_back(d1);
+    for (auto c : chain) skip_ops_.insert(c);
+    attn_[&d2] = AttnMatch{q, k, vv, scale, causal};
+  }
+}
+
+void Planner::emit_attention(const Op& op, const AttnMatch& m) {
+  const Value* res = op.results[0];
+  auto contiguous = [&](const Value* v) -> BufRef {
+    Layout L = layout_of(v);
+    if (!is_row_major(v->type.dims, L.strides)) {
+      L.buf = emit_strided_copy(L, v->type.dtype, v->type.dims, "copy:attention_operand");
+    }
+    return L.buf;
+  };
+  Step s;
+  s.kind = StepKind::ATTENTION;
+  s.label = "attention:%" + res->name;
+  const int r = m.q->type.rank();
+  s.aBH = 1;
+  for (int i = 0; i < r - 2; i++) s.aBH *= m.q->type.dims[i];
+  s.aSq = m.q->type.dims[r - 2];
+  s.aSk = m.k->type.dims[r - 2];
+  s.aD = m.q->type.dims[r - 1];
+  s.a_scale = m.scale;
+  s.a_causal = m.causal;
+  s.aq = contiguous(m.q); s.ak = contiguous(m.k); s.av = contiguous(m.v);
+  s.ao = materialise(res);
+  double pairs = m.causal ? 0.0 : (double)s.aSq * (double)s.aSk;
+  if (m.causal) for (int64_t i = 0; i < s.aSq; i++) pairs += (double)std::min<int64_t>(i + 1, s.aSk);
+  s.flops = 4.0 * (double)s.aBH * (double)s.aD * pairs;
+  s.bytes = (double)m.q->type.byte_size() + (double)m.k->type.byte_size() + (double)m.v->type.byte_size() + (double)res->type.byte_size();
+  plan_.steps.push_back(std::move(s));
 }
 
 // ---- classification ---------------------------------------------------------------------------------------------
@@ -1217,6 +1359,7 @@ Plan Planner::run() {
   for (auto a : m_.args) {
     plan_.arg_types.push_back(a->type);
   }
+  match_attention();
   classify();
   for (auto a : m_.args) {
     BufRef b;
@@ -1250,7 +1393,11 @@ Plan Planner::run() {
         }
         switch (op.kind) {
           case OpKind::REDUCE: emit_reduce(op); break;
-          case OpKind::DOT_GENERAL: emit_dot(op); break;
+          case OpKind::DOT_GENERAL: {
+            auto it = attn_.find(&op);
+            if (it != attn_.end()) emit_attention(op, it->second); else emit_dot(op);
+            break;
+          }
           case OpKind::TRANSPOSE: case OpKind::RESHAPE: emit_view_or_copy(op); break;
           case OpKind::ALL_REDUCE: case OpKind::ALL_GATHER: emit_collective(op); break;
           default: unimplemented(std::string(op_name(op.kind)) + " has no lowering");
