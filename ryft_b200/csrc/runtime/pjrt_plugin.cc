@@ -1098,17 +1098,35 @@ static PJRT_Error* LoadedExecutable_Execute(PJRT_LoadedExecutable_Execute_Args* 
   PJRT_Error* first_err = nullptr;
   for (auto& L : launches) if (L.err && !first_err) first_err = L.err;
 
+  // A launch that was poisoned fails on the host, before anything is enqueued.  Replicas of one execution meet in
+  // collectives, so if any local replica is poisoned none of them may start: the others are aborted as well, which
+  // keeps every GPU out of a collective that could never complete.
+  if (!first_err) {
+    int poisoned_k = -1;
+    for (size_t k = 0; k < locals.size(); k++) {
+      PJRT_Device* dev = le->addressable[locals[k]];
+      std::lock_guard<std::mutex> pl(dev->poison_mu);
+      auto it = dev->poisoned.find(launch_id);
+      if (it != dev->poisoned.end()) {
+        launches[k].err = make_error(it->second.first, it->second.second);
+        dev->poisoned.erase(it);
+        if (poisoned_k < 0) poisoned_k = (int)k;
+      }
+    }
+    if (poisoned_k >= 0) {
+      for (size_t k = 0; k < locals.size(); k++)
+        if (!launches[k].err)
+          launches[k].err = make_error(PJRT_Error_Code_ABORTED, "not launched: replica " + std::to_string(le->logical_ids[locals[poisoned_k]].replica) +
+                                                                    " of this execution failed before launch (" + launches[poisoned_k].err->message + ")");
+      first_err = launches[poisoned_k].err;
+    }
+  }
   if (!first_err) {
     auto run_one = [&](size_t k) {
       const int li = locals[k];
       PJRT_Device* dev = le->addressable[li];
       PerLaunch& L = launches[k];
       std::lock_guard<std::mutex> dl(dev->launch_mu);
-      {
-        std::lock_guard<std::mutex> pl(dev->poison_mu);
-        auto it = dev->poisoned.find(launch_id);
-        if (it != dev->poisoned.end()) { L.err = make_error(it->second.first, it->second.second); dev->poisoned.erase(it); return; }
-      }
       L.err = run_plan(le, li, le->logical_ids[li].replica, L.args, L.outs);
     };
     if (locals.size() == 1) run_one(0);

@@ -89,11 +89,26 @@ def test_c2_epilogue_is_fused_into_the_gemm():
     assert "arena 0 B" in dump                                               # nothing is materialised
 
 
-def test_c3_mask_is_folded_and_never_materialised():
-    dump = ryft_b200.plan_dump(configs.c3_program(1, 2, 256, 64))
-    # iota / compare / select run inside the first GEMM's epilogue as index arithmetic
-    assert "load iota1; cmp iota2 aux=2;" in dump and "select #0xff800000" in dump
-    assert dump.count("gemm ") == 2 and dump.count("reduce ") == 2
+def test_c3_is_recognised_as_fused_attention():
+    dump = ryft_b200.plan_dump(configs.c3_program())
+    assert "1 steps" in dump and "attention " in dump and "BH=128 Sq=4096 Sk=4096 D=128" in dump and "causal" in dump
+    assert "arena 0 B" in dump                                               # no score tensor exists
+    dump = ryft_b200.plan_dump(configs.c3_program(1, 2, 256, 64, causal=False))
+    assert "attention " in dump and "causal" not in dump
+
+
+def test_causal_mask_is_folded_into_the_gemm_epilogue():
+    # the scores of config 3 alone (no softmax behind them): iota / compare / select run as index arithmetic in the
+    # epilogue of the QK^T GEMM and the mask is never materialised
+    import math
+    b = Builder()
+    q = b.arg([2, 256, 64], "bf16"); k = b.arg([2, 256, 64], "bf16")
+    s = b.dot_general(q, k, ([0], [0]), ([2], [2]), out_dtype="f32")
+    s = b.multiply(s, b.splat(1.0 / math.sqrt(64), s))
+    mask = b.compare("GE", b.iota(0, [256, 256], "i32"), b.iota(1, [256, 256], "i32"), "SIGNED")
+    s = b.select(b.broadcast_in_dim(mask, [1, 2], [2, 256, 256]), s, b.splat(float("-inf"), s))
+    dump = ryft_b200.plan_dump(b.build(s))
+    assert "1 steps" in dump and "load iota1; cmp iota2 aux=2;" in dump and "select #0xff800000" in dump
 
 
 def test_c4_plan_shape():

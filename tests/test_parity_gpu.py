@@ -257,9 +257,38 @@ def test_tensor_core_and_cuda_core_paths_agree_at_full_c2_size(client):
 
 # ---- whole configurations at reduced sizes ------------------------------------------------------------------------------
 def test_c3_attention_unfused_path(client):
-    args = (2, 3, 256, 64)
-    check_program(client, configs.c3_program(*args), configs.c3_inputs(*args), "c3 small")
-    check_program(client, configs.c3_program(1, 2, 128, 128, causal=False), configs.c3_inputs(1, 2, 128, 128), "c3 non-causal")
+    """The attention program executed op by op (GEMM with the mask folded into its epilogue, reduces, elementwise):
+    the same rounding points as a CPU evaluation, so the standard tolerances apply."""
+    os.environ["B2X_FUSED_ATTENTION"] = "0"
+    try:
+        args = (2, 3, 256, 64)
+        check_program(client, configs.c3_program(*args), configs.c3_inputs(*args), "c3 small")
+        check_program(client, configs.c3_program(1, 2, 128, 128, causal=False), configs.c3_inputs(1, 2, 128, 128), "c3 non-causal")
+    finally:
+        del os.environ["B2X_FUSED_ATTENTION"]
+
+
+@pytest.mark.parametrize("B,H,S,D,causal", [(2, 3, 256, 64, True), (1, 2, 128, 128, False), (1, 2, 512, 128, True), (1, 1, 200, 128, True),
+                                             (2, 1, 1000, 64, False), (1, 1, 1152, 128, True)])
+def test_c3_attention_fused_kernel(client, B, H, S, D, causal):
+    """The fused kernel rounds the softmax weights to bf16 before they are normalised by the row sum (online softmax
+    cannot know the sum earlier); the program, and the oracle, round after.  Both are one bf16 rounding of every weight,
+    so the two results may differ by at most 2 * 2^-9 * sum_k p_k |v_k| per output element, plus the standard allowance
+    for the final bf16 rounding.  The bound is evaluated with the oracle itself (softmax weights applied to |V|)."""
+    import ryft_b200
+    text = configs.c3_program(B, H, S, D, causal=causal)
+    assert "attention " in ryft_b200.plan_dump(text)
+    q, k, v = configs.c3_inputs(B, H, S, D)
+    (got,) = run_gpu(client, text, [q, k, v])
+    (want,) = run_oracle(text, [q, k, v])
+    (spread,) = run_oracle(text, [q, k, np.abs(v.astype(np.float32)).astype(BF16)])
+    g, w, sp = got.astype(np.float64), want.astype(np.float64), spread.astype(np.float64)
+    rms = float(np.sqrt(np.mean(w ** 2)))
+    allowed = 1e-2 * np.maximum(np.abs(w), rms) + 2.0 ** -8 * sp
+    worst = float(np.max(np.abs(g - w) / allowed))
+    assert worst <= 1.0, f"fused attention exceeds the rounding bound by a factor {worst:.2f}"
+    # and the bulk agrees much more tightly than the bound
+    assert float(np.sqrt(np.mean((g - w) ** 2))) <= 3e-3 * rms + 1e-4
 
 
 def test_c3_causal_property(client):
