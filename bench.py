@@ -155,6 +155,9 @@ def time_device(client, exe, bufs, steps: int, warmup: int, world: int, stream_h
     t0.record(s)
     for _ in range(steps):
         last = exe.execute([pjrt.ExecutionDeviceInputs(bufs)])
+    # a step ends when its last output exists (a trailing all-reduce runs on the communication stream)
+    for out in last[0].outputs:
+        out.wait_until_ready_on_stream(stream_handle)
     t1.record(s)
     last[0].done.await_()
     t1.synchronize()
@@ -346,7 +349,12 @@ def main():
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "own":
         args.warmup = 3
+    # libraries (NCCL, the CUDA runtime) may print banners to stdout: keep stdout for the one JSON line
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     line = run_reference(args) if args.impl == "reference" else run_own(args)
+    sys.stdout.flush()
+    os.dup2(real_stdout, 1)
     if line is not None:
         print(json.dumps(line), flush=True)
 

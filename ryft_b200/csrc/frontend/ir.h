@@ -127,6 +127,9 @@ constexpr int kInternal = 13;
 // Parses MLIR text (pretty or generic op forms).  Throws CompileError.
 std::unique_ptr<Module> parse_module(const std::string& text);
 
+// Exact algebraic rewrites applied before planning (see canonicalize.cc).
+void canonicalize(Module& m);
+
 // Shape/dtype verification of every op against StableHLO's rules; fills nothing, throws on violation.
 void verify_module(const Module& m);
 

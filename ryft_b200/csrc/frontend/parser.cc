@@ -937,6 +937,8 @@ std::unique_ptr<Module> parse_module(const std::string& text) {
   Parser p(text);
   auto m = p.parse();
   verify_module(*m);
+  canonicalize(*m);
+  verify_module(*m);
   return m;
 }
 

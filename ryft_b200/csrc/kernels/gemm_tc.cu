@@ -1,7 +1,29 @@
 // Entry points of the tcgen05 GEMM (kernel: gemm_tc.cuh) and the f32 hi/lo split used by the 3xTF32 scheme.
 #include "gemm_tc.cuh"
 
+#include <atomic>
+#include <mutex>
+
 namespace b2x {
+
+static __device__ int32_t g_sched[kSchedSlots * 2];
+
+// Next scheduler pair for the current device (round robin).  Only the address of the array is taken here; device
+// code reads and resets it.
+int32_t* sched_slot() {
+  static std::mutex mu;
+  static int32_t* base[64] = {};
+  static unsigned next[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lk(mu);
+  if (!base[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_sched) != cudaSuccess) return nullptr;
+    base[dev] = (int32_t*)p;
+  }
+  return base[dev] + 2 * (next[dev]++ % kSchedSlots);
+}
 
 // ---- f32 -> hi/lo TF32 split for the 3xTF32 scheme ------------------------------------------------------------------
 // out rows are K-major with 3K elements: sel 0 -> [hi | hi | lo], sel 1 -> [hi | lo | hi].

@@ -30,6 +30,7 @@ struct TcParams {
   int64_t num_tiles;
   int32_t k_blocks;
   uint32_t idesc;
+  int32_t* sched;      // [0] next tile to hand out, [1] CTAs that have finished (the last one resets both)
 };
 
 constexpr int TC_BM = 128;
@@ -40,7 +41,7 @@ struct TcSmem {
   static constexpr int B_BYTES = BN * 128;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + slack for 1024-byte alignment
+  static constexpr int TOTAL = BAR_OFFSET + 384 + 1024;  // barriers, tile ring + slack for 1024-byte alignment
 };
 
 template <int BN, int STAGES, bool TF32, int ID>
@@ -59,11 +60,16 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t smem_base = smem_u32(smem);
   uint64_t* bars = (uint64_t*)(smem + SM::BAR_OFFSET);
-  // barrier slots: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], drain
+  // barrier slots: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], drain, sched_full[4], sched_empty[4]
   const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * STAGES, bar_tfull = bar_empty + 8 * STAGES,
-                 bar_tempty = bar_tfull + 16, bar_drain = bar_tempty + 16;
-  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 5);
+                 bar_tempty = bar_tfull + 16, bar_drain = bar_tempty + 16, bar_sfull = bar_drain + 8, bar_sempty = bar_sfull + 32;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 5 + 8);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  // Tiles are handed out dynamically: the producer draws the next tile index from a global counter and publishes it
+  // to the other roles through this ring, so a CTA that starts late (its SM was busy with another kernel, e.g. a
+  // collective) simply takes fewer tiles.
+  volatile int32_t* tile_ring = (volatile int32_t*)(tmem_slot + 2);
+  constexpr int RING = 4;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -71,6 +77,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
     for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
     for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 4); }
     mbar_init(bar_drain, 1);
+    for (int r = 0; r < RING; r++) { mbar_init(bar_sfull + 8 * r, 1); mbar_init(bar_sempty + 8 * r, 5); }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -93,7 +100,14 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int64_t t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+      for (int64_t local = 0; ok; local++) {
+        const int slot = (int)(local & (RING - 1));
+        if (!mbar_wait(bar_sempty + 8 * slot, (uint32_t)(((local / RING) & 1) ^ 1), abort_flag, status, 5)) { ok = false; break; }
+        int64_t t = (int64_t)atomicAdd(p.sched, 1);
+        if (t >= p.num_tiles) t = -1;
+        tile_ring[slot] = (int32_t)t;
+        mbar_arrive(bar_sfull + 8 * slot);
+        if (t < 0) break;
         const int b = (int)(t / tiles_per_batch);
         const int64_t rem = t - (int64_t)b * tiles_per_batch;
         const int m0 = (int)(rem % p.num_m_tiles) * TC_BM;
@@ -130,8 +144,12 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      int64_t local = 0;
-      for (int64_t t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x, local++) {
+      for (int64_t local = 0; ok; local++) {
+        const int slot = (int)(local & (RING - 1));
+        if (!mbar_wait(bar_sfull + 8 * slot, (uint32_t)((local / RING) & 1), abort_flag, status, 6)) { ok = false; break; }
+        const int32_t t = tile_ring[slot];
+        mbar_arrive(bar_sempty + 8 * slot);
+        if (t < 0) break;
         const int acc = (int)(local & 1);
         const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
         if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, status, 2)) { ok = false; break; }
@@ -164,8 +182,13 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
     // ------------------------------------------------ epilogue ------------------------------------------------------
     const int quad = warp & 3;              // TMEM lanes [32*quad, 32*quad + 32)
     bool ok = true;
-    int64_t local = 0;
-    for (int64_t t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x, local++) {
+    for (int64_t local = 0; ok; local++) {
+      const int slot = (int)(local & (RING - 1));
+      if (!mbar_wait(bar_sfull + 8 * slot, (uint32_t)((local / RING) & 1), abort_flag, status, 7)) { ok = false; break; }
+      const int64_t t = tile_ring[slot];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_sempty + 8 * slot);
+      if (t < 0) break;
       const int acc = (int)(local & 1);
       const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
       const int b = (int)(t / tiles_per_batch);
@@ -220,10 +243,22 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(p.sched + 1, 1) == (int)gridDim.x - 1) { p.sched[0] = 0; p.sched[1] = 0; __threadfence(); }
+  }
 }
 
+// Scheduler counters: a ring of (next tile, finished CTAs) pairs in device memory, one pair per launch in flight.
+// A pair returns to zero when its launch retires, so no memset is needed between launches.
+constexpr int kSchedSlots = 256;
+int32_t* sched_slot();   // defined in gemm_tc.cu
+
 template <int BN, int STAGES, bool TF32, int ID>
-static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, const B2xVmProgram& epi, int32_t* status, cudaStream_t stream) {
+static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p_in, const B2xVmProgram& epi, int32_t* status, cudaStream_t stream) {
+  TcParams p = p_in;
+  p.sched = sched_slot();
+  if (!p.sched) return (int)cudaErrorUnknown;
   using SM = TcSmem<BN, STAGES, TF32>;
   auto kern = k_gemm_tc<BN, STAGES, TF32, ID>;
   {

@@ -142,7 +142,7 @@ PJRT_Error* run_plan(PJRT_LoadedExecutable* le, int local_index, int replica, co
         }
         if (timed) B2X_CUDA(cudaEventRecord(t1, dev->comm));
         B2X_CUDA(cudaEventRecord(pd.coll_done[s.coll_id], dev->comm));
-        outstanding.push_back(s.coll_id);
+        if (!s.coll_detached) outstanding.push_back(s.coll_id);
         break;
       }
       case StepKind::COPY:

@@ -1144,6 +1144,17 @@ static PJRT_Error* LoadedExecutable_Execute(PJRT_LoadedExecutable_Execute_Args* 
     PerLaunch& L = launches[k];
     cudaSetDevice(dev->cuda_ordinal);
     const bool failed = L.err != nullptr;
+    // Collectives that the compute stream does not wait for still belong to this execution: its outputs and its
+    // completion event are recorded on the communication stream, behind everything the compute stream has queued.
+    cudaStream_t done_stream = dev->compute;
+    if (!failed && le->core->plans[0].has_detached_collectives) {
+      cudaEvent_t join;
+      cudaEventCreateWithFlags(&join, cudaEventDisableTiming);
+      cudaEventRecord(join, dev->compute);
+      cudaStreamWaitEvent(dev->comm, join, 0);
+      cudaEventDestroy(join);
+      done_stream = dev->comm;
+    }
     for (size_t o = 0; o < n_outs; o++) {
       PJRT_Buffer* ob = o < L.out_bufs.size() ? L.out_bufs[o] : nullptr;
       if (!ob) {
@@ -1152,7 +1163,7 @@ static PJRT_Error* LoadedExecutable_Execute(PJRT_LoadedExecutable_Execute_Args* 
         ob->pjrt_type = to_pjrt_type(ob->type.dtype); ob->owns = false;
       }
       if (failed) { ob->err_code = L.err->code; ob->err_msg = L.err->message; }
-      else { cudaEventCreateWithFlags(&ob->ready, cudaEventDisableTiming); cudaEventRecord(ob->ready, dev->compute); }
+      else { cudaEventCreateWithFlags(&ob->ready, cudaEventDisableTiming); cudaEventRecord(ob->ready, done_stream); }
       if (a->output_lists && a->output_lists[k]) a->output_lists[k][o] = ob;
     }
     // inputs are read by the enqueued kernels: their memory must not be reused before those finish
@@ -1174,7 +1185,7 @@ static PJRT_Error* LoadedExecutable_Execute(PJRT_LoadedExecutable_Execute_Args* 
       else {
         cudaEvent_t ce;
         cudaEventCreateWithFlags(&ce, cudaEventDisableTiming);
-        cudaEventRecord(ce, dev->compute);
+        cudaEventRecord(ce, done_stream);
         PJRT_Device* d = dev;
         le->client->post({ce, dev->cuda_ordinal, ev, [d](PJRT_Error_Code* code, std::string* msg) {
                             if (*code == PJRT_Error_Code_OK && d->status_host[0] != 0) {

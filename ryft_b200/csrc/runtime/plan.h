@@ -73,6 +73,8 @@ struct Step {
   std::vector<std::vector<int64_t>> replica_groups;
   int coll_id = -1;                // index among the plan's collective steps (they run on the communication stream)
   std::vector<int> wait_colls;     // collective ids whose completion this step must wait for before it starts
+  bool coll_detached = false;      // no step of the plan waits for it and it touches no arena memory: the compute stream
+                                   // does not wait for it either, so it overlaps with the next execution
 
   // COPY
   BufRef c_src, c_dst;
@@ -91,6 +93,7 @@ struct Plan {
   std::vector<Step> steps;
   int64_t arena_bytes = 0;
   int num_collectives = 0;
+  bool has_detached_collectives = false;
   std::vector<uint8_t> const_pool;
   double total_flops = 0, total_bytes = 0;
   int num_replicas = 1, num_partitions = 1;

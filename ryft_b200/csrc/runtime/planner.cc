@@ -106,6 +106,7 @@ struct ValueState {
   Layout layout;
   int alloc = -1;            // arena allocation id when it owns TEMP memory
   int out_index = -1;        // first module output slot it is written to directly
+  bool preassigned = false;  // memory was chosen before its producer ran (in-place collective result)
 };
 
 struct Alloc { int64_t bytes; int first, last; int64_t offset = -1; };
@@ -216,8 +217,26 @@ class Planner {
     s.layout.strides = strides;
   }
   // Gives `v` fresh memory: a module output slot when it is returned, arena memory otherwise.
+  // When `v` exists only to be all-reduced, the collective runs in place: `v` is produced directly in the buffer of
+  // the collective's result (an output buffer when that result is returned).
+  const Value* in_place_result(const Value* v) const {
+    if (v->users.size() != 1 || v->users[0]->kind != OpKind::ALL_REDUCE) return nullptr;
+    for (auto o : m_.outputs) if (o == v) return nullptr;
+    const Op* ar = v->users[0];
+    int hits = 0;
+    const Value* r = nullptr;
+    for (size_t i = 0; i < ar->operands.size(); i++) if (ar->operands[i] == v) { hits++; r = ar->results[i]; }
+    return hits == 1 ? r : nullptr;
+  }
   BufRef materialise(const Value* v) {
     ValueState& s = st(v);
+    if (s.has_layout && s.layout.buf.valid() && s.preassigned) return s.layout.buf;
+    if (const Value* r = in_place_result(v)) {
+      BufRef shared = materialise(r);
+      st(r).preassigned = true;
+      set_layout(v, shared, row_major_strides(v->type.dims));
+      return shared;
+    }
     BufRef b;
     for (size_t i = 0; i < m_.outputs.size(); i++)
       if (m_.outputs[i] == v) { b.kind = BufRef::OUT; b.index = (int)i; s.out_index = (int)i; break; }
@@ -1275,6 +1294,7 @@ void Planner::schedule_collectives() {
   plan_.num_collectives = n;
   for (size_t i = 0; i < out.size(); i++) {
     if (out[i].coll_id < 0) continue;
+    bool waited = false;
     for (size_t j = i + 1; j < out.size(); j++) {
       std::vector<BufRef> r, w;
       step_bufs(out[j], &r, &w);
@@ -1283,7 +1303,12 @@ void Planner::schedule_collectives() {
         for (auto& b : r) if (same_buf(b, c.dst)) dep = true;
         for (auto& b : w) if (same_buf(b, c.dst) || same_buf(b, c.src)) dep = true;
       }
-      if (dep) { out[j].wait_colls.push_back(out[i].coll_id); break; }
+      if (dep) { out[j].wait_colls.push_back(out[i].coll_id); waited = true; break; }
+    }
+    if (!waited) {
+      bool arena = false;
+      for (auto& c : out[i].colls) if (c.src.kind == BufRef::TEMP || c.dst.kind == BufRef::TEMP) arena = true;
+      if (!arena) { out[i].coll_detached = true; plan_.has_detached_collectives = true; }
     }
   }
   plan_.steps = std::move(out);
@@ -1488,7 +1513,7 @@ std::string Plan::dump() const {
         break;
       case StepKind::ALL_REDUCE: case StepKind::ALL_GATHER:
         o << (s.kind == StepKind::ALL_REDUCE ? "all_reduce" : "all_gather") << " #" << s.coll_id << " " << buf_str(s.colls[0].src) << " -> " << buf_str(s.colls[0].dst)
-          << " count=" << s.colls[0].count << " groups=" << s.replica_groups.size() << "\n";
+          << " count=" << s.colls[0].count << " groups=" << s.replica_groups.size() << (s.coll_detached ? " detached" : "") << "\n";
         break;
       case StepKind::COPY: o << "copy " << s.label << " " << buf_str(s.c_src) << " -> " << buf_str(s.c_dst) << " " << s.c_bytes << " B\n"; break;
     }
