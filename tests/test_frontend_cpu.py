@@ -120,14 +120,22 @@ def test_c4_plan_shape():
     assert first.count("store") == 2 and ":bf16" in first and ":f32" not in first.split("vm:")[1].split("code:")[0]
 
 
-def test_c5_collectives_are_split_and_hoisted_behind_their_producers():
+def test_c5_collectives_are_split_hoisted_and_run_in_place():
     dump = ryft_b200.plan_dump(configs.c4_program(replicas=8), num_replicas=8)
     lines = [l for l in dump.splitlines() if l.lstrip().startswith("[")]
-    kinds = [l.split("]")[1].split()[0 if "(wait" not in l else 2] for l in lines]
     first_ar = next(i for i, l in enumerate(lines) if "all_reduce #0" in l)
     last_gemm = max(i for i, l in enumerate(lines) if " gemm " in l)
     assert first_ar < last_gemm, "the first gradient all-reduce must start before the last GEMM is issued"
-    assert sum("(wait #" in l for l in lines) == 2
+    # the divide by the replica count (a power of two) moved in front of the collective and into the GEMM epilogue:
+    # no scaling pass remains, the collectives run in place on the output buffers and nothing in the plan waits for them
+    assert "elementwise fused:stablehlo.multiply:%60" not in dump and dump.count("elementwise ") == 1
+    assert "out1 -> out1" in dump and "out0 -> out0" in dump and dump.count("detached") == 2
+    assert "load acc0; mul #0x3e000000; store T0;" in dump       # accumulator * 1/8 straight into the output
+
+
+def test_scale_by_a_non_power_of_two_is_not_moved():
+    dump = ryft_b200.plan_dump(configs.c4_program(256, 128, 384, replicas=3), num_replicas=3)
+    assert dump.count("elementwise ") == 3 and "(wait #" in dump   # loss scale + two gradient scaling passes behind the all-reduce
 
 
 @pytest.mark.parametrize("body,needle", [
