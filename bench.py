@@ -127,6 +127,10 @@ def program_for(config: str, n_replicas: int):
         return configs.c3_program(), 2.0 * 4 * 32 * 128 * 4096 * 4097
     if config == "c1":
         return configs.c1_program(), 2.0 * 512 * 768 * 512
+    if config == "ew":
+        return configs.ew_program(), 2.0 * 32 * 2048 * 2048        # counted as 2 flops per element; the metric that matters is GB/s
+    if config == "red":
+        return configs.red_program(), 2.0 * 8192 * 4096
     raise SystemExit(f"unknown config {config}")
 
 
@@ -136,7 +140,7 @@ def inputs_for(config: str, replica: int):
         return configs.c4_inputs(T_FULL, D_FULL, F_FULL, seed=4, replica=replica)
     if config == "c4":
         return configs.c4_inputs(T_FULL, D_FULL, F_FULL)
-    return {"c2": configs.c2_inputs, "c3": configs.c3_inputs, "c1": configs.c1_inputs}[config]()
+    return {"c2": configs.c2_inputs, "c3": configs.c3_inputs, "c1": configs.c1_inputs, "ew": configs.ew_inputs, "red": configs.red_inputs}[config]()
 
 
 def time_device(client, exe, bufs, steps: int, warmup: int, world: int, stream_handle: int, local: int):
@@ -237,6 +241,22 @@ def run_own(args) -> dict:
         roofline = {"bound": "tensor", "kernel": "k_gemm_tc (tcgen05, 128xBN tiles)", "achieved": achieved, "peak": peaks["bf16_tflops_sustained"],
                     "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": None,
                     "peak_source": f"{peaks['source']} (sustained cuBLAS bf16)", "avg_launch_ms": gemm_ms / max(gemm_launches, 1)}
+    hbm_cfg = {"ew": (32 * 2048 * 2048 * 6.0 + 8192, "elementwise", "k_elementwise (fused add + tanh + convert)"),
+               "red": (8192 * 4096 * 4.0, "reduce", "k_reduce_rows (square prologue, two passes)")}
+    if config in hbm_cfg:
+        algo_bytes, prefix, kname = hbm_cfg[config]
+        k_ms = sum(t["ms"] for t in timings if t["label"].startswith(prefix) and t["bytes"] > 1e6)
+        if k_ms > 0:
+            gbs = algo_bytes * args.steps / (k_ms * 1e-3) / 1e9
+            roofline = {"bound": "hbm", "kernel": kname, "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                        "traffic": None, "peak_source": peaks["source"], "avg_launch_ms": k_ms / args.steps}
+    if config == "c3":
+        a_ms = sum(t["ms"] for t in timings if t["label"].startswith("attention"))
+        if a_ms > 0:
+            achieved = flops_per_replica * args.steps / (a_ms * 1e-3) / 1e12
+            roofline = {"bound": "tensor", "kernel": "k_attention (tcgen05, online softmax)", "achieved": achieved, "peak": peaks["bf16_tflops_sustained"],
+                        "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": None,
+                        "peak_source": f"{peaks['source']} (sustained cuBLAS bf16)", "avg_launch_ms": a_ms / args.steps}
     if config == "c2" and gemm_ms > 0:
         algo_bytes = 301_998_080.0
         gbs = algo_bytes * args.steps / (gemm_ms * 1e-3) / 1e9
@@ -251,7 +271,9 @@ def run_own(args) -> dict:
         "config": {"workload": {"c5": f"config 5: MLP fwd+bwd gradient step, tokens {T_FULL} x d {D_FULL} x ff {F_FULL} per replica, all_reduce(sum) of "
                                       f"f32 dW1+dW2 ({2 * D_FULL * F_FULL * 4} B) over {n_rep} replica(s), divide by replica count",
                                 "c4": "config 4: MLP fwd+bwd gradient step on one GPU", "c2": "config 2: batched bf16 dot_general + bias + tanh + convert",
-                                "c3": "config 3: causal attention written out in StableHLO", "c1": "config 1: f32 dot_general 512x768x512"}[config],
+                                "c3": "config 3: causal attention written out in StableHLO", "c1": "config 1: f32 dot_general 512x768x512",
+                                "ew": "micro: config 2's epilogue chain standalone, tanh(f32[32,2048,2048] + bias) -> bf16",
+                                "red": "micro: config 4's loss reduction standalone, sum of squares of f32[8192,4096]"}[config],
                    "replicas": n_rep, "parallelism": f"dp{n_rep}", "l2": "inputs (>= 320 MiB per step) exceed the 126 MB L2; no flush needed"},
         "gpu_launches": launches_per_exec * args.steps, "clocks": clocks,
         "steps_breakdown": [{"label": t["label"], "ms_per_step": t["ms"] / max(t["executions"], 1)} for t in timings],
@@ -275,7 +297,7 @@ def extras(client, peaks, local) -> dict:
     """dot_general (config 2) and attention (config 3) at full size, timed briefly on the same GPU."""
     from ryft_b200 import pjrt
     out = {}
-    for cfg, steps in (("c2", 20), ("c3", 3), ("c1", 20)):
+    for cfg, steps in (("c2", 20), ("c3", 5), ("c1", 20), ("ew", 10), ("red", 20)):
         try:
             text, flops = program_for(cfg, 1)
             exe = client.compile(pjrt.Program.mlir(text))
@@ -284,8 +306,9 @@ def extras(client, peaks, local) -> dict:
             ms, timings, _ = time_device(client, exe, bufs, steps, 3, 1, dev.compute_stream(), local)
             out[cfg] = {"ms_per_step": ms / steps, "tflops": flops * steps / (ms * 1e-3) / 1e12,
                         "steps_breakdown": [{"label": t["label"], "ms_per_step": t["ms"] / max(t["executions"], 1)} for t in timings]}
-            if cfg == "c2":
-                out[cfg]["hbm_gbs"] = 301_998_080.0 * steps / (ms * 1e-3) / 1e9
+            algo = {"c2": 301_998_080.0, "ew": 32 * 2048 * 2048 * 6.0 + 8192, "red": 8192 * 4096 * 4.0}.get(cfg)
+            if algo:
+                out[cfg]["hbm_gbs"] = algo * steps / (ms * 1e-3) / 1e9
                 out[cfg]["hbm_frac"] = out[cfg]["hbm_gbs"] / peaks["hbm_gbs"]
             del bufs, exe
         except Exception as e:  # report, never hide
@@ -343,7 +366,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
-    ap.add_argument("--config", default="c5", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--config", default="c5", choices=["c1", "c2", "c3", "c4", "c5", "ew", "red"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
     args = ap.parse_args()

@@ -167,3 +167,31 @@ def c4_inputs(T=8192, D=4096, F=16384, seed=3, replica: int | None = None):
 
 
 C4_GEMM_FLOPS = lambda T, D, F: 5 * 2.0 * T * D * F
+
+
+# ---- micro-configurations for the HBM-bound kernels (the epilogue chain of config 2 and the loss reduction of config 4,
+# ---- standalone at their native sizes) ----------------------------------------------------------------------------------
+def ew_program(B=32, M=2048, N=2048) -> str:
+    """tanh(acc + bias) -> bf16 over an f32 [B, M, N] tensor: reads 4 B, writes 2 B per element."""
+    b = Builder()
+    acc = b.arg([B, M, N], "f32")
+    bias = b.arg([N], "f32")
+    y = b.tanh(b.add(acc, b.broadcast_in_dim(bias, [2], [B, M, N])))
+    return b.build(b.convert(y, "bf16"))
+
+
+def ew_inputs(B=32, M=2048, N=2048, seed=5):
+    rng = np.random.default_rng(seed)
+    return [rng.standard_normal((B, M, N), dtype=np.float32) * np.float32(0.1), rng.standard_normal((N,), dtype=np.float32) * np.float32(0.1)]
+
+
+def red_program(T=8192, D=4096) -> str:
+    """sum(y * y) / (T * D) over an f32 [T, D] tensor: reads 4 B per element."""
+    b = Builder()
+    y = b.arg([T, D], "f32")
+    ssq = b.reduce(b.multiply(y, y), b.constant(0.0, [], "f32"), "add", [0, 1])
+    return b.build(b.multiply(ssq, b.constant(1.0 / (float(T) * float(D)), [], "f32")))
+
+
+def red_inputs(T=8192, D=4096, seed=6):
+    return [np.random.default_rng(seed).standard_normal((T, D), dtype=np.float32)]

@@ -3,12 +3,13 @@
 //   C[b][m][n] = sum_k A[b][m][k] * B[b][k][n],  A and B bf16 / f16 (kind::f16) or f32 read as TF32 (kind::tf32),
 //   f32 accumulation in TMEM, result handed to the fused elementwise epilogue program (vm.cuh) which does the stores.
 //
-// One CTA per SM (grid = min(tiles, 148)), 192 threads:
+// One CTA per SM (grid = min(tiles, 148)), 320 threads:
 //   warp 0     TMA producer: per k-block one 128 x BK tile of A and one BN x BK tile of B into a STAGES-deep ring of
 //              128-byte-swizzled shared-memory buffers (cp.async.bulk.tensor, per CTA, no multicast);
 //   warp 1     MMA issuer: one elected lane issues tcgen05.mma (128 x BN x 16) over the ring, commits each stage back
 //              to the producer and each finished accumulator to the epilogue; also owns TMEM allocation;
-//   warps 2-5  epilogue: tcgen05.ld the 128 x BN f32 accumulator (each warp its 32 lanes), run the epilogue program on
+//   warps 2-9  epilogue: tcgen05.ld the 128 x BN f32 accumulator (each warp its 32 lanes and one half of the columns, so
+//              that two warps per scheduler hide each other's latencies), run the epilogue program on
 //              8-wide row vectors and store.  Two accumulators (2 x BN TMEM columns) let tile i's epilogue overlap
 //              tile i+1's main loop.
 // Either operand may be K-major (k contiguous) or MN-major (m or n contiguous); the second form covers the
@@ -45,7 +46,7 @@ struct TcSmem {
 };
 
 template <int BN, int STAGES, bool TF32, int ID>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ TcParams p,
           const __grid_constant__ B2xVmProgram epi, int32_t* status) {
   using namespace sm100;
@@ -75,9 +76,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-    for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 4); }
+    for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 8); }
     mbar_init(bar_drain, 1);
-    for (int r = 0; r < RING; r++) { mbar_init(bar_sfull + 8 * r, 1); mbar_init(bar_sempty + 8 * r, 5); }
+    for (int r = 0; r < RING; r++) { mbar_init(bar_sfull + 8 * r, 1); mbar_init(bar_sempty + 8 * r, 9); }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -181,6 +182,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   } else {
     // ------------------------------------------------ epilogue ------------------------------------------------------
     const int quad = warp & 3;              // TMEM lanes [32*quad, 32*quad + 32)
+    const int half = (warp - 2) >> 2;       // columns [half * BN/2, (half + 1) * BN/2)
     bool ok = true;
     for (int64_t local = 0; ok; local++) {
       const int slot = (int)(local & (RING - 1));
@@ -199,11 +201,12 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       tc_fence_after();
       const int64_t row = (int64_t)m0 + quad * 32 + lane;
       const bool row_ok = row < p.M;
-      const uint64_t row_lin = (uint64_t)(((int64_t)b * p.M + row) * p.N);
+      VmRow vrow;
+      vm_row_begin(epi, (uint64_t)((int64_t)b * p.M + (row_ok ? row : 0)), (uint32_t)p.N, vrow);
       if constexpr (ID != 0) {
         // specialised epilogue: straight-line code, four 8-wide vectors per 32-column TMEM load
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; c++) {
+        for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); c++) {
           uint32_t r[32];
           tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32), r);
           tc_wait_ld();
@@ -215,7 +218,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                 uint32_t a0[8], out[8];
 #pragma unroll
                 for (int j = 0; j < 8; j++) a0[j] = r[v * 8 + j];
-                vm_run<8, ID>(epi, row_lin + (uint64_t)col, a0, out);
+                vm_run_row<8, ID>(epi, vrow, (uint32_t)col, a0, out);
               }
             }
           }
@@ -223,12 +226,12 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       } else {
         // interpreted epilogue: one inlined copy of the interpreter, fed 8 columns at a time
 #pragma unroll 1
-        for (int c = 0; c < BN / 8; c++) {
+        for (int c = half * (BN / 16); c < (half + 1) * (BN / 16); c++) {
           uint32_t a0[8], out[8];
           tmem_ld_32x8(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 8), a0);
           tc_wait_ld();
           const int col = n0 + c * 8;
-          if (row_ok && col < p.N) vm_run<8, 0>(epi, row_lin + (uint64_t)col, a0, out);
+          if (row_ok && col < p.N) vm_run_row<8, 0>(epi, vrow, (uint32_t)col, a0, out);
         }
       }
       tc_fence_before();
@@ -273,7 +276,7 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcPar
     }
   }
   int64_t grid = p.num_tiles < kNumSms ? p.num_tiles : kNumSms;
-  kern<<<(unsigned)grid, 192, SM::TOTAL, stream>>>(tmA, tmB, p, epi, status);
+  kern<<<(unsigned)grid, 320, SM::TOTAL, stream>>>(tmA, tmB, p, epi, status);
   count_launch();
   return (int)cudaGetLastError();
 }

@@ -201,6 +201,25 @@ __device__ __forceinline__ float vm_tanh_fast(float x) {
   return y;
 }
 
+// tanh to within about 2 ulp without divergent branches: odd polynomial for |x| < 0.3, 1 - 2 / (1 + e^{2|x|}) above
+// (ex2.approx and rcp.approx are each within 2^-22 relative, the result is >= 0.29 there so the absolute error of the
+// quotient stays below one ulp of the result).
+__device__ __forceinline__ float vm_tanh(float x) {
+  const float ax = fabsf(x);
+  const float x2 = x * x;
+  float p = fmaf(x2, -0.00886323552f, 0.0218694885f);      // -1382/155925, 62/2835
+  p = fmaf(x2, p, -0.0539682540f);                          // -17/315
+  p = fmaf(x2, p, 0.133333333f);                            // 2/15
+  p = fmaf(x2, p, -0.333333333f);                           // -1/3
+  const float small = fmaf(x * x2, p, x);
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(ax * 2.88539008f));   // e^{2|x|}
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.0f));
+  const float big = copysignf(fmaf(-2.0f, r, 1.0f), x);
+  return ax < 0.3f ? small : big;
+}
+
 template <typename T>
 __device__ __forceinline__ bool vm_cmp(T x, T y, uint8_t dir) {
   switch (dir) {
@@ -318,8 +337,11 @@ __device__ __forceinline__ int64_t vm_offset(const B2xVmTensor& T, const int64_t
 
 // One instruction.  Every argument except the state is uniform across the grid; when the caller passes compile-time
 // constants (specialised programs) the switches below fold away and only the selected op's code remains.
+// `off[t]` is tensor t's element offset for this vector without the part contributed by `col` along the innermost dim
+// (callers that have no separate column pass col = 0 and fold everything into off).
 template <int V>
-__device__ __forceinline__ void vm_exec(const B2xVmProgram& P, const int64_t (&coord)[B2X_VM_MAX_DIMS], const int nd, const uint8_t op,
+__device__ __forceinline__ void vm_exec(const B2xVmProgram& P, const int64_t (&coord)[B2X_VM_MAX_DIMS], const int nd,
+                                        const int64_t (&off)[B2X_VM_MAX_TENSORS], const int64_t col, const uint8_t op,
                                         const uint8_t src_kind, const uint8_t src_idx, const uint8_t aux, const uint8_t tc, const uint8_t rnd,
                                         const uint32_t imm, const uint8_t elem, const uint32_t (&acc0)[V], VmState<V>& S) {
   // ---- operand fetch ----
@@ -330,7 +352,10 @@ __device__ __forceinline__ void vm_exec(const B2xVmProgram& P, const int64_t (&c
     case VM_SRC_TENSOR:
       if (op != VM_STORE) {
         const B2xVmTensor& T = P.tensors[src_idx];
-        vm_fetch<V>(T.ptr, elem, vm_offset(T, coord, nd), T.stride[nd - 1], S.b);
+        int64_t o = 0;
+#pragma unroll
+        for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) if (t == src_idx) o = off[t];
+        vm_fetch<V>(T.ptr, elem, o + col * T.stride[nd - 1], T.stride[nd - 1], S.b);
       }
       break;
     case VM_SRC_IMM:
@@ -342,6 +367,7 @@ __device__ __forceinline__ void vm_exec(const B2xVmProgram& P, const int64_t (&c
       int32_t c0 = 0;
 #pragma unroll
       for (int d = 0; d < B2X_VM_MAX_DIMS; d++) if (d == src_idx) c0 = (int32_t)coord[d];
+      if (inner) c0 += (int32_t)col;
 #pragma unroll
       for (int j = 0; j < V; j++) {
         int32_t c = c0 + (inner ? j : 0);
@@ -368,7 +394,10 @@ __device__ __forceinline__ void vm_exec(const B2xVmProgram& P, const int64_t (&c
       break;
     case VM_STORE: {
       const B2xVmTensor& T = P.tensors[src_idx];
-      vm_put<V>(T.ptr, elem, vm_offset(T, coord, nd), T.stride[nd - 1], S.acc);
+      int64_t o = 0;
+#pragma unroll
+      for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) if (t == src_idx) o = off[t];
+      vm_put<V>(T.ptr, elem, o + col * T.stride[nd - 1], T.stride[nd - 1], S.acc);
       narrow = false;
       break;
     }
@@ -404,7 +433,7 @@ __device__ __forceinline__ void vm_exec(const B2xVmProgram& P, const int64_t (&c
       if (tc == VM_F32) B2X_VM_UN_F(fabsf(x))
       else if (tc == VM_S32) { _Pragma("unroll") for (int j = 0; j < V; j++) { int x = (int)S.acc[j]; S.acc[j] = (uint32_t)(x < 0 ? -x : x); } }
       break;
-    case VM_TANH: if (aux) B2X_VM_UN_F(vm_tanh_fast(x)) else B2X_VM_UN_F(tanhf(x)) break;
+    case VM_TANH: if (aux) B2X_VM_UN_F(vm_tanh_fast(x)) else B2X_VM_UN_F(vm_tanh(x)) break;
     case VM_EXP: if (aux) B2X_VM_UN_F(__expf(x)) else B2X_VM_UN_F(expf(x)) break;
     case VM_SQRT: B2X_VM_UN_F(sqrtf(x)) break;
     case VM_LOG: if (aux) B2X_VM_UN_F(__logf(x)) else B2X_VM_UN_RARE(VM_LOG) break;
@@ -464,22 +493,19 @@ template <int ID> struct VmStatic { static constexpr int n = 0; };
 namespace b2x {
 
 template <int V, int ID, int PC>
-__device__ __forceinline__ void vm_unroll(const B2xVmProgram& P, const int64_t (&coord)[B2X_VM_MAX_DIMS], const int nd, const uint32_t (&acc0)[V],
-                                          VmState<V>& S) {
+__device__ __forceinline__ void vm_unroll(const B2xVmProgram& P, const int64_t (&coord)[B2X_VM_MAX_DIMS], const int nd,
+                                          const int64_t (&off)[B2X_VM_MAX_TENSORS], const int64_t col, const uint32_t (&acc0)[V], VmState<V>& S) {
   if constexpr (PC < VmStatic<ID>::n) {
     constexpr VmSig G = VmStatic<ID>::at(PC);
     constexpr uint8_t elem = (G.src_kind == VM_SRC_TENSOR) ? VmStatic<ID>::elem(G.src_idx) : (uint8_t)0;
-    vm_exec<V>(P, coord, nd, G.op, G.src_kind, G.src_idx, G.aux, G.tc, G.rnd, P.code[PC].imm, elem, acc0, S);
-    vm_unroll<V, ID, PC + 1>(P, coord, nd, acc0, S);
+    vm_exec<V>(P, coord, nd, off, col, G.op, G.src_kind, G.src_idx, G.aux, G.tc, G.rnd, P.code[PC].imm, elem, acc0, S);
+    vm_unroll<V, ID, PC + 1>(P, coord, nd, off, col, acc0, S);
   }
 }
 
-// Runs the program for the V elements whose first element has linear index `lin` in the root shape.
-// `acc0` feeds VM_SRC_ACC0 operands.  On return `acc` holds the final accumulator (used by reductions).
-template <int V, int ID = 0>
-__device__ __forceinline__ void vm_run(const B2xVmProgram& P, uint64_t lin, const uint32_t (&acc0)[V], uint32_t (&acc)[V]) {
-  int64_t coord[B2X_VM_MAX_DIMS];
-  vm_coords(P, lin, coord);
+template <int V, int ID>
+__device__ __forceinline__ void vm_run_core(const B2xVmProgram& P, const int64_t (&coord)[B2X_VM_MAX_DIMS], const int64_t (&off)[B2X_VM_MAX_TENSORS],
+                                            const int64_t col, const uint32_t (&acc0)[V], uint32_t (&acc)[V]) {
   const int nd = P.n_dims;
   VmState<V> S;
 #pragma unroll
@@ -489,13 +515,63 @@ __device__ __forceinline__ void vm_run(const B2xVmProgram& P, uint64_t lin, cons
     for (int pc = 0; pc < P.n_instr; pc++) {
       const B2xVmInstr I = P.code[pc];
       const uint8_t elem = (I.src_kind == VM_SRC_TENSOR) ? P.tensors[I.src_idx].elem : (uint8_t)0;
-      vm_exec<V>(P, coord, nd, I.op, I.src_kind, I.src_idx, I.aux, I.tc, I.rnd, I.imm, elem, acc0, S);
+      vm_exec<V>(P, coord, nd, off, col, I.op, I.src_kind, I.src_idx, I.aux, I.tc, I.rnd, I.imm, elem, acc0, S);
     }
   } else {
-    vm_unroll<V, ID, 0>(P, coord, nd, acc0, S);
+    vm_unroll<V, ID, 0>(P, coord, nd, off, col, acc0, S);
   }
 #pragma unroll
   for (int j = 0; j < V; j++) acc[j] = S.acc[j];
+}
+
+// Runs the program for the V elements whose first element has linear index `lin` in the root shape.
+// `acc0` feeds VM_SRC_ACC0 operands.  On return `acc` holds the final accumulator (used by reductions).
+template <int V, int ID = 0>
+__device__ __forceinline__ void vm_run(const B2xVmProgram& P, uint64_t lin, const uint32_t (&acc0)[V], uint32_t (&acc)[V]) {
+  int64_t coord[B2X_VM_MAX_DIMS];
+  vm_coords(P, lin, coord);
+  int64_t off[B2X_VM_MAX_TENSORS];
+#pragma unroll
+  for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) off[t] = (t < P.n_tensors) ? vm_offset(P.tensors[t], coord, P.n_dims) : 0;
+  vm_run_core<V, ID>(P, coord, off, 0, acc0, acc);
+}
+
+// Row-wise driver for kernels that walk a [rows, N] result one row at a time (GEMM epilogues): the coordinate
+// decomposition and every tensor's row offset are computed once per row, each vector then only adds its column.
+struct VmRow {
+  int64_t coord[B2X_VM_MAX_DIMS];
+  int64_t off[B2X_VM_MAX_TENSORS];
+  bool fast;     // the innermost program dim is a whole number of rows
+  uint64_t row;
+  uint32_t N;
+};
+__device__ __forceinline__ void vm_row_begin(const B2xVmProgram& P, uint64_t row, uint32_t N, VmRow& R) {
+  const int nd = P.n_dims;
+  const uint64_t inner = (uint64_t)P.dim[nd - 1];
+  R.row = row; R.N = N;
+  R.fast = (inner % N) == 0;
+#pragma unroll
+  for (int d = 0; d < B2X_VM_MAX_DIMS; d++) R.coord[d] = 0;
+#pragma unroll
+  for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) R.off[t] = 0;
+  if (!R.fast) return;
+  const uint64_t per = inner / N;            // rows folded into the innermost program dim
+  uint64_t outer = row / per;
+  const int64_t inner_base = (int64_t)((row - outer * per) * N);
+#pragma unroll
+  for (int d = B2X_VM_MAX_DIMS - 2; d >= 1; d--) {
+    if (d < nd - 1) { const uint64_t n = (uint64_t)P.dim[d]; const uint64_t q = outer / n; R.coord[d] = (int64_t)(outer - q * n); outer = q; }
+  }
+  if (nd >= 2) R.coord[0] = (int64_t)outer;
+#pragma unroll
+  for (int d = 0; d < B2X_VM_MAX_DIMS; d++) if (d == nd - 1) R.coord[d] = inner_base;
+#pragma unroll
+  for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) if (t < P.n_tensors) R.off[t] = vm_offset(P.tensors[t], R.coord, nd);
+}
+template <int V, int ID = 0>
+__device__ __forceinline__ void vm_run_row(const B2xVmProgram& P, const VmRow& R, uint32_t col, const uint32_t (&acc0)[V], uint32_t (&acc)[V]) {
+  if (R.fast) vm_run_core<V, ID>(P, R.coord, R.off, (int64_t)col, acc0, acc);
+  else vm_run<V, ID>(P, R.row * R.N + col, acc0, acc);
 }
 
 // Signature hash of a program (structure only: ops, operand kinds, classes, rounding, tensor element types).
