@@ -5,7 +5,8 @@
 // (builders: crates/ryft-mlir/src/dialects/stable_hlo/operations/linear_algebra.rs:756-797, functional.rs:188-219,
 // comparison.rs:136-164, control_flow.rs:263) and replaces it with this kernel; no score tensor touches HBM.
 //
-// One CTA per (batch*head, 128-row query tile), heaviest (longest causal prefix) tiles first.  192 threads:
+// One CTA per (batch*head, 128-row query tile); the tiles of one head are adjacent in the grid (K/V reuse in L2),
+// longest causal prefix first.  192 threads:
 //   warp 0      TMA producer: Q once, then K and V blocks of 128 keys into a 2-deep ring (per-CTA loads, no multicast)
 //   warp 1      MMA issuer: S_j = Q K_j^T into one of two TMEM score buffers, O += P_j V_j into a TMEM accumulator;
 //               S_{j+1} is issued before P_j is consumed so the tensor pipe works while the softmax warps run
@@ -77,8 +78,10 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = p.n_q_tiles - 1 - (int)(blockIdx.x / p.BH);
-  const int bh = (int)(blockIdx.x % p.BH);
+  // consecutive CTAs are the query tiles of one (batch, head), longest causal prefix first: they run together and find
+  // that head's K and V in L2
+  const int bh = (int)(blockIdx.x / p.n_q_tiles);
+  const int qt = p.n_q_tiles - 1 - (int)(blockIdx.x % p.n_q_tiles);
   const int q0 = qt * AT_M;
   int64_t k_end = p.Sk;
   if (p.causal && (int64_t)q0 + AT_M < k_end) k_end = (int64_t)q0 + AT_M;

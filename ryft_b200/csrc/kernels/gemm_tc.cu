@@ -91,6 +91,15 @@ extern "C" int b2x_launch_gemm_tc(const B2xGemmArgs* a, const B2xVmProgram* epil
   p.num_n_tiles = (int)((a->N + BN - 1) / BN);
   p.num_tiles = (int64_t)p.num_m_tiles * p.num_n_tiles * a->batch;
   p.k_blocks = (int)((a->K + BK - 1) / BK);
+  {
+    // A slab of a group ~ 32 MiB (a quarter of the 126 MB L2)
+    const int64_t slab_per_m_tile = (int64_t)TC_BM * a->K * es;
+    int64_t gm = (32ll << 20) / (slab_per_m_tile > 0 ? slab_per_m_tile : 1);
+    if (gm < 4) gm = 4;
+    if (gm > 64) gm = 64;
+    if (gm > p.num_m_tiles) gm = p.num_m_tiles;
+    p.group_m = (int)gm;
+  }
   p.idesc = sm100::make_idesc(tf32 ? 2u : (a->elem == EL_BF16 ? 1u : 0u), a_mn, b_mn, TC_BM, (uint32_t)BN);
   if (tf32) {
     if (BN == 256) return launch_tc<256, 4, true, 0>(tmA, tmB, p, *epilogue, status, stream);

@@ -3,13 +3,13 @@
 //   C[b][m][n] = sum_k A[b][m][k] * B[b][k][n],  A and B bf16 / f16 (kind::f16) or f32 read as TF32 (kind::tf32),
 //   f32 accumulation in TMEM, result handed to the fused elementwise epilogue program (vm.cuh) which does the stores.
 //
-// One CTA per SM (grid = min(tiles, 148)), 320 threads:
+// One CTA per SM (grid = min(tiles, 148)), 64 + 32 * TC_EPI_WARPS threads:
 //   warp 0     TMA producer: per k-block one 128 x BK tile of A and one BN x BK tile of B into a STAGES-deep ring of
 //              128-byte-swizzled shared-memory buffers (cp.async.bulk.tensor, per CTA, no multicast);
 //   warp 1     MMA issuer: one elected lane issues tcgen05.mma (128 x BN x 16) over the ring, commits each stage back
 //              to the producer and each finished accumulator to the epilogue; also owns TMEM allocation;
-//   warps 2-9  epilogue: tcgen05.ld the 128 x BN f32 accumulator (each warp its 32 lanes and one half of the columns, so
-//              that two warps per scheduler hide each other's latencies), run the epilogue program on
+//   warps 2..  epilogue: tcgen05.ld the 128 x BN f32 accumulator (each warp its 32 lanes and every fourth 32-column
+//              chunk, so that four warps per scheduler hide each other's latencies), run the epilogue program on
 //              8-wide row vectors and store.  Two accumulators (2 x BN TMEM columns) let tile i's epilogue overlap
 //              tile i+1's main loop.
 // Either operand may be K-major (k contiguous) or MN-major (m or n contiguous); the second form covers the
@@ -30,11 +30,33 @@ struct TcParams {
   int32_t num_m_tiles, num_n_tiles;
   int64_t num_tiles;
   int32_t k_blocks;
+  int32_t group_m;     // m-tiles per raster group: a group's A slab stays in L2 while its n-tiles stream by
   uint32_t idesc;
   int32_t* sched;      // [0] next tile to hand out, [1] CTAs that have finished (the last one resets both)
 };
 
 constexpr int TC_BM = 128;
+constexpr int TC_EPI_WARPS = 16;                    // four per TMEM lane quarter, i.e. four per warp scheduler
+constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;
+constexpr int TC_COL_PARTS = TC_EPI_WARPS / 4;
+
+// Tile order: batches outermost; inside a batch, groups of `group_m` m-tiles, and inside a group m fastest.  Tiles that
+// run at the same time then share a few rows of A and a few columns of B, and consecutive waves reuse the group's A
+// slab out of L2 instead of streaming all of A from HBM once per wave.
+__device__ __forceinline__ void tc_tile_coords(const struct TcParams& p, int64_t t, int BN, int* b, int* m0, int* n0);
+
+__device__ __forceinline__ void tc_tile_coords(const TcParams& p, int64_t t, int BN, int* b, int* m0, int* n0) {
+  const int64_t per_batch = (int64_t)p.num_m_tiles * p.num_n_tiles;
+  const int bb = (int)(t / per_batch);
+  const int64_t r = t - (int64_t)bb * per_batch;
+  const int64_t per_group = (int64_t)p.group_m * p.num_n_tiles;
+  const int g = (int)(r / per_group);
+  const int64_t in = r - (int64_t)g * per_group;
+  const int gm = min(p.group_m, p.num_m_tiles - g * p.group_m);
+  *b = bb;
+  *m0 = (g * p.group_m + (int)(in % gm)) * TC_BM;
+  *n0 = (int)(in / gm) * BN;
+}
 
 template <int BN, int STAGES, bool TF32>
 struct TcSmem {
@@ -46,7 +68,7 @@ struct TcSmem {
 };
 
 template <int BN, int STAGES, bool TF32, int ID>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(TC_THREADS, 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ TcParams p,
           const __grid_constant__ B2xVmProgram epi, int32_t* status) {
   using namespace sm100;
@@ -76,9 +98,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-    for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 8); }
+    for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, TC_EPI_WARPS); }
     mbar_init(bar_drain, 1);
-    for (int r = 0; r < RING; r++) { mbar_init(bar_sfull + 8 * r, 1); mbar_init(bar_sempty + 8 * r, 9); }
+    for (int r = 0; r < RING; r++) { mbar_init(bar_sfull + 8 * r, 1); mbar_init(bar_sempty + 8 * r, TC_EPI_WARPS + 1); }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -93,7 +115,6 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int64_t tiles_per_batch = (int64_t)p.num_m_tiles * p.num_n_tiles;
 
   if (warp == 0) {
     // ------------------------------------------------ TMA producer ------------------------------------------------
@@ -109,10 +130,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         tile_ring[slot] = (int32_t)t;
         mbar_arrive(bar_sfull + 8 * slot);
         if (t < 0) break;
-        const int b = (int)(t / tiles_per_batch);
-        const int64_t rem = t - (int64_t)b * tiles_per_batch;
-        const int m0 = (int)(rem % p.num_m_tiles) * TC_BM;
-        const int n0 = (int)(rem / p.num_m_tiles) * BN;
+        int b, m0, n0;
+        tc_tile_coords(p, t, BN, &b, &m0, &n0);
         for (int kb = 0; kb < p.k_blocks; kb++) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, status, 1)) { ok = false; break; }
           const uint32_t full = bar_full + 8 * stage;
@@ -182,7 +201,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   } else {
     // ------------------------------------------------ epilogue ------------------------------------------------------
     const int quad = warp & 3;              // TMEM lanes [32*quad, 32*quad + 32)
-    const int half = (warp - 2) >> 2;       // columns [half * BN/2, (half + 1) * BN/2)
+    const int part = (warp - 2) >> 2;       // column chunks part, part + TC_COL_PARTS, ...
     bool ok = true;
     for (int64_t local = 0; ok; local++) {
       const int slot = (int)(local & (RING - 1));
@@ -193,10 +212,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       if (t < 0) break;
       const int acc = (int)(local & 1);
       const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
-      const int b = (int)(t / tiles_per_batch);
-      const int64_t rem = t - (int64_t)b * tiles_per_batch;
-      const int m0 = (int)(rem % p.num_m_tiles) * TC_BM;
-      const int n0 = (int)(rem / p.num_m_tiles) * BN;
+      int b, m0, n0;
+      tc_tile_coords(p, t, BN, &b, &m0, &n0);
       if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, status, 4)) { ok = false; break; }
       tc_fence_after();
       const int64_t row = (int64_t)m0 + quad * 32 + lane;
@@ -206,7 +223,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       if constexpr (ID != 0) {
         // specialised epilogue: straight-line code, four 8-wide vectors per 32-column TMEM load
 #pragma unroll 1
-        for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); c++) {
+        for (int c = part; c < BN / 32; c += TC_COL_PARTS) {
           uint32_t r[32];
           tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32), r);
           tc_wait_ld();
@@ -226,7 +243,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       } else {
         // interpreted epilogue: one inlined copy of the interpreter, fed 8 columns at a time
 #pragma unroll 1
-        for (int c = half * (BN / 16); c < (half + 1) * (BN / 16); c++) {
+        for (int c = part; c < BN / 8; c += TC_COL_PARTS) {
           uint32_t a0[8], out[8];
           tmem_ld_32x8(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 8), a0);
           tc_wait_ld();
@@ -276,7 +293,7 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcPar
     }
   }
   int64_t grid = p.num_tiles < kNumSms ? p.num_tiles : kNumSms;
-  kern<<<(unsigned)grid, 320, SM::TOTAL, stream>>>(tmA, tmB, p, epi, status);
+  kern<<<(unsigned)grid, TC_THREADS, SM::TOTAL, stream>>>(tmA, tmB, p, epi, status);
   count_launch();
   return (int)cudaGetLastError();
 }

@@ -195,7 +195,7 @@ extern "C" int b2x_reduce_splits(int64_t A, int64_t R, int64_t B) {
   // Enough independent pieces to fill 148 SMs without starving each piece of work.
   int64_t outputs = A * ((B + 255) / 256 > 1 ? (B + 255) / 256 : 1);
   if (outputs >= 296 || R < 4096) return 1;
-  int64_t s = (592 + outputs - 1) / outputs;
+  int64_t s = (1184 + outputs - 1) / outputs;
   if (s > R / 2048) s = R / 2048;
   if (s > 1024) s = 1024;
   return (int)(s < 1 ? 1 : s);

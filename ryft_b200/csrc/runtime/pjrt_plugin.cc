@@ -781,7 +781,7 @@ static PJRT_Error* build_core(PJRT_Client* client, const std::string& code, cons
     if (const char* g = getenv("B2X_GEMM")) po.allow_tensor_core = strcmp(g, "simt") != 0;
     if (const char* f = getenv("B2X_FUSED_ATTENTION")) po.allow_fused_attention = strcmp(f, "0") != 0;
     if (const char* f = getenv("B2X_EPILOGUE_FUSION")) po.allow_epilogue_fusion = strcmp(f, "0") != 0;
-    if (const char* f = getenv("B2X_FAST_MATH")) po.fast_math = strcmp(f, "0") != 0;
+    if (const char* f = getenv("B2X_PRECISE_MATH")) po.precise_math = strcmp(f, "0") != 0;
     if (co.use_spmd_partitioning && co.num_partitions > 1)
       return make_error(PJRT_Error_Code_UNIMPLEMENTED, "automatic SPMD partitioning is not supported; express the collectives in the program");
     core->plans.push_back(build_plan(*mod, po, 0));

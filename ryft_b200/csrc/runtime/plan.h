@@ -108,9 +108,8 @@ struct PlanOptions {
   bool allow_fused_attention = true;
   bool allow_epilogue_fusion = true;
   int precision = 0;               // Precision::{Default,High,Highest}
-  bool fast_math = false;          // B2X_FAST_MATH=1: hardware-approximate tanh/exp/log where the value is rounded to a
-                                   // 16-bit float before it is stored (about 2^-11 relative error, i.e. frequent one-ulp
-                                   // differences in bf16 results); off by default so that results match a CPU evaluation
+  bool precise_math = false;       // B2X_PRECISE_MATH=1: no hardware-approximate tanh/exp/log anywhere (by default they are used
+                                   // only for 16-bit float values that are just returned from the program)
 };
 
 // Lowers a verified module to a plan.  `replica` is only used to fold stablehlo.replica_id (plans are otherwise

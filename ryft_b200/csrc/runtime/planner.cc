@@ -176,6 +176,7 @@ class Planner {
     const Value* acc0_value = nullptr;  // value delivered through VM_SRC_ACC0 (GEMM result)
     struct Out { int node; int tensor; };
     std::vector<Out> outs;
+    std::vector<bool> out_terminal;     // per output: the value only leaves the program (no op of the program reads it)
     std::set<int> iota_root_dims;
     std::vector<B2xVmInstr> code;
     std::vector<int> free_temps;
@@ -328,6 +329,10 @@ void Planner::GroupBuilder::add_output(const Value* v, const BufRef& buf) {
   int n = node_for(v, ident);
   int t = add_tensor(buf, v->type.dtype, row_major_strides(root_dims));
   outs.push_back({n, t});
+  bool terminal = true;
+  for (auto u : v->users) if (u->kind != OpKind::RETURN) terminal = false;
+  out_terminal.resize(outs.size(), false);
+  out_terminal[outs.size() - 1] = terminal;
 }
 
 int Planner::GroupBuilder::alloc_temp() {
@@ -397,7 +402,10 @@ void Planner::GroupBuilder::gen(int ni) {
     }
   };
   auto un = [&](uint8_t vop, uint8_t aux) { gen(n.in[0]); emit(vop, nullptr, -1, aux, ci.cls, ci.rnd); };
-  const uint8_t fast = (P->opt_.fast_math && !n.precise) ? 1 : 0;
+  // Hardware-approximate tanh/exp/log (about 2^-11 relative error) only where the value is rounded to a 16-bit float
+  // and then only returned from the program: the approximation stays below that type's rounding step and nothing
+  // downstream can amplify it.  Everything that another op reads is computed accurately.
+  const uint8_t fast = (n.precise || P->opt_.precise_math) ? 0 : 1;
   switch (op.kind) {
     case OpKind::ADD: bin(VM_ADD, VM_ADD, 0, ci.cls, ci.rnd); break;
     case OpKind::MULTIPLY: bin(VM_MUL, VM_MUL, 0, ci.cls, ci.rnd); break;
@@ -525,12 +533,15 @@ VmBinding Planner::GroupBuilder::finish(int final_node) {
   for (auto& o : outs) nodes[o.node].uses++;
   if (final_node >= 0) nodes[final_node].uses++;
   for (auto& n : nodes) n.remaining = n.uses;
-  for (auto& o : outs) { DType t = nodes[o.node].dtype; if (t != DType::BF16 && t != DType::F16) nodes[o.node].precise = true; }
+  for (size_t oi = 0; oi < outs.size(); oi++) {
+    DType t = nodes[outs[oi].node].dtype;
+    const bool terminal = oi < out_terminal.size() && out_terminal[oi];
+    if ((t != DType::BF16 && t != DType::F16) || !terminal) nodes[outs[oi].node].precise = true;
+  }
   if (final_node >= 0) nodes[final_node].precise = true;
   for (int i = (int)nodes.size() - 1; i >= 0; i--) {
     GNode& n = nodes[i];
     if (!n.precise || n.k != GNode::OPN) continue;
-    if (n.dtype == DType::BF16 || n.dtype == DType::F16) continue;
     for (int j : n.in) nodes[j].precise = true;
   }
 
@@ -803,7 +814,7 @@ int reduce_splits_impl(int64_t A, int64_t R, int64_t B) {
   // Enough independent pieces to fill the machine (148 SMs x a few CTAs) without starving each piece of work.
   int64_t outputs = A * std::max<int64_t>(1, (B + 255) / 256);
   if (outputs >= 296 || R < 4096) return 1;
-  int64_t s = std::min<int64_t>((592 + outputs - 1) / outputs, R / 2048);
+  int64_t s = std::min<int64_t>((1184 + outputs - 1) / outputs, R / 2048);
   return (int)std::max<int64_t>(1, std::min<int64_t>(s, 1024));
 }
 
