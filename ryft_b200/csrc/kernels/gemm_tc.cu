@@ -90,6 +90,7 @@ extern "C" int b2x_launch_gemm_tc(const B2xGemmArgs* a, const B2xVmProgram* epil
   p.num_m_tiles = (int)((a->M + TC_BM - 1) / TC_BM);
   p.num_n_tiles = (int)((a->N + BN - 1) / BN);
   p.num_tiles = (int64_t)p.num_m_tiles * p.num_n_tiles * a->batch;
+  if (p.num_tiles >= (1ll << 31)) return (int)cudaErrorInvalidValue;
   p.k_blocks = (int)((a->K + BK - 1) / BK);
   {
     // A slab of a group ~ 32 MiB (a quarter of the 126 MB L2)

@@ -17,6 +17,7 @@
 // Bound: tensor pipe for K >= ~1024 (algorithmic FLOPs = 2*B*M*N*K); HBM (output bytes) for short K.
 // Every mbarrier wait is bounded (sm100.cuh); on expiry the CTA unwinds, frees TMEM and reports through `status`.
 #pragma once
+#include <type_traits>
 #include "../../../include/b2x_kernels.h"
 #include "common.cuh"
 #include "sm100.cuh"
@@ -46,16 +47,19 @@ constexpr int TC_COL_PARTS = TC_EPI_WARPS / 4;
 __device__ __forceinline__ void tc_tile_coords(const struct TcParams& p, int64_t t, int BN, int* b, int* m0, int* n0);
 
 __device__ __forceinline__ void tc_tile_coords(const TcParams& p, int64_t t, int BN, int* b, int* m0, int* n0) {
-  const int64_t per_batch = (int64_t)p.num_m_tiles * p.num_n_tiles;
-  const int bb = (int)(t / per_batch);
-  const int64_t r = t - (int64_t)bb * per_batch;
-  const int64_t per_group = (int64_t)p.group_m * p.num_n_tiles;
-  const int g = (int)(r / per_group);
-  const int64_t in = r - (int64_t)g * per_group;
-  const int gm = min(p.group_m, p.num_m_tiles - g * p.group_m);
-  *b = bb;
-  *m0 = (g * p.group_m + (int)(in % gm)) * TC_BM;
-  *n0 = (int)(in / gm) * BN;
+  // the launcher rejects problems with 2^31 or more tiles, so 32-bit divisions suffice
+  const uint32_t per_batch = (uint32_t)p.num_m_tiles * (uint32_t)p.num_n_tiles;
+  const uint32_t t32 = (uint32_t)t;
+  const uint32_t bb = t32 / per_batch;
+  const uint32_t r = t32 - bb * per_batch;
+  const uint32_t per_group = (uint32_t)p.group_m * (uint32_t)p.num_n_tiles;
+  const uint32_t g = r / per_group;
+  const uint32_t in = r - g * per_group;
+  const uint32_t gm = (uint32_t)min(p.group_m, p.num_m_tiles - (int)g * p.group_m);
+  const uint32_t nn = in / gm;
+  *b = (int)bb;
+  *m0 = (int)(g * (uint32_t)p.group_m + (in - nn * gm)) * TC_BM;
+  *n0 = (int)nn * BN;
 }
 
 template <int BN, int STAGES, bool TF32>
@@ -203,6 +207,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
     const int quad = warp & 3;              // TMEM lanes [32*quad, 32*quad + 32)
     const int part = (warp - 2) >> 2;       // column chunks part, part + TC_COL_PARTS, ...
     bool ok = true;
+    const VmRowPlan rplan = vm_row_plan(epi, (uint32_t)p.N);
     for (int64_t local = 0; ok; local++) {
       const int slot = (int)(local & (RING - 1));
       if (!mbar_wait(bar_sfull + 8 * slot, (uint32_t)((local / RING) & 1), abort_flag, status, 7)) { ok = false; break; }
@@ -219,38 +224,45 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       const int64_t row = (int64_t)m0 + quad * 32 + lane;
       const bool row_ok = row < p.M;
       VmRow vrow;
-      vm_row_begin(epi, (uint64_t)((int64_t)b * p.M + (row_ok ? row : 0)), (uint32_t)p.N, vrow);
-      if constexpr (ID != 0) {
-        // specialised epilogue: straight-line code, four 8-wide vectors per 32-column TMEM load
+      vm_row_begin(epi, rplan, (uint64_t)((int64_t)b * p.M + (row_ok ? row : 0)), (uint32_t)p.N, vrow);
+      // one decision per warp: tcgen05.ld below is warp-collective, so all lanes must take the same loop
+      const bool row_vec = __all_sync(0xffffffffu, vrow.vec);
+      auto chunks = [&](auto vec_tag) {
+        constexpr bool VEC = decltype(vec_tag)::value;
+        if constexpr (ID != 0) {
+          // specialised epilogue: straight-line code, four 8-wide vectors per 32-column TMEM load
 #pragma unroll 1
-        for (int c = part; c < BN / 32; c += TC_COL_PARTS) {
-          uint32_t r[32];
-          tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32), r);
-          tc_wait_ld();
-          if (row_ok) {
+          for (int c = part; c < BN / 32; c += TC_COL_PARTS) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32), r);
+            tc_wait_ld();
+            if (row_ok) {
 #pragma unroll
-            for (int v = 0; v < 4; v++) {
-              const int col = n0 + c * 32 + v * 8;
-              if (col < p.N) {
-                uint32_t a0[8], out[8];
+              for (int v = 0; v < 4; v++) {
+                const int col = n0 + c * 32 + v * 8;
+                if (col < p.N) {
+                  uint32_t a0[8], out[8];
 #pragma unroll
-                for (int j = 0; j < 8; j++) a0[j] = r[v * 8 + j];
-                vm_run_row<8, ID>(epi, vrow, (uint32_t)col, a0, out);
+                  for (int j = 0; j < 8; j++) a0[j] = r[v * 8 + j];
+                  if constexpr (VEC) vm_run_row_vec<8, ID>(epi, vrow, (uint32_t)col, a0, out);
+                  else vm_run_row<8, ID>(epi, vrow, (uint32_t)col, a0, out);
+                }
               }
             }
           }
-        }
-      } else {
-        // interpreted epilogue: one inlined copy of the interpreter, fed 8 columns at a time
+        } else {
+          // interpreted epilogue: one inlined copy of the interpreter, fed 8 columns at a time
 #pragma unroll 1
-        for (int c = part; c < BN / 8; c += TC_COL_PARTS) {
-          uint32_t a0[8], out[8];
-          tmem_ld_32x8(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 8), a0);
-          tc_wait_ld();
-          const int col = n0 + c * 8;
-          if (row_ok && col < p.N) vm_run_row<8, 0>(epi, vrow, (uint32_t)col, a0, out);
+          for (int c = part; c < BN / 8; c += TC_COL_PARTS) {
+            uint32_t a0[8], out[8];
+            tmem_ld_32x8(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 8), a0);
+            tc_wait_ld();
+            const int col = n0 + c * 8;
+            if (row_ok && col < p.N) vm_run_row<8, 0>(epi, vrow, (uint32_t)col, a0, out);
+          }
         }
-      }
+      };
+      if (ID != 0 && row_vec) chunks(std::true_type{}); else chunks(std::false_type{});
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);

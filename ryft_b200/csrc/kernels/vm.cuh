@@ -158,10 +158,18 @@ __device__ __forceinline__ void vm_put(void* ptr, const uint8_t elem, int64_t of
     }
     if (es == 2 && ((uintptr_t)base & (V * 2 - 1)) == 0) {
       uint32_t raw[(V + 1) / 2];
+      if (elem == EL_BF16 && V % 2 == 0) {
 #pragma unroll
-      for (int j = 0; j < (V + 1) / 2; j++) raw[j] = 0;
+        for (int j = 0; j < V / 2; j++) {
+          const __nv_bfloat162 h = __floats2bfloat162_rn(u2f(a[2 * j]), u2f(a[2 * j + 1]));
+          raw[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+      } else {
 #pragma unroll
-      for (int j = 0; j < V; j++) raw[j / 2] |= vm_encode(a[j], elem) << ((j & 1) * 16);
+        for (int j = 0; j < (V + 1) / 2; j++) raw[j] = 0;
+#pragma unroll
+        for (int j = 0; j < V; j++) raw[j / 2] |= vm_encode(a[j], elem) << ((j & 1) * 16);
+      }
       vm_st_bytes<V * 2>(base, raw);
       return;
     }
@@ -182,6 +190,71 @@ __device__ __forceinline__ void vm_put(void* ptr, const uint8_t elem, int64_t of
     if (es == 4) vm_st_bytes<4>(p, &raw); else if (es == 2) vm_st_bytes<2>(p, &raw); else vm_st_bytes<1>(p, &raw);
   }
 }
+
+// Row-contiguous variants for the row-wise driver: `p` is the byte address of the vector's first element, already
+// checked (once per row) to be 16-byte aligned whenever the tensor is contiguous along the row.
+template <int V>
+__device__ __forceinline__ void vm_fetch_row(const char* p, const uint8_t elem, const bool contiguous, uint32_t (&b)[V]) {
+  const int es = vm_elem_size(elem);
+  if (!contiguous) {
+    uint32_t raw;
+    if (es == 4) vm_ld_bytes<4>(p, &raw); else if (es == 2) vm_ld_bytes<2>(p, &raw); else vm_ld_bytes<1>(p, &raw);
+    raw = vm_decode(raw, elem);
+#pragma unroll
+    for (int j = 0; j < V; j++) b[j] = raw;
+  } else if (es == 4) {
+    vm_ld_bytes<V * 4>(p, b);
+  } else if (es == 2) {
+    uint32_t raw[(V + 1) / 2];
+    vm_ld_bytes<V * 2>(p, raw);
+#pragma unroll
+    for (int j = 0; j < V; j++) b[j] = vm_decode((raw[j / 2] >> ((j & 1) * 16)) & 0xffffu, elem);
+  } else {
+    uint32_t raw[(V + 3) / 4];
+    vm_ld_bytes<V>(p, raw);
+#pragma unroll
+    for (int j = 0; j < V; j++) b[j] = vm_decode((raw[j / 4] >> ((j & 3) * 8)) & 0xffu, elem);
+  }
+}
+template <int V>
+__device__ __forceinline__ void vm_put_row(char* p, const uint8_t elem, const uint32_t (&a)[V]) {
+  const int es = vm_elem_size(elem);
+  if (es == 4) {
+    uint32_t raw[V];
+#pragma unroll
+    for (int j = 0; j < V; j++) raw[j] = vm_encode(a[j], elem);
+    vm_st_bytes<V * 4>(p, raw);
+  } else if (es == 2) {
+    uint32_t raw[(V + 1) / 2];
+    if (elem == EL_BF16) {
+#pragma unroll
+      for (int j = 0; j < V / 2; j++) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(u2f(a[2 * j]), u2f(a[2 * j + 1]));
+        raw[j] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < (V + 1) / 2; j++) raw[j] = 0;
+#pragma unroll
+      for (int j = 0; j < V; j++) raw[j / 2] |= vm_encode(a[j], elem) << ((j & 1) * 16);
+    }
+    vm_st_bytes<V * 2>(p, raw);
+  } else {
+    uint32_t raw[(V + 3) / 4];
+#pragma unroll
+    for (int j = 0; j < (V + 3) / 4; j++) raw[j] = 0;
+#pragma unroll
+    for (int j = 0; j < V; j++) raw[j / 4] |= vm_encode(a[j], elem) << ((j & 3) * 8);
+    vm_st_bytes<V>(p, raw);
+  }
+}
+
+// Per-row addressing state of the row-wise driver's fast path: byte address of each tensor's element (row, column 0)
+// and the byte step per column (0 for tensors broadcast along the row).
+struct VmRowAddr {
+  const char* rp[B2X_VM_MAX_TENSORS];
+  int32_t cs[B2X_VM_MAX_TENSORS];
+};
 
 __device__ __forceinline__ float vm_fmax(float x, float y) { return (x != x) ? x : ((y != y) ? y : fmaxf(x, y)); }
 __device__ __forceinline__ float vm_fmin(float x, float y) { return (x != x) ? x : ((y != y) ? y : fminf(x, y)); }
@@ -339,9 +412,9 @@ __device__ __forceinline__ int64_t vm_offset(const B2xVmTensor& T, const int64_t
 // constants (specialised programs) the switches below fold away and only the selected op's code remains.
 // `off[t]` is tensor t's element offset for this vector without the part contributed by `col` along the innermost dim
 // (callers that have no separate column pass col = 0 and fold everything into off).
-template <int V>
+template <int V, bool RF = false>
 __device__ __forceinline__ void vm_exec(const B2xVmProgram& P, const int64_t (&coord)[B2X_VM_MAX_DIMS], const int nd,
-                                        const int64_t (&off)[B2X_VM_MAX_TENSORS], const int64_t col, const uint8_t op,
+                                        const int64_t (&off)[B2X_VM_MAX_TENSORS], const VmRowAddr& RA, const int64_t col, const uint8_t op,
                                         const uint8_t src_kind, const uint8_t src_idx, const uint8_t aux, const uint8_t tc, const uint8_t rnd,
                                         const uint32_t imm, const uint8_t elem, const uint32_t (&acc0)[V], VmState<V>& S) {
   // ---- operand fetch ----
@@ -351,11 +424,18 @@ __device__ __forceinline__ void vm_exec(const B2xVmProgram& P, const int64_t (&c
       break;
     case VM_SRC_TENSOR:
       if (op != VM_STORE) {
-        const B2xVmTensor& T = P.tensors[src_idx];
-        int64_t o = 0;
+        if constexpr (RF) {
+          const char* rp = nullptr; int32_t cs = 0;
 #pragma unroll
-        for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) if (t == src_idx) o = off[t];
-        vm_fetch<V>(T.ptr, elem, o + col * T.stride[nd - 1], T.stride[nd - 1], S.b);
+          for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) if (t == src_idx) { rp = RA.rp[t]; cs = RA.cs[t]; }
+          vm_fetch_row<V>(rp + (int64_t)((int32_t)col * cs), elem, cs != 0, S.b);
+        } else {
+          const B2xVmTensor& T = P.tensors[src_idx];
+          int64_t o = 0;
+#pragma unroll
+          for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) if (t == src_idx) o = off[t];
+          vm_fetch<V>(T.ptr, elem, o + col * T.stride[nd - 1], T.stride[nd - 1], S.b);
+        }
       }
       break;
     case VM_SRC_IMM:
@@ -393,6 +473,14 @@ __device__ __forceinline__ void vm_exec(const B2xVmProgram& P, const int64_t (&c
       narrow = false;
       break;
     case VM_STORE: {
+      if constexpr (RF) {
+        const char* rp = nullptr; int32_t cs = 0;
+#pragma unroll
+        for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) if (t == src_idx) { rp = RA.rp[t]; cs = RA.cs[t]; }
+        vm_put_row<V>(const_cast<char*>(rp) + (int64_t)((int32_t)col * cs), elem, S.acc);
+        narrow = false;
+        break;
+      }
       const B2xVmTensor& T = P.tensors[src_idx];
       int64_t o = 0;
 #pragma unroll
@@ -475,8 +563,20 @@ __device__ __forceinline__ void vm_exec(const B2xVmProgram& P, const int64_t (&c
     default: break;
   }
   if (narrow && rnd != VM_RN_NONE && !(op == VM_CVT && rnd == VM_RN_PRED)) {
+    if (rnd == VM_RN_BF16 && V % 2 == 0) {
+      // pairs through the packed conversion: it issues on the ALU pipes, the scalar one on the 16-lane XU pipe that
+      // tanh/exp also need
 #pragma unroll
-    for (int j = 0; j < V; j++) S.acc[j] = vm_narrow(S.acc[j], rnd);
+      for (int j = 0; j < V / 2; j++) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(u2f(S.acc[2 * j]), u2f(S.acc[2 * j + 1]));
+        const uint32_t raw = *reinterpret_cast<const uint32_t*>(&h);
+        S.acc[2 * j] = raw << 16;
+        S.acc[2 * j + 1] = raw & 0xffff0000u;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < V; j++) S.acc[j] = vm_narrow(S.acc[j], rnd);
+    }
   }
 }
 
@@ -492,20 +592,21 @@ template <int ID> struct VmStatic { static constexpr int n = 0; };
 #include "vm_static_table.h"
 namespace b2x {
 
-template <int V, int ID, int PC>
+template <int V, int ID, bool RF, int PC>
 __device__ __forceinline__ void vm_unroll(const B2xVmProgram& P, const int64_t (&coord)[B2X_VM_MAX_DIMS], const int nd,
-                                          const int64_t (&off)[B2X_VM_MAX_TENSORS], const int64_t col, const uint32_t (&acc0)[V], VmState<V>& S) {
+                                          const int64_t (&off)[B2X_VM_MAX_TENSORS], const VmRowAddr& RA, const int64_t col,
+                                          const uint32_t (&acc0)[V], VmState<V>& S) {
   if constexpr (PC < VmStatic<ID>::n) {
     constexpr VmSig G = VmStatic<ID>::at(PC);
     constexpr uint8_t elem = (G.src_kind == VM_SRC_TENSOR) ? VmStatic<ID>::elem(G.src_idx) : (uint8_t)0;
-    vm_exec<V>(P, coord, nd, off, col, G.op, G.src_kind, G.src_idx, G.aux, G.tc, G.rnd, P.code[PC].imm, elem, acc0, S);
-    vm_unroll<V, ID, PC + 1>(P, coord, nd, off, col, acc0, S);
+    vm_exec<V, RF>(P, coord, nd, off, RA, col, G.op, G.src_kind, G.src_idx, G.aux, G.tc, G.rnd, P.code[PC].imm, elem, acc0, S);
+    vm_unroll<V, ID, RF, PC + 1>(P, coord, nd, off, RA, col, acc0, S);
   }
 }
 
-template <int V, int ID>
+template <int V, int ID, bool RF = false>
 __device__ __forceinline__ void vm_run_core(const B2xVmProgram& P, const int64_t (&coord)[B2X_VM_MAX_DIMS], const int64_t (&off)[B2X_VM_MAX_TENSORS],
-                                            const int64_t col, const uint32_t (&acc0)[V], uint32_t (&acc)[V]) {
+                                            const VmRowAddr& RA, const int64_t col, const uint32_t (&acc0)[V], uint32_t (&acc)[V]) {
   const int nd = P.n_dims;
   VmState<V> S;
 #pragma unroll
@@ -515,10 +616,10 @@ __device__ __forceinline__ void vm_run_core(const B2xVmProgram& P, const int64_t
     for (int pc = 0; pc < P.n_instr; pc++) {
       const B2xVmInstr I = P.code[pc];
       const uint8_t elem = (I.src_kind == VM_SRC_TENSOR) ? P.tensors[I.src_idx].elem : (uint8_t)0;
-      vm_exec<V>(P, coord, nd, off, col, I.op, I.src_kind, I.src_idx, I.aux, I.tc, I.rnd, I.imm, elem, acc0, S);
+      vm_exec<V, RF>(P, coord, nd, off, RA, col, I.op, I.src_kind, I.src_idx, I.aux, I.tc, I.rnd, I.imm, elem, acc0, S);
     }
   } else {
-    vm_unroll<V, ID, 0>(P, coord, nd, off, col, acc0, S);
+    vm_unroll<V, ID, RF, 0>(P, coord, nd, off, RA, col, acc0, S);
   }
 #pragma unroll
   for (int j = 0; j < V; j++) acc[j] = S.acc[j];
@@ -533,7 +634,8 @@ __device__ __forceinline__ void vm_run(const B2xVmProgram& P, uint64_t lin, cons
   int64_t off[B2X_VM_MAX_TENSORS];
 #pragma unroll
   for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) off[t] = (t < P.n_tensors) ? vm_offset(P.tensors[t], coord, P.n_dims) : 0;
-  vm_run_core<V, ID>(P, coord, off, 0, acc0, acc);
+  VmRowAddr ra;      // unused outside the row-wise fast path
+  vm_run_core<V, ID>(P, coord, off, ra, 0, acc0, acc);
 }
 
 // Row-wise driver for kernels that walk a [rows, N] result one row at a time (GEMM epilogues): the coordinate
@@ -541,37 +643,91 @@ __device__ __forceinline__ void vm_run(const B2xVmProgram& P, uint64_t lin, cons
 struct VmRow {
   int64_t coord[B2X_VM_MAX_DIMS];
   int64_t off[B2X_VM_MAX_TENSORS];
+  VmRowAddr addr;
   bool fast;     // the innermost program dim is a whole number of rows
+  bool vec;      // fast, and every tensor is either broadcast along the row or contiguous with a 16-byte aligned row start
   uint64_t row;
   uint32_t N;
 };
-__device__ __forceinline__ void vm_row_begin(const B2xVmProgram& P, uint64_t row, uint32_t N, VmRow& R) {
+// What vm_row_begin needs that does not depend on the row: computed once per thread, outside the loop over tiles.
+struct VmRowPlan {
+  bool fast;      // the innermost program dim is a whole number of rows
+  bool small;     // row numbers and all outer dims fit in 32 bits: the row is decomposed with 32-bit divisions
+  uint64_t per;   // rows folded into the innermost program dim
+};
+__device__ __forceinline__ VmRowPlan vm_row_plan(const B2xVmProgram& P, uint32_t N) {
+  VmRowPlan L;
   const int nd = P.n_dims;
   const uint64_t inner = (uint64_t)P.dim[nd - 1];
+  L.fast = (inner % N) == 0;
+  L.per = L.fast ? inner / N : 1;
+  uint64_t rows = L.per;
+  bool small = true;
+#pragma unroll
+  for (int d = 0; d < B2X_VM_MAX_DIMS - 1; d++) {
+    if (d < nd - 1) { const uint64_t n = (uint64_t)P.dim[d]; small = small && n <= 0x7fffffffull && rows <= 0x7fffffffull; rows *= n; }
+  }
+  L.small = small && rows <= 0x7fffffffull;
+  return L;
+}
+__device__ __forceinline__ void vm_row_begin(const B2xVmProgram& P, const VmRowPlan& L, uint64_t row, uint32_t N, VmRow& R) {
+  const int nd = P.n_dims;
   R.row = row; R.N = N;
-  R.fast = (inner % N) == 0;
+  R.fast = L.fast;
+  R.vec = false;
 #pragma unroll
   for (int d = 0; d < B2X_VM_MAX_DIMS; d++) R.coord[d] = 0;
 #pragma unroll
-  for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) R.off[t] = 0;
+  for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) { R.off[t] = 0; R.addr.rp[t] = nullptr; R.addr.cs[t] = 0; }
   if (!R.fast) return;
-  const uint64_t per = inner / N;            // rows folded into the innermost program dim
-  uint64_t outer = row / per;
-  const int64_t inner_base = (int64_t)((row - outer * per) * N);
+  int64_t inner_base;
+  if (L.small) {
+    const uint32_t per = (uint32_t)L.per, r32 = (uint32_t)row;
+    uint32_t outer = r32 / per;
+    inner_base = (int64_t)((uint64_t)(r32 - outer * per) * N);
 #pragma unroll
-  for (int d = B2X_VM_MAX_DIMS - 2; d >= 1; d--) {
-    if (d < nd - 1) { const uint64_t n = (uint64_t)P.dim[d]; const uint64_t q = outer / n; R.coord[d] = (int64_t)(outer - q * n); outer = q; }
+    for (int d = B2X_VM_MAX_DIMS - 2; d >= 1; d--) {
+      if (d < nd - 1) { const uint32_t n = (uint32_t)P.dim[d]; const uint32_t q = outer / n; R.coord[d] = (int64_t)(outer - q * n); outer = q; }
+    }
+    if (nd >= 2) R.coord[0] = (int64_t)outer;
+  } else {
+    const uint64_t per = L.per;
+    uint64_t outer = row / per;
+    inner_base = (int64_t)((row - outer * per) * N);
+#pragma unroll
+    for (int d = B2X_VM_MAX_DIMS - 2; d >= 1; d--) {
+      if (d < nd - 1) { const uint64_t n = (uint64_t)P.dim[d]; const uint64_t q = outer / n; R.coord[d] = (int64_t)(outer - q * n); outer = q; }
+    }
+    if (nd >= 2) R.coord[0] = (int64_t)outer;
   }
-  if (nd >= 2) R.coord[0] = (int64_t)outer;
 #pragma unroll
   for (int d = 0; d < B2X_VM_MAX_DIMS; d++) if (d == nd - 1) R.coord[d] = inner_base;
 #pragma unroll
   for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) if (t < P.n_tensors) R.off[t] = vm_offset(P.tensors[t], R.coord, nd);
+  bool vec = true;
+#pragma unroll
+  for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) {
+    if (t < P.n_tensors) {
+      const int es = vm_elem_size(P.tensors[t].elem);
+      const int64_t istride = P.tensors[t].stride[nd - 1];
+      const char* rp = (const char*)P.tensors[t].ptr + R.off[t] * es;
+      R.addr.rp[t] = rp;
+      R.addr.cs[t] = (int32_t)istride * es;
+      vec = vec && es <= 4 && (istride == 0 || (istride == 1 && ((uintptr_t)rp & 15) == 0));
+    }
+  }
+  R.vec = vec && (uint64_t)N * 8 < 0x7fffffffull;
 }
 template <int V, int ID = 0>
 __device__ __forceinline__ void vm_run_row(const B2xVmProgram& P, const VmRow& R, uint32_t col, const uint32_t (&acc0)[V], uint32_t (&acc)[V]) {
-  if (R.fast) vm_run_core<V, ID>(P, R.coord, R.off, (int64_t)col, acc0, acc);
+  if (R.fast) vm_run_core<V, ID>(P, R.coord, R.off, R.addr, (int64_t)col, acc0, acc);
   else vm_run<V, ID>(P, R.row * R.N + col, acc0, acc);
+}
+// Same, for rows with R.vec set: tensor operands are addressed through R.addr with no per-vector stride or alignment
+// decisions.  `col` must be a multiple of 8 elements.
+template <int V, int ID = 0>
+__device__ __forceinline__ void vm_run_row_vec(const B2xVmProgram& P, const VmRow& R, uint32_t col, const uint32_t (&acc0)[V], uint32_t (&acc)[V]) {
+  vm_run_core<V, ID, true>(P, R.coord, R.off, R.addr, (int64_t)col, acc0, acc);
 }
 
 // Signature hash of a program (structure only: ops, operand kinds, classes, rounding, tensor element types).

@@ -554,6 +554,17 @@ VmBinding Planner::GroupBuilder::finish(int final_node) {
     code.push_back(I);
   }
   if (final_node >= 0) gen(final_node);
+  // A store into a 16-bit float tensor rounds to nearest-even itself: the rounding step of the instruction before it is
+  // redundant when the accumulator is overwritten right after the store.
+  for (size_t i = 1; i < code.size(); i++) {
+    if (code[i].op != VM_STORE) continue;
+    const bool acc_dead = (i + 1 == code.size() && final_node < 0) || (i + 1 < code.size() && code[i + 1].op == VM_LOAD);
+    if (!acc_dead) continue;
+    B2xVmInstr& prev = code[i - 1];
+    if (prev.op == VM_STORE || prev.op == VM_SAVE || prev.op == VM_SELECT || prev.op == VM_RSELECT) continue;
+    const DType elem = tensors[code[i].src_idx].dt;
+    if ((elem == DType::BF16 && prev.rnd == VM_RN_BF16) || (elem == DType::F16 && prev.rnd == VM_RN_F16)) prev.rnd = VM_RN_NONE;
+  }
   if ((int)code.size() > B2X_VM_MAX_INSTR)
     unimplemented("an elementwise fusion group compiles to " + std::to_string(code.size()) + " instructions; the limit is " + std::to_string(B2X_VM_MAX_INSTR));
 
