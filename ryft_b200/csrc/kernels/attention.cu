@@ -6,17 +6,20 @@
 // comparison.rs:136-164, control_flow.rs:263) and replaces it with this kernel; no score tensor touches HBM.
 //
 // One CTA per (batch*head, 128-row query tile); the tiles of one head are adjacent in the grid (K/V reuse in L2),
-// longest causal prefix first.  192 threads:
-//   warp 0      TMA producer: Q once, then K and V blocks of 128 keys into a 2-deep ring (per-CTA loads, no multicast)
-//   warp 1      MMA issuer: S_j = Q K_j^T into one of two TMEM score buffers, O += P_j V_j into a TMEM accumulator;
-//               S_{j+1} is issued before P_j is consumed so the tensor pipe works while the softmax warps run
-//   warps 2-5   online softmax, one query row per thread: row max and exp2 from TMEM (two passes over 32-column
-//               chunks), P_j written as bf16 into 128-byte-swizzled shared memory for the second MMA; the output
-//               accumulator is rescaled only when the running max grew by more than 2^8 (exact: the same stale max is
-//               used for the row sum), and is normalised by the row sum at the end
+// longest causal prefix first.  The key blocks of a tile (128 keys each) are dealt alternately to two independent
+// softmax streams: stream s owns blocks j = s, s + 2, ..., its own score buffer, probability buffer, K/V stage and
+// output accumulator, and keeps its own running (max, sum).  While one stream exponentiates, the tensor pipe works
+// for the other; the two partial results are merged once, at the end.  320 threads:
+//   warp 0      TMA producer: Q once, then K_j and V_j into stage j & 1 as soon as that stage's previous K (after its
+//               Q K^T retired) or V (after its P V retired) is free; per-CTA loads, no multicast
+//   warp 1      MMA issuer: S_s = Q K_j^T into TMEM score buffer s, O_s += P_s V_j into TMEM accumulator s
+//   warps 2-5   softmax stream 0, warps 6-9 stream 1; one query row per thread: the 128 scores of the row are read from
+//               TMEM once and stay in registers (row max, exp2, row sum), P goes as bf16 into 128-byte-swizzled
+//               shared memory for the second MMA; the accumulator is rescaled only when the running max grew by more
+//               than 2^8 (exact: the same stale max is used for the row sum)
 // Causal tiles above the diagonal are skipped; the diagonal block and ragged key tails are masked in registers.
-// Bound: tensor pipe / MUFU (exp2); algorithmic FLOPs = 4 * BH * D * (number of unmasked score elements).
-// Every mbarrier wait is bounded; on expiry the CTA unwinds, frees TMEM and reports through `status`.
+// Bound: tensor pipe / MUFU (exp2), about equal for D = 128; algorithmic FLOPs = 4 * BH * D * (unmasked scores).
+// Every wait is bounded; on expiry the CTA unwinds, frees TMEM and reports through `status`.
 #include "../../../include/b2x_kernels.h"
 #include "common.cuh"
 #include "sm100.cuh"
@@ -43,10 +46,10 @@ struct AttnSmem {
   static constexpr int KV_BYTES = AT_N * D * 2;
   static constexpr int P_BYTES = AT_M * AT_N * 2;
   static constexpr int Q_OFF = 0;
-  static constexpr int K_OFF = Q_OFF + Q_BYTES;            // 2 stages
+  static constexpr int K_OFF = Q_OFF + Q_BYTES;            // 2 stages (one per stream)
   static constexpr int V_OFF = K_OFF + 2 * KV_BYTES;       // 2 stages
-  static constexpr int P_OFF = V_OFF + 2 * KV_BYTES;
-  static constexpr int BAR_OFF = P_OFF + P_BYTES;
+  static constexpr int P_OFF = V_OFF + 2 * KV_BYTES;       // 2 buffers
+  static constexpr int BAR_OFF = P_OFF + 2 * P_BYTES;      // 19 barriers, TMEM slot, abort flag
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
@@ -57,25 +60,29 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
             const __grid_constant__ AttnParams p, int32_t* status) {
   using namespace sm100;
   using SM = AttnSmem<D>;
   constexpr int DC = D / 64;                 // 64-wide (128-byte) chunks of the head dimension
-  constexpr uint32_t TMEM_COLS = 512;        // S0 [0,128), S1 [128,256), O [256, 256 + D)
+  constexpr uint32_t TMEM_COLS = 512;        // S0 [0,128), S1 [128,256), O0 [256, 256 + D), O1 [256 + D, 256 + 2 D)
   constexpr uint32_t CHUNK_BYTES = 128 * 128;  // one [128 rows x 128 bytes] swizzled sub-tile
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
   uint64_t* bars = (uint64_t*)(smem + SM::BAR_OFF);
-  // barriers: q_full, k_full[2], v_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, pv_done, drain
+  // barriers (each [2] is indexed by stream): q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2],
+  // s_empty[2], p_full[2], pv_done[2], merge, drain
   const uint32_t b0 = smem_u32(bars);
-  const uint32_t bar_q = b0, bar_kf = b0 + 8, bar_vf = b0 + 24, bar_kve = b0 + 40, bar_sf = b0 + 56, bar_se = b0 + 72, bar_pf = b0 + 88,
-                 bar_pv = b0 + 96, bar_drain = b0 + 104;
-  uint32_t* tmem_slot = (uint32_t*)(bars + 14);
+  const uint32_t bar_q = b0, bar_kf = b0 + 8, bar_ke = b0 + 24, bar_vf = b0 + 40, bar_ve = b0 + 56, bar_sf = b0 + 72, bar_se = b0 + 88,
+                 bar_pf = b0 + 104, bar_pv = b0 + 120, bar_merge = b0 + 136, bar_drain = b0 + 144;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 19);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  // per stream and row (max * scale_log2, sum) for the final merge; stream s keeps them at the start of its own
+  // probability buffer, which is idle once its last P V product has retired
+  auto merge_slot = [&](int s, int row) -> float2* { return (float2*)(smem + SM::P_OFF + s * SM::P_BYTES) + row; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // consecutive CTAs are the query tiles of one (batch, head), longest causal prefix first: they run together and find
@@ -90,10 +97,10 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
   if (threadIdx.x == 0) {
     mbar_init(bar_q, 1);
     for (int s = 0; s < 2; s++) {
-      mbar_init(bar_kf + 8 * s, 1); mbar_init(bar_vf + 8 * s, 1); mbar_init(bar_kve + 8 * s, 1);
-      mbar_init(bar_sf + 8 * s, 1); mbar_init(bar_se + 8 * s, 4);
+      mbar_init(bar_kf + 8 * s, 1); mbar_init(bar_ke + 8 * s, 1); mbar_init(bar_vf + 8 * s, 1); mbar_init(bar_ve + 8 * s, 1);
+      mbar_init(bar_sf + 8 * s, 1); mbar_init(bar_se + 8 * s, 4); mbar_init(bar_pf + 8 * s, 4); mbar_init(bar_pv + 8 * s, 1);
     }
-    mbar_init(bar_pf, 4); mbar_init(bar_pv, 1); mbar_init(bar_drain, 1);
+    mbar_init(bar_merge, 8); mbar_init(bar_drain, 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
@@ -103,7 +110,6 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_o = tmem_base + 256;
 
   if (warp == 0) {
     // ---------------------------------------------- TMA producer --------------------------------------------------
@@ -111,18 +117,36 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       mbar_expect_tx(bar_q, SM::Q_BYTES);
 #pragma unroll
       for (int c = 0; c < DC; c++) tma_load_3d(sbase + SM::Q_OFF + c * CHUNK_BYTES, &tmQ, bar_q, c * 64, q0, bh);
+      // K_j and V_j go into stage j & 1; each is issued as soon as its stage is free, whichever comes first
+      int jk = 0, jv = 0;
+      uint32_t idle = 0;
       bool ok = true;
-      for (int j = 0; j < nblk && ok; j++) {
-        const int st = j & 1;
-        if (!mbar_wait(bar_kve + 8 * st, (uint32_t)(((j >> 1) & 1) ^ 1), abort_flag, status, 11)) { ok = false; break; }
-        mbar_expect_tx(bar_kf + 8 * st, SM::KV_BYTES);
+      while (jk < nblk || jv < nblk) {
+        bool progress = false;
+        if (jk < nblk) {
+          const int s = jk & 1, it = jk >> 1;
+          if (it == 0 || mbar_try_wait(bar_ke + 8 * s, (uint32_t)((it - 1) & 1))) {
+            mbar_expect_tx(bar_kf + 8 * s, SM::KV_BYTES);
 #pragma unroll
-        for (int c = 0; c < DC; c++) tma_load_3d(sbase + SM::K_OFF + st * SM::KV_BYTES + c * CHUNK_BYTES, &tmK, bar_kf + 8 * st, c * 64, j * AT_N, bh);
-        mbar_expect_tx(bar_vf + 8 * st, SM::KV_BYTES);
+            for (int c = 0; c < DC; c++) tma_load_3d(sbase + SM::K_OFF + s * SM::KV_BYTES + c * CHUNK_BYTES, &tmK, bar_kf + 8 * s, c * 64, jk * AT_N, bh);
+            jk++; progress = true;
+          }
+        }
+        if (jv < nblk) {
+          const int s = jv & 1, it = jv >> 1;
+          if (it == 0 || mbar_try_wait(bar_ve + 8 * s, (uint32_t)((it - 1) & 1))) {
+            mbar_expect_tx(bar_vf + 8 * s, SM::KV_BYTES);
 #pragma unroll
-        for (int c = 0; c < DC; c++) tma_load_3d(sbase + SM::V_OFF + st * SM::KV_BYTES + c * CHUNK_BYTES, &tmV, bar_vf + 8 * st, c * 64, j * AT_N, bh);
+            for (int c = 0; c < DC; c++) tma_load_3d(sbase + SM::V_OFF + s * SM::KV_BYTES + c * CHUNK_BYTES, &tmV, bar_vf + 8 * s, c * 64, jv * AT_N, bh);
+            jv++; progress = true;
+          }
+        }
+        if (progress) { idle = 0; continue; }
+        if (++idle > (1u << 22)) { *abort_flag = 1; atomicCAS(status, 0, 11); ok = false; break; }
+        if (idle > 16) { if (*abort_flag) { ok = false; break; } __nanosleep(idle > 4096 ? 256 : 32); }
       }
       if (!ok) {
+        // let copies already in flight land before the CTA's shared memory goes away
         for (int s = 0; s < 2; s++)
           for (uint32_t i = 0; i < (1u << 16); i++) {
             if ((mbar_try_wait(bar_kf + 8 * s, 0) || mbar_try_wait(bar_kf + 8 * s, 1)) && (mbar_try_wait(bar_vf + 8 * s, 0) || mbar_try_wait(bar_vf + 8 * s, 1))) break;
@@ -135,114 +159,124 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     if (lane == 0) {
       bool ok = mbar_wait(bar_q, 0, abort_flag, status, 12);
       auto issue_qk = [&](int j) -> bool {
-        const int st = j & 1, sb = j & 1;
-        if (!mbar_wait(bar_kf + 8 * st, (uint32_t)((j >> 1) & 1), abort_flag, status, 13)) return false;
-        if (!mbar_wait(bar_se + 8 * sb, (uint32_t)(((j >> 1) & 1) ^ 1), abort_flag, status, 14)) return false;
+        const int s = j & 1, it = j >> 1;
+        if (!mbar_wait(bar_kf + 8 * s, (uint32_t)(it & 1), abort_flag, status, 13)) return false;
         tc_fence_after();
-        const uint32_t qa = sbase + SM::Q_OFF, ka = sbase + SM::K_OFF + st * SM::KV_BYTES;
+        const uint32_t qa = sbase + SM::Q_OFF, ka = sbase + SM::K_OFF + s * SM::KV_BYTES;
 #pragma unroll
         for (int k = 0; k < D / 16; k++) {
           const uint32_t off = (uint32_t)(k >> 2) * CHUNK_BYTES + (uint32_t)(k & 3) * 32;
-          umma_ss<false>(tmem_base + (uint32_t)(sb * 128), make_smem_desc(qa + off, 16, 1024), make_smem_desc(ka + off, 16, 1024), p.idesc_qk, k > 0 ? 1u : 0u);
+          umma_ss<false>(tmem_base + (uint32_t)(s * 128), make_smem_desc(qa + off, 16, 1024), make_smem_desc(ka + off, 16, 1024), p.idesc_qk, k > 0 ? 1u : 0u);
         }
-        tc_commit(bar_sf + 8 * sb);
+        tc_commit(bar_sf + 8 * s);    // scores ready for stream s
+        tc_commit(bar_ke + 8 * s);    // K stage free
         return true;
       };
       if (ok && nblk > 0) ok = issue_qk(0);
+      if (ok && nblk > 1) ok = issue_qk(1);
       for (int j = 0; j < nblk && ok; j++) {
-        if (j + 1 < nblk) { if (!issue_qk(j + 1)) { ok = false; break; } }
-        const int st = j & 1;
-        if (!mbar_wait(bar_vf + 8 * st, (uint32_t)((j >> 1) & 1), abort_flag, status, 15)) { ok = false; break; }
-        if (!mbar_wait(bar_pf, (uint32_t)(j & 1), abort_flag, status, 16)) { ok = false; break; }
+        const int s = j & 1, it = j >> 1;
+        // the stream has copied block j's scores into registers: its score buffer can take block j + 2
+        if (j + 2 < nblk) {
+          if (!mbar_wait(bar_se + 8 * s, (uint32_t)(it & 1), abort_flag, status, 14)) { ok = false; break; }
+          if (!issue_qk(j + 2)) { ok = false; break; }
+        }
+        if (!mbar_wait(bar_vf + 8 * s, (uint32_t)(it & 1), abort_flag, status, 15)) { ok = false; break; }
+        if (!mbar_wait(bar_pf + 8 * s, (uint32_t)(it & 1), abort_flag, status, 16)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t pa = sbase + SM::P_OFF, va = sbase + SM::V_OFF + st * SM::KV_BYTES;
+        const uint32_t pa = sbase + SM::P_OFF + s * SM::P_BYTES, va = sbase + SM::V_OFF + s * SM::KV_BYTES;
+        const uint32_t o_tmem = tmem_base + 256u + (uint32_t)(s * D);
 #pragma unroll
         for (int k = 0; k < AT_N / 16; k++) {
           // A = P (K-major: keys contiguous); B = V (MN-major: head-dim chunks of 64 are CHUNK_BYTES apart, 8 key rows per 1 KiB)
           const uint32_t aoff = (uint32_t)(k >> 2) * CHUNK_BYTES + (uint32_t)(k & 3) * 32;
-          umma_ss<false>(tmem_o, make_smem_desc(pa + aoff, 16, 1024), make_smem_desc(va + (uint32_t)k * 2048, CHUNK_BYTES, 1024), p.idesc_pv,
-                         (j > 0 || k > 0) ? 1u : 0u);
+          umma_ss<false>(o_tmem, make_smem_desc(pa + aoff, 16, 1024), make_smem_desc(va + (uint32_t)k * 2048, CHUNK_BYTES, 1024), p.idesc_pv,
+                         (it > 0 || k > 0) ? 1u : 0u);
         }
-        tc_commit(bar_kve + 8 * st);
-        tc_commit(bar_pv);
+        tc_commit(bar_ve + 8 * s);    // V stage free
+        tc_commit(bar_pv + 8 * s);    // accumulator s and probability buffer s may be touched again
       }
       tc_commit(bar_drain);
       mbar_wait(bar_drain, 0, abort_flag, nullptr, 0);
     }
   } else {
     // ---------------------------------------------- softmax ---------------------------------------------------------
+    const int s = (warp - 2) >> 2;                // stream
     const int quad = warp & 3;
     const int row = quad * 32 + lane;             // row of the tile == TMEM lane
     const int64_t qrow = (int64_t)q0 + row;
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    const uint32_t s_addr = tmem_base + lane_addr + (uint32_t)(s * 128);
+    const uint32_t o_addr = tmem_base + lane_addr + 256u + (uint32_t)(s * D);
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
-    uint8_t* prow = smem + SM::P_OFF + row * 128;
-    for (int j = 0; j < nblk && ok; j++) {
-      const int sb = j & 1;
-      if (!mbar_wait(bar_sf + 8 * sb, (uint32_t)((j >> 1) & 1), abort_flag, status, 17)) { ok = false; break; }
+    uint8_t* prow = smem + SM::P_OFF + s * SM::P_BYTES + row * 128;
+    const int n_mine = nblk > s ? (nblk - s + 1) / 2 : 0;    // blocks s, s + 2, ...
+    for (int it = 0; it < n_mine && ok; it++) {
+      const int j = 2 * it + s;
+      if (!mbar_wait(bar_sf + 8 * s, (uint32_t)(it & 1), abort_flag, status, 17)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t s_addr = tmem_base + lane_addr + (uint32_t)(sb * 128);
-      // columns of this block that this row may attend to: [0, limit]
+      uint32_t r[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; c++) tmem_ld_32x32(s_addr + (uint32_t)(c * 32), r[c]);
+      tc_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_se + 8 * s);
+      // columns of this block that this row may attend to: [0, lim]
       int64_t lim = p.Sk - 1 - (int64_t)j * AT_N;
       if (p.causal) { const int64_t c = qrow - (int64_t)j * AT_N; lim = c < lim ? c : lim; }
       const bool need_mask = __any_sync(0xffffffffu, lim < AT_N - 1);
-      // pass 1: row max
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < AT_N / 32; c++) {
-        uint32_t r[32];
-        tmem_ld_32x32(s_addr + (uint32_t)(c * 32), r);
-        tc_wait_ld();
-        if (need_mask) {
+      if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; i++) { float v = __uint_as_float(r[i]); mx = (c * 32 + i <= lim) ? fmaxf(mx, v) : mx; }
-        } else {
+        for (int c = 0; c < 4; c++)
 #pragma unroll
-          for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(r[i]));
-        }
+          for (int i = 0; i < 32; i++) { if (c * 32 + i > lim) r[c][i] = 0xff800000u; mx = fmaxf(mx, __uint_as_float(r[c][i])); }
+      } else {
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < 4; c++)
+#pragma unroll
+          for (int i = 0; i < 32; i++) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[c][i]));
+        mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       }
       float alpha = 1.f;
       bool rescale = false;
-      if (j == 0) m_used = mx;
+      if (it == 0) m_used = mx;
       else if ((mx - m_used) * p.scale_log2 > 8.0f) { alpha = fast_exp2((m_used - mx) * p.scale_log2); l *= alpha; m_used = mx; rescale = true; }
-      // the previous P V product must have retired before O is touched or P is overwritten
-      if (j > 0) {
-        if (!mbar_wait(bar_pv, (uint32_t)((j - 1) & 1), abort_flag, status, 18)) { ok = false; break; }
+      // this stream's previous P V product must have retired before its accumulator is touched or its P overwritten
+      if (it > 0) {
+        if (!mbar_wait(bar_pv + 8 * s, (uint32_t)((it - 1) & 1), abort_flag, status, 18)) { ok = false; break; }
         tc_fence_after();
         if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
           for (int c = 0; c < D / 32; c++) {
-            uint32_t r[32];
-            tmem_ld_32x32(tmem_o + lane_addr + (uint32_t)(c * 32), r);
+            uint32_t o[32];
+            tmem_ld_32x32(o_addr + (uint32_t)(c * 32), o);
             tc_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            // 32 columns back in two 16-column stores
+            for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
             uint32_t lo[16], hi[16];
 #pragma unroll
-            for (int i = 0; i < 16; i++) { lo[i] = r[i]; hi[i] = r[16 + i]; }
-            tmem_st_32x16(tmem_o + lane_addr + (uint32_t)(c * 32), lo);
-            tmem_st_32x16(tmem_o + lane_addr + (uint32_t)(c * 32 + 16), hi);
+            for (int i = 0; i < 16; i++) { lo[i] = o[i]; hi[i] = o[16 + i]; }
+            tmem_st_32x16(o_addr + (uint32_t)(c * 32), lo);
+            tmem_st_32x16(o_addr + (uint32_t)(c * 32 + 16), hi);
           }
           tc_wait_st();
         }
       }
-      // pass 2: p = exp2(s * scale_log2 - m * scale_log2), row sum, bf16 P into swizzled shared memory
-      const float mneg = -m_used * p.scale_log2;
-      float psum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < AT_N / 32; c++) {
-        uint32_t r[32];
-        tmem_ld_32x32(s_addr + (uint32_t)(c * 32), r);
-        tc_wait_ld();
-        float pv[32];
+      // p = exp2(s * scale_log2 - m * scale_log2) (a masked score is -inf and gives exactly 0), row sum, bf16 P into
+      // swizzled shared memory; a fully masked row (m = -inf) gives 0 everywhere
+      const float mneg = (m_used == -INFINITY) ? 0.f : -m_used * p.scale_log2;
+      float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
 #pragma unroll
         for (int i = 0; i < 32; i++) {
-          float e = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, mneg));
-          if (need_mask) e = (c * 32 + i <= lim) ? e : 0.f;
-          pv[i] = e;
-          psum += e;
+          const float e = fast_exp2(fmaf(__uint_as_float(r[c][i]), p.scale_log2, mneg));
+          r[c][i] = __float_as_uint(e);
+          ps4[i & 3] += e;
         }
         // 32 keys = 64 bytes = four 16-byte pieces of this row; piece index within the 128-byte line is XOR-swizzled
 #pragma unroll
@@ -250,7 +284,7 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
           uint32_t w[4];
 #pragma unroll
           for (int h = 0; h < 4; h++) {
-            __nv_bfloat162 t = __floats2bfloat162_rn(pv[q * 8 + 2 * h], pv[q * 8 + 2 * h + 1]);
+            __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(r[c][q * 8 + 2 * h]), __uint_as_float(r[c][q * 8 + 2 * h + 1]));
             w[h] = *reinterpret_cast<uint32_t*>(&t);
           }
           const int piece = c * 4 + q;                 // 0..15 over the 128 keys
@@ -258,26 +292,46 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
           *reinterpret_cast<uint4*>(prow + sub * CHUNK_BYTES + ((in ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
-      l += psum;
-      // S buffer free for the block after next; P visible to the tensor-core (async) proxy
+      l += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
+      // P visible to the tensor-core (async) proxy
       tc_fence_before();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      if (lane == 0) { mbar_arrive(bar_se + 8 * sb); mbar_arrive(bar_pf); }
+      if (lane == 0) mbar_arrive(bar_pf + 8 * s);
     }
-    // ---- epilogue: O / l -> bf16 -> global ----
-    if (ok && nblk > 0) ok = mbar_wait(bar_pv, (uint32_t)((nblk - 1) & 1), abort_flag, status, 19);
+    // ---- merge the two streams and write O / l as bf16 ----
+    if (ok && n_mine > 0) ok = mbar_wait(bar_pv + 8 * s, (uint32_t)((n_mine - 1) & 1), abort_flag, status, 19);
+    *merge_slot(s, row) = make_float2((n_mine > 0 && m_used != -INFINITY) ? m_used * p.scale_log2 : -INFINITY, n_mine > 0 ? l : 0.f);
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_merge);
+    if (ok) ok = mbar_wait(bar_merge, 0, abort_flag, status, 20);
     if (ok) {
       tc_fence_after();
-      const float inv = (nblk > 0 && l > 0.f) ? __fdividef(1.0f, l) : 0.f;
+      const float2 mine = *merge_slot(s, row), other = *merge_slot(s ^ 1, row);
+      const float mm = fmaxf(mine.x, other.x);
+      const float a_mine = (mine.x == -INFINITY) ? 0.f : fast_exp2(mine.x - mm);
+      const float a_other = (other.x == -INFINITY) ? 0.f : fast_exp2(other.x - mm);
+      const float lsum = mine.y * a_mine + other.y * a_other;
+      const float inv = lsum > 0.f ? __fdividef(1.0f, lsum) : 0.f;
+      const float w_mine = a_mine * inv, w_other = a_other * inv;
+      const bool have_mine = n_mine > 0, have_other = (nblk > (s ^ 1));
+      const uint32_t o_mine = o_addr, o_other = tmem_base + lane_addr + 256u + (uint32_t)((s ^ 1) * D);
       __nv_bfloat16* orow = p.out + ((int64_t)bh * p.Sq + qrow) * D;
+      // stream s writes head-dim columns [s * D/2, (s + 1) * D/2)
 #pragma unroll 1
-      for (int c = 0; c < D / 32; c++) {
-        uint32_t r[32];
-        if (nblk > 0) { tmem_ld_32x32(tmem_o + lane_addr + (uint32_t)(c * 32), r); tc_wait_ld(); }
-        else {
+      for (int c = s * (D / 64); c < (s + 1) * (D / 64); c++) {
+        uint32_t x[32], y[32];
+        if (have_mine) tmem_ld_32x32(o_mine + (uint32_t)(c * 32), x);
+        if (have_other) tmem_ld_32x32(o_other + (uint32_t)(c * 32), y);
+        tc_wait_ld();
+        float f[32];
 #pragma unroll
-          for (int i = 0; i < 32; i++) r[i] = 0;
+        for (int i = 0; i < 32; i++) {
+          float v = 0.f;
+          if (have_mine) v = __uint_as_float(x[i]) * w_mine;
+          if (have_other) v = fmaf(__uint_as_float(y[i]), w_other, v);
+          f[i] = v;
         }
         if (qrow < p.Sq) {
 #pragma unroll
@@ -285,7 +339,7 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             uint32_t w[4];
 #pragma unroll
             for (int h = 0; h < 4; h++) {
-              __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(r[q * 8 + 2 * h]) * inv, __uint_as_float(r[q * 8 + 2 * h + 1]) * inv);
+              __nv_bfloat162 t = __floats2bfloat162_rn(f[q * 8 + 2 * h], f[q * 8 + 2 * h + 1]);
               w[h] = *reinterpret_cast<uint32_t*>(&t);
             }
             *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -330,7 +384,7 @@ static int launch_attention(const B2xAttentionArgs* a, int32_t* status, cudaStre
   const int64_t grid = (int64_t)p.n_q_tiles * a->BH;
   if (grid <= 0) return 0;
   if (grid > 0x7fffffff) return (int)cudaErrorInvalidValue;
-  kern<<<(unsigned)grid, 192, SM::TOTAL, stream>>>(tmQ, tmK, tmV, p, status);
+  kern<<<(unsigned)grid, 320, SM::TOTAL, stream>>>(tmQ, tmK, tmV, p, status);
   count_launch();
   return (int)cudaGetLastError();
 }

@@ -31,6 +31,7 @@ struct TcParams {
   int32_t num_m_tiles, num_n_tiles;
   int64_t num_tiles;
   int32_t k_blocks;
+  int32_t transposed;  // multi-store epilogues on short-K problems go through shared memory (see tc_transposed_epilogue)
   int32_t group_m;     // m-tiles per raster group: a group's A slab stays in L2 while its n-tiles stream by
   uint32_t idesc;
   int32_t* sched;      // [0] next tile to hand out, [1] CTAs that have finished (the last one resets both)
@@ -62,13 +63,28 @@ __device__ __forceinline__ void tc_tile_coords(const TcParams& p, int64_t t, int
   *n0 = (int)nn * BN;
 }
 
-template <int BN, int STAGES, bool TF32>
+// A warp-wide store with one row per lane keeps the load/store unit busy for 32 cycles (one per cache line touched);
+// with four lanes per row it is 8, but the round trip through shared memory costs about as much as one such store.
+// Measured on the MLP step: a two-store epilogue behind a K = 4096 GEMM gains 11 %; single-store programs, and epilogues
+// behind a K = 16384 GEMM (which have four times as long per tile), lose a few per cent to the extra work.  So the
+// transposed path is compiled for programs with two or more stores and taken when K <= 8192.
+template <int ID>
+__host__ __device__ constexpr bool tc_transposed_epilogue() {
+  if constexpr (ID == 0) return false;
+  else return vm_static_stores<ID>() >= 2;
+}
+
+template <int BN, int STAGES, bool TF32, bool STAGING>
 struct TcSmem {
   static constexpr int A_BYTES = TC_BM * 128;   // 128 rows (or k-lines x chunks) of 128 bytes
   static constexpr int B_BYTES = BN * 128;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-  static constexpr int TOTAL = BAR_OFFSET + 384 + 1024;  // barriers, tile ring + slack for 1024-byte alignment
+  static constexpr int STAGING_OFFSET = BAR_OFFSET + 384;                 // barriers and the tile ring come first
+  // per epilogue warp 16 rows of 32 f32 columns; only kernels that contain the transposed epilogue pay for it (shared
+  // memory a kernel does not ask for stays available to the SM as L1 cache)
+  static constexpr int STAGING_BYTES = STAGING ? TC_EPI_WARPS * 2048 : 0;
+  static constexpr int TOTAL = STAGING_OFFSET + STAGING_BYTES + 1024;     // + slack for 1024-byte alignment
 };
 
 template <int BN, int STAGES, bool TF32, int ID>
@@ -76,7 +92,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ TcParams p,
           const __grid_constant__ B2xVmProgram epi, int32_t* status) {
   using namespace sm100;
-  using SM = TcSmem<BN, STAGES, TF32>;
+  using SM = TcSmem<BN, STAGES, TF32, tc_transposed_epilogue<ID>()>;
   constexpr int ES = TF32 ? 4 : 2;
   constexpr int BK = 128 / ES;            // elements per 128-byte line: 64 (16-bit) or 32 (tf32)
   constexpr int UMMA_K = 32 / ES;         // 16 or 8
@@ -223,6 +239,51 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       tc_fence_after();
       const int64_t row = (int64_t)m0 + quad * 32 + lane;
       const bool row_ok = row < p.M;
+      if constexpr (tc_transposed_epilogue<ID>()) {
+        // Transposed epilogue: the accumulator chunk goes through shared memory so that four adjacent lanes own one
+        // row's 32 columns.  Every global access of the program is then contiguous over 4 lanes x 8 elements (128 bytes
+        // of f32, 64 of bf16) instead of one 16-byte piece per row.
+        const int wrow0 = m0 + quad * 32;
+        int nrows = (int)min((int64_t)32, p.M - (int64_t)wrow0);
+        VmRowBlock blk;
+        blk.ok = false;
+        if (p.transposed) vm_row_block(epi, rplan, (uint64_t)((int64_t)b * p.M + (nrows > 0 ? wrow0 : 0)), (uint32_t)(nrows > 0 ? nrows : 1), (uint32_t)p.N, blk);
+        if (__all_sync(0xffffffffu, blk.ok)) {
+          const uint32_t stg = smem_base + SM::STAGING_OFFSET + (uint32_t)(warp - 2) * 2048u;
+#pragma unroll 1
+          for (int c = part; c < BN / 32; c += TC_COL_PARTS) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32), r);
+            tc_wait_ld();
+            const int col = n0 + c * 32 + (lane & 3) * 8;
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+              __syncwarp();
+              if ((lane >> 4) == half) {
+                const uint32_t rowaddr = stg + (uint32_t)(lane & 15) * 128u;
+#pragma unroll
+                for (int j = 0; j < 8; j++) sts_v4(rowaddr + (uint32_t)((j ^ (lane & 7)) << 4), r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+              }
+              __syncwarp();
+#pragma unroll
+              for (int run = 0; run < 2; run++) {
+                const int rloc = run * 8 + (lane >> 2);
+                const int rowidx = half * 16 + rloc;
+                const int j0 = (lane & 3) * 2;
+                uint32_t a0[8], out[8];
+                lds_v4(stg + (uint32_t)rloc * 128u + (uint32_t)((j0 ^ (rloc & 7)) << 4), a0[0], a0[1], a0[2], a0[3]);
+                lds_v4(stg + (uint32_t)rloc * 128u + (uint32_t)(((j0 + 1) ^ (rloc & 7)) << 4), a0[4], a0[5], a0[6], a0[7]);
+                if (rowidx < nrows && col < p.N) vm_run_block_row<8, ID>(epi, blk, (uint32_t)rowidx, (uint32_t)col, a0, out);
+              }
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+          continue;
+        }
+      }
+      // Thread = row.
       VmRow vrow;
       vm_row_begin(epi, rplan, (uint64_t)((int64_t)b * p.M + (row_ok ? row : 0)), (uint32_t)p.N, vrow);
       // one decision per warp: tcgen05.ld below is warp-collective, so all lanes must take the same loop
@@ -291,7 +352,7 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcPar
   TcParams p = p_in;
   p.sched = sched_slot();
   if (!p.sched) return (int)cudaErrorUnknown;
-  using SM = TcSmem<BN, STAGES, TF32>;
+  using SM = TcSmem<BN, STAGES, TF32, tc_transposed_epilogue<ID>()>;
   auto kern = k_gemm_tc<BN, STAGES, TF32, ID>;
   {
     // per device: the attribute belongs to the function on the current device

@@ -57,21 +57,23 @@ __device__ __forceinline__ void vm_ld_bytes(const void* p, uint32_t* raw) {
     raw[0] = __ldg((const uint8_t*)p);
   }
 }
+// Stores are streaming (evict-first in L2): results are written once, and a kernel's own operands, which the other
+// CTAs are still re-reading out of L2, should not be pushed out by them.
 template <int NB>
 __device__ __forceinline__ void vm_st_bytes(void* p, const uint32_t* raw) {
   if constexpr (NB == 32) {
-    *((uint4*)p) = make_uint4(raw[0], raw[1], raw[2], raw[3]);
-    *((uint4*)p + 1) = make_uint4(raw[4], raw[5], raw[6], raw[7]);
+    __stcs((uint4*)p, make_uint4(raw[0], raw[1], raw[2], raw[3]));
+    __stcs((uint4*)p + 1, make_uint4(raw[4], raw[5], raw[6], raw[7]));
   } else if constexpr (NB == 16) {
-    *((uint4*)p) = make_uint4(raw[0], raw[1], raw[2], raw[3]);
+    __stcs((uint4*)p, make_uint4(raw[0], raw[1], raw[2], raw[3]));
   } else if constexpr (NB == 8) {
-    *((uint2*)p) = make_uint2(raw[0], raw[1]);
+    __stcs((uint2*)p, make_uint2(raw[0], raw[1]));
   } else if constexpr (NB == 4) {
-    *((uint32_t*)p) = raw[0];
+    __stcs((uint32_t*)p, raw[0]);
   } else if constexpr (NB == 2) {
-    *((uint16_t*)p) = (uint16_t)raw[0];
+    __stcs((uint16_t*)p, (uint16_t)raw[0]);
   } else {
-    *((uint8_t*)p) = (uint8_t)raw[0];
+    __stcs((uint8_t*)p, (uint8_t)raw[0]);
   }
 }
 
@@ -592,6 +594,14 @@ template <int ID> struct VmStatic { static constexpr int n = 0; };
 #include "vm_static_table.h"
 namespace b2x {
 
+// Number of global stores a specialised program issues per vector.
+template <int ID>
+__host__ __device__ constexpr int vm_static_stores() {
+  int k = 0;
+  for (int i = 0; i < VmStatic<ID>::n; i++) if (VmStatic<ID>::at(i).op == VM_STORE) k++;
+  return k;
+}
+
 template <int V, int ID, bool RF, int PC>
 __device__ __forceinline__ void vm_unroll(const B2xVmProgram& P, const int64_t (&coord)[B2X_VM_MAX_DIMS], const int nd,
                                           const int64_t (&off)[B2X_VM_MAX_TENSORS], const VmRowAddr& RA, const int64_t col,
@@ -728,6 +738,61 @@ __device__ __forceinline__ void vm_run_row(const B2xVmProgram& P, const VmRow& R
 template <int V, int ID = 0>
 __device__ __forceinline__ void vm_run_row_vec(const B2xVmProgram& P, const VmRow& R, uint32_t col, const uint32_t (&acc0)[V], uint32_t (&acc)[V]) {
   vm_run_core<V, ID, true>(P, R.coord, R.off, R.addr, (int64_t)col, acc0, acc);
+}
+
+// Addressing of a block of consecutive result rows whose tensor offsets are affine in the row number (the usual case:
+// a 32-row slice of a GEMM tile never straddles an outer program dim unless that dim is tiny).  All fields are the
+// same for every thread that passes the same arguments.  Row r of the block (0 <= r < nrows) has tensor t's column 0 at
+// base[t] + r * step[t]; its coordinates are `coord` with r * coord_mul added at dim coord_dim.
+struct VmRowBlock {
+  int64_t coord[B2X_VM_MAX_DIMS];
+  const char* base[B2X_VM_MAX_TENSORS];
+  int64_t step[B2X_VM_MAX_TENSORS];
+  int32_t cs[B2X_VM_MAX_TENSORS];
+  int32_t coord_dim;
+  int64_t coord_mul;
+  bool ok;       // affine, contiguous-or-broadcast along the row, every row start 16-byte aligned
+};
+__device__ __forceinline__ void vm_row_block(const B2xVmProgram& P, const VmRowPlan& L, uint64_t row0, uint32_t nrows, uint32_t N, VmRowBlock& B) {
+  const int nd = P.n_dims;
+  VmRow R;
+  vm_row_begin(P, L, row0, N, R);
+#pragma unroll
+  for (int d = 0; d < B2X_VM_MAX_DIMS; d++) B.coord[d] = R.coord[d];
+  bool ok = R.vec;
+  const bool folded = L.per > 1 || nd < 2;
+  B.coord_dim = folded ? nd - 1 : nd - 2;
+  B.coord_mul = folded ? (int64_t)N : 1;
+  // the block must stay inside one value of every dim outside coord_dim
+  int64_t at = 0, extent = 1;
+#pragma unroll
+  for (int d = 0; d < B2X_VM_MAX_DIMS; d++) if (d == B.coord_dim) { at = R.coord[d]; extent = P.dim[d]; }
+  ok = ok && (at + (int64_t)(nrows - 1) * B.coord_mul < extent);
+#pragma unroll
+  for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) {
+    B.base[t] = R.addr.rp[t]; B.cs[t] = R.addr.cs[t]; B.step[t] = 0;
+    if (t < P.n_tensors) {
+      const int es = vm_elem_size(P.tensors[t].elem);
+      int64_t st = 0;
+#pragma unroll
+      for (int d = 0; d < B2X_VM_MAX_DIMS; d++) if (d == B.coord_dim) st = P.tensors[t].stride[d];
+      B.step[t] = st * B.coord_mul * es;
+      ok = ok && (R.addr.cs[t] == 0 || (B.step[t] & 15) == 0);
+    }
+  }
+  B.ok = ok;
+}
+// Runs the program for the 8-wide vector at column `col` of row r of the block.
+template <int V, int ID>
+__device__ __forceinline__ void vm_run_block_row(const B2xVmProgram& P, const VmRowBlock& B, uint32_t r, uint32_t col, const uint32_t (&acc0)[V], uint32_t (&acc)[V]) {
+  int64_t coord[B2X_VM_MAX_DIMS];
+  int64_t off[B2X_VM_MAX_TENSORS];
+  VmRowAddr ra;
+#pragma unroll
+  for (int d = 0; d < B2X_VM_MAX_DIMS; d++) coord[d] = B.coord[d] + (d == B.coord_dim ? (int64_t)r * B.coord_mul : 0);
+#pragma unroll
+  for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) { off[t] = 0; ra.rp[t] = B.base[t] + (int64_t)r * B.step[t]; ra.cs[t] = B.cs[t]; }
+  vm_run_core<V, ID, true>(P, coord, off, ra, (int64_t)col, acc0, acc);
 }
 
 // Signature hash of a program (structure only: ops, operand kinds, classes, rounding, tensor element types).
