@@ -9,10 +9,10 @@
 // longest causal prefix first.  The key blocks of a tile (128 keys each) are dealt alternately to two independent
 // softmax streams: stream s owns blocks j = s, s + 2, ..., its own score buffer, probability buffer, K/V stage and
 // output accumulator, and keeps its own running (max, sum).  While one stream exponentiates, the tensor pipe works
-// for the other; the two partial results are merged once, at the end.  320 threads:
+// for the other; the two partial results are merged once, at the end.  352 threads:
 //   warp 0      TMA producer: Q once, then K_j and V_j into stage j & 1 as soon as that stage's previous K (after its
 //               Q K^T retired) or V (after its P V retired) is free; per-CTA loads, no multicast
-//   warp 1      MMA issuer: S_s = Q K_j^T into TMEM score buffer s, O_s += P_s V_j into TMEM accumulator s
+//   warps 1,10  MMA issuers, one per stream: S_s = Q K_j^T into TMEM score buffer s, O_s += P_s V_j into accumulator s
 //   warps 2-5   softmax stream 0, warps 6-9 stream 1; one query row per thread: the 128 scores of the row are read from
 //               TMEM once and stay in registers (row max, exp2, row sum), P goes as bf16 into 128-byte-swizzled
 //               shared memory for the second MMA; the accumulator is rescaled only when the running max grew by more
@@ -49,7 +49,7 @@ struct AttnSmem {
   static constexpr int K_OFF = Q_OFF + Q_BYTES;            // 2 stages (one per stream)
   static constexpr int V_OFF = K_OFF + 2 * KV_BYTES;       // 2 stages
   static constexpr int P_OFF = V_OFF + 2 * KV_BYTES;       // 2 buffers
-  static constexpr int BAR_OFF = P_OFF + 2 * P_BYTES;      // 19 barriers, TMEM slot, abort flag
+  static constexpr int BAR_OFF = P_OFF + 2 * P_BYTES;      // 20 barriers, TMEM slot, abort flag
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
@@ -59,8 +59,32 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Two f32 lanes per instruction (sm_100 packed single precision) and the three-input maximum: the softmax warps are
+// bound by instruction issue, and these halve the count of everything except the exponentials themselves.
+__device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, uint32_t& lo, uint32_t& hi) { asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 template <int D>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(352, 1)
 k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
             const __grid_constant__ AttnParams p, int32_t* status) {
   using namespace sm100;
@@ -77,8 +101,8 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
   // s_empty[2], p_full[2], pv_done[2], merge, drain
   const uint32_t b0 = smem_u32(bars);
   const uint32_t bar_q = b0, bar_kf = b0 + 8, bar_ke = b0 + 24, bar_vf = b0 + 40, bar_ve = b0 + 56, bar_sf = b0 + 72, bar_se = b0 + 88,
-                 bar_pf = b0 + 104, bar_pv = b0 + 120, bar_merge = b0 + 136, bar_drain = b0 + 144;
-  uint32_t* tmem_slot = (uint32_t*)(bars + 19);
+                 bar_pf = b0 + 104, bar_pv = b0 + 120, bar_merge = b0 + 136, bar_drain = b0 + 144;   // drain[2]
+  uint32_t* tmem_slot = (uint32_t*)(bars + 20);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   // per stream and row (max * scale_log2, sum) for the final merge; stream s keeps them at the start of its own
   // probability buffer, which is idle once its last P V product has retired
@@ -100,7 +124,7 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       mbar_init(bar_kf + 8 * s, 1); mbar_init(bar_ke + 8 * s, 1); mbar_init(bar_vf + 8 * s, 1); mbar_init(bar_ve + 8 * s, 1);
       mbar_init(bar_sf + 8 * s, 1); mbar_init(bar_se + 8 * s, 4); mbar_init(bar_pf + 8 * s, 4); mbar_init(bar_pv + 8 * s, 1);
     }
-    mbar_init(bar_merge, 8); mbar_init(bar_drain, 1);
+    mbar_init(bar_merge, 8); mbar_init(bar_drain, 1); mbar_init(bar_drain + 8, 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
@@ -154,12 +178,15 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
           }
       }
     }
-  } else if (warp == 1) {
-    // ---------------------------------------------- MMA issuer ------------------------------------------------------
+  } else if (warp == 1 || warp == 10) {
+    // ---------------------------------------------- MMA issuers -----------------------------------------------------
+    // One issuing thread per stream, so that a stream whose probabilities are late never holds up the other stream's
+    // next score block.  The two threads touch disjoint TMEM columns and shared-memory buffers (Q is only read).
     if (lane == 0) {
+      const int s = warp == 1 ? 0 : 1;
+      const int n_mine = nblk > s ? (nblk - s + 1) / 2 : 0;
       bool ok = mbar_wait(bar_q, 0, abort_flag, status, 12);
-      auto issue_qk = [&](int j) -> bool {
-        const int s = j & 1, it = j >> 1;
+      auto issue_qk = [&](int it) -> bool {
         if (!mbar_wait(bar_kf + 8 * s, (uint32_t)(it & 1), abort_flag, status, 13)) return false;
         tc_fence_after();
         const uint32_t qa = sbase + SM::Q_OFF, ka = sbase + SM::K_OFF + s * SM::KV_BYTES;
@@ -168,18 +195,16 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
           const uint32_t off = (uint32_t)(k >> 2) * CHUNK_BYTES + (uint32_t)(k & 3) * 32;
           umma_ss<false>(tmem_base + (uint32_t)(s * 128), make_smem_desc(qa + off, 16, 1024), make_smem_desc(ka + off, 16, 1024), p.idesc_qk, k > 0 ? 1u : 0u);
         }
-        tc_commit(bar_sf + 8 * s);    // scores ready for stream s
+        tc_commit(bar_sf + 8 * s);    // scores ready for the stream
         tc_commit(bar_ke + 8 * s);    // K stage free
         return true;
       };
-      if (ok && nblk > 0) ok = issue_qk(0);
-      if (ok && nblk > 1) ok = issue_qk(1);
-      for (int j = 0; j < nblk && ok; j++) {
-        const int s = j & 1, it = j >> 1;
-        // the stream has copied block j's scores into registers: its score buffer can take block j + 2
-        if (j + 2 < nblk) {
+      if (ok && n_mine > 0) ok = issue_qk(0);
+      for (int it = 0; it < n_mine && ok; it++) {
+        // the stream has copied this block's scores into registers: its score buffer can take its next block
+        if (it + 1 < n_mine) {
           if (!mbar_wait(bar_se + 8 * s, (uint32_t)(it & 1), abort_flag, status, 14)) { ok = false; break; }
-          if (!issue_qk(j + 2)) { ok = false; break; }
+          if (!issue_qk(it + 1)) { ok = false; break; }
         }
         if (!mbar_wait(bar_vf + 8 * s, (uint32_t)(it & 1), abort_flag, status, 15)) { ok = false; break; }
         if (!mbar_wait(bar_pf + 8 * s, (uint32_t)(it & 1), abort_flag, status, 16)) { ok = false; break; }
@@ -194,10 +219,11 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                          (it > 0 || k > 0) ? 1u : 0u);
         }
         tc_commit(bar_ve + 8 * s);    // V stage free
-        tc_commit(bar_pv + 8 * s);    // accumulator s and probability buffer s may be touched again
+        tc_commit(bar_pv + 8 * s);    // the stream's accumulator and probability buffer may be touched again
       }
-      tc_commit(bar_drain);
-      mbar_wait(bar_drain, 0, abort_flag, nullptr, 0);
+      // everything this thread issued must retire before TMEM is released
+      tc_commit(bar_drain + 8 * s);
+      mbar_wait(bar_drain + 8 * s, 0, abort_flag, nullptr, 0);
     }
   } else {
     // ---------------------------------------------- softmax ---------------------------------------------------------
@@ -238,7 +264,7 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
 #pragma unroll
         for (int c = 0; c < 4; c++)
 #pragma unroll
-          for (int i = 0; i < 32; i++) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[c][i]));
+          for (int i = 0; i < 16; i++) mx4[i & 3] = max3(mx4[i & 3], __uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1]));
         mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       }
       float alpha = 1.f;
@@ -269,22 +295,23 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       // p = exp2(s * scale_log2 - m * scale_log2) (a masked score is -inf and gives exactly 0), row sum, bf16 P into
       // swizzled shared memory; a fully masked row (m = -inf) gives 0 everywhere
       const float mneg = (m_used == -INFINITY) ? 0.f : -m_used * p.scale_log2;
-      float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint32_t sc_bits = __float_as_uint(p.scale_log2), mn_bits = __float_as_uint(mneg);
+      const uint64_t sc2 = pack2(sc_bits, sc_bits), mn2 = pack2(mn_bits, mn_bits);
+      uint64_t ps2[2] = {0ull, 0ull};
 #pragma unroll
       for (int c = 0; c < 4; c++) {
-#pragma unroll
-        for (int i = 0; i < 32; i++) {
-          const float e = fast_exp2(fmaf(__uint_as_float(r[c][i]), p.scale_log2, mneg));
-          r[c][i] = __float_as_uint(e);
-          ps4[i & 3] += e;
-        }
         // 32 keys = 64 bytes = four 16-byte pieces of this row; piece index within the 128-byte line is XOR-swizzled
 #pragma unroll
         for (int q = 0; q < 4; q++) {
           uint32_t w[4];
 #pragma unroll
           for (int h = 0; h < 4; h++) {
-            __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(r[c][q * 8 + 2 * h]), __uint_as_float(r[c][q * 8 + 2 * h + 1]));
+            const int i = q * 8 + 2 * h;
+            uint32_t t0, t1;
+            unpack2(fma2(pack2(r[c][i], r[c][i + 1]), sc2, mn2), t0, t1);
+            const float e0 = fast_exp2(__uint_as_float(t0)), e1 = fast_exp2(__uint_as_float(t1));
+            ps2[h & 1] = add2(ps2[h & 1], pack2(__float_as_uint(e0), __float_as_uint(e1)));
+            __nv_bfloat162 t = __floats2bfloat162_rn(e0, e1);
             w[h] = *reinterpret_cast<uint32_t*>(&t);
           }
           const int piece = c * 4 + q;                 // 0..15 over the 128 keys
@@ -292,7 +319,11 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
           *reinterpret_cast<uint4*>(prow + sub * CHUNK_BYTES + ((in ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
-      l += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
+      {
+        uint32_t a0, a1, b0, b1;
+        unpack2(ps2[0], a0, a1); unpack2(ps2[1], b0, b1);
+        l += (__uint_as_float(a0) + __uint_as_float(a1)) + (__uint_as_float(b0) + __uint_as_float(b1));
+      }
       // P visible to the tensor-core (async) proxy
       tc_fence_before();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -384,7 +415,7 @@ static int launch_attention(const B2xAttentionArgs* a, int32_t* status, cudaStre
   const int64_t grid = (int64_t)p.n_q_tiles * a->BH;
   if (grid <= 0) return 0;
   if (grid > 0x7fffffff) return (int)cudaErrorInvalidValue;
-  kern<<<(unsigned)grid, 320, SM::TOTAL, stream>>>(tmQ, tmK, tmV, p, status);
+  kern<<<(unsigned)grid, 352, SM::TOTAL, stream>>>(tmQ, tmK, tmV, p, status);
   count_launch();
   return (int)cudaGetLastError();
 }
