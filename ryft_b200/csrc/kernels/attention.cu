@@ -66,6 +66,7 @@ __device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) {
   asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
   return r;
 }
+__device__ __forceinline__ uint64_t splat2(float v) { return pack2(__float_as_uint(v), __float_as_uint(v)); }
 __device__ __forceinline__ void unpack2(uint64_t v, uint32_t& lo, uint32_t& hi) { asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v)); }
 __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
   uint64_t r;
@@ -77,12 +78,12 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
 }
+// NaN-propagating, so that a NaN score poisons its row as it does in an unfused softmax
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
   return r;
 }
-
 template <int D>
 __global__ void __launch_bounds__(352, 1)
 k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -235,8 +236,8 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     const uint32_t s_addr = tmem_base + lane_addr + (uint32_t)(s * 128);
     const uint32_t o_addr = tmem_base + lane_addr + 256u + (uint32_t)(s * D);
     float m_used = -INFINITY, l = 0.f;
-    bool ok = true;
-    uint8_t* prow = smem + SM::P_OFF + s * SM::P_BYTES + row * 128;
+    bool ok = true, poisoned = false;
+    const uint32_t prow_s = sbase + (uint32_t)(SM::P_OFF + s * SM::P_BYTES + row * 128);
     const int n_mine = nblk > s ? (nblk - s + 1) / 2 : 0;    // blocks s, s + 2, ...
     for (int it = 0; it < n_mine && ok; it++) {
       const int j = 2 * it + s;
@@ -253,20 +254,24 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       int64_t lim = p.Sk - 1 - (int64_t)j * AT_N;
       if (p.causal) { const int64_t c = qrow - (int64_t)j * AT_N; lim = c < lim ? c : lim; }
       const bool need_mask = __any_sync(0xffffffffu, lim < AT_N - 1);
-      float mx = -INFINITY;
       if (need_mask) {
 #pragma unroll
         for (int c = 0; c < 4; c++)
 #pragma unroll
-          for (int i = 0; i < 32; i++) { if (c * 32 + i > lim) r[c][i] = 0xff800000u; mx = fmaxf(mx, __uint_as_float(r[c][i])); }
-      } else {
+          for (int i = 0; i < 32; i++) if (c * 32 + i > lim) r[c][i] = 0xff800000u;
+      }
+      float mx;
+      {
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
         for (int c = 0; c < 4; c++)
 #pragma unroll
           for (int i = 0; i < 16; i++) mx4[i & 3] = max3(mx4[i & 3], __uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1]));
-        mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        mx = max3(mx4[0], mx4[1], max3(mx4[2], mx4[3], -INFINITY));
       }
+      // a NaN score makes the whole row NaN (as max and sum do in the unfused program); keep the arithmetic finite
+      // and poison the row sum at the end
+      if (mx != mx) { poisoned = true; mx = 0.f; }
       float alpha = 1.f;
       bool rescale = false;
       if (it == 0) m_used = mx;
@@ -307,8 +312,9 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
 #pragma unroll
           for (int h = 0; h < 4; h++) {
             const int i = q * 8 + 2 * h;
+            const uint64_t x2 = fma2(pack2(r[c][i], r[c][i + 1]), sc2, mn2);
             uint32_t t0, t1;
-            unpack2(fma2(pack2(r[c][i], r[c][i + 1]), sc2, mn2), t0, t1);
+            unpack2(x2, t0, t1);
             const float e0 = fast_exp2(__uint_as_float(t0)), e1 = fast_exp2(__uint_as_float(t1));
             ps2[h & 1] = add2(ps2[h & 1], pack2(__float_as_uint(e0), __float_as_uint(e1)));
             __nv_bfloat162 t = __floats2bfloat162_rn(e0, e1);
@@ -316,7 +322,7 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
           }
           const int piece = c * 4 + q;                 // 0..15 over the 128 keys
           const int sub = piece >> 3, in = piece & 7;
-          *reinterpret_cast<uint4*>(prow + sub * CHUNK_BYTES + ((in ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          sts_v4(prow_s + (uint32_t)(sub * CHUNK_BYTES + ((in ^ (row & 7)) << 4)), w[0], w[1], w[2], w[3]);
         }
       }
       {
@@ -332,6 +338,7 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     }
     // ---- merge the two streams and write O / l as bf16 ----
     if (ok && n_mine > 0) ok = mbar_wait(bar_pv + 8 * s, (uint32_t)((n_mine - 1) & 1), abort_flag, status, 19);
+    if (poisoned) l = __int_as_float(0x7fc00000);
     *merge_slot(s, row) = make_float2((n_mine > 0 && m_used != -INFINITY) ? m_used * p.scale_log2 : -INFINITY, n_mine > 0 ? l : 0.f);
     tc_fence_before();
     __syncwarp();
@@ -344,7 +351,7 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       const float a_mine = (mine.x == -INFINITY) ? 0.f : fast_exp2(mine.x - mm);
       const float a_other = (other.x == -INFINITY) ? 0.f : fast_exp2(other.x - mm);
       const float lsum = mine.y * a_mine + other.y * a_other;
-      const float inv = lsum > 0.f ? __fdividef(1.0f, lsum) : 0.f;
+      const float inv = !(lsum <= 0.f) ? __fdividef(1.0f, lsum) : 0.f;   // a NaN sum stays NaN
       const float w_mine = a_mine * inv, w_other = a_other * inv;
       const bool have_mine = n_mine > 0, have_other = (nblk > (s ^ 1));
       const uint32_t o_mine = o_addr, o_other = tmem_base + lane_addr + 256u + (uint32_t)((s ^ 1) * D);
