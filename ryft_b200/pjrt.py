@@ -843,6 +843,43 @@ class TorchStoreKeyValueStore(KeyValueStore):
         self.store.set(key, value)
 
 
+class KvCallbacks:
+    """The two C callbacks `PJRT_Client_Create` takes for a distributed key-value store
+    (`PJRT_KeyValueGetCallback` / `PJRT_KeyValuePutCallback`, crates/ryft-pjrt/src/clients.rs:849-964), backed by a
+    `KeyValueStore`.  The plugin calls them from its own threads; a returned value stays alive until the plugin calls
+    the deleter it was handed."""
+
+    GET = _args("KvGet", [("key", _vp), ("key_size", _sz), ("timeout_in_ms", _i), ("callback_error", _vp), ("user_arg", _vp),
+                           ("value", _vp), ("value_size", _sz), ("value_deleter_callback", _vp)])
+    PUT = _args("KvPut", [("key", _vp), ("key_size", _sz), ("value", _vp), ("value_size", _sz), ("callback_error", _vp), ("user_arg", _vp)])
+
+    def __init__(self, store: KeyValueStore):
+        self.store = store
+        self.live = {}
+
+        def deleter(ptr):
+            self.live.pop(ptr, None)
+        self._deleter = C.CFUNCTYPE(None, _vp)(deleter)
+
+        def kv_get(p):
+            g = KvCallbacks.GET.from_address(p)
+            val = store.get(_str(g.key, g.key_size), g.timeout_in_ms)
+            buf = C.create_string_buffer(val, len(val))
+            addr = C.addressof(buf)
+            self.live[addr] = buf
+            g.value = addr; g.value_size = len(val); g.value_deleter_callback = C.cast(self._deleter, _vp)
+            return None
+
+        def kv_put(p):
+            g = KvCallbacks.PUT.from_address(p)
+            store.put(_str(g.key, g.key_size), C.string_at(g.value, g.value_size))
+            return None
+        self._get = C.CFUNCTYPE(_vp, _vp)(kv_get)
+        self._put = C.CFUNCTYPE(_vp, _vp)(kv_put)
+        self.get_ptr = C.cast(self._get, _vp)
+        self.put_ptr = C.cast(self._put, _vp)
+
+
 class Client:
     """`Client` (crates/ryft-pjrt/src/clients.rs)."""
 
@@ -877,33 +914,9 @@ class Client:
         self.handle = a.client
 
     def _install_kv(self, a, store: KeyValueStore):
-        GET = _args("KvGet", [("key", _vp), ("key_size", _sz), ("timeout_in_ms", _i), ("callback_error", _vp), ("user_arg", _vp),
-                               ("value", _vp), ("value_size", _sz), ("value_deleter_callback", _vp)])
-        PUT = _args("KvPut", [("key", _vp), ("key_size", _sz), ("value", _vp), ("value_size", _sz), ("callback_error", _vp), ("user_arg", _vp)])
-        live = {}
-
-        def deleter(ptr):
-            live.pop(ptr, None)
-        self._kv_deleter = C.CFUNCTYPE(None, _vp)(deleter)
-
-        def kv_get(p):
-            g = GET.from_address(p)
-            key = _str(g.key, g.key_size)
-            val = store.get(key, g.timeout_in_ms)
-            buf = C.create_string_buffer(val, len(val))
-            addr = C.addressof(buf)
-            live[addr] = buf
-            g.value = addr; g.value_size = len(val); g.value_deleter_callback = C.cast(self._kv_deleter, _vp)
-            return None
-
-        def kv_put(p):
-            g = PUT.from_address(p)
-            store.put(_str(g.key, g.key_size), C.string_at(g.value, g.value_size))
-            return None
-        self._kv_get = C.CFUNCTYPE(_vp, _vp)(kv_get)
-        self._kv_put = C.CFUNCTYPE(_vp, _vp)(kv_put)
-        a.kv_get_callback = C.cast(self._kv_get, _vp)
-        a.kv_put_callback = C.cast(self._kv_put, _vp)
+        self._kv = KvCallbacks(store)
+        a.kv_get_callback = self._kv.get_ptr
+        a.kv_put_callback = self._kv.put_ptr
 
     def platform_name(self) -> str:
         a = A["Client_PlatformName"](); a.client = self.handle

@@ -115,3 +115,13 @@ def test_poisoned_replica_aborts_the_whole_execution_without_touching_the_gpus(c
     for o in ok:
         o.done.await_()
     assert ok[0].outputs[0].to_numpy().tolist() == [3.0] * 1024
+
+
+@needs2
+def test_two_replica_gradient_step_matches_the_committed_fixture(client):
+    from test_golden_fixtures import load
+    text, ins, outs = load("c5_mlp_gradients_2_replicas")
+    _, got = run_replicated(client, text, ins)
+    for r in range(2):
+        for k, (g, w) in enumerate(zip(got[r], outs[r])):
+            assert_close(g, w, f"c5 fixture replica {r} output {k}")
