@@ -18,6 +18,7 @@
 // Every mbarrier wait is bounded (sm100.cuh); on expiry the CTA unwinds, frees TMEM and reports through `status`.
 #pragma once
 #include <type_traits>
+#include <cstring>
 #include "../../../include/b2x_kernels.h"
 #include "common.cuh"
 #include "sm100.cuh"
@@ -31,6 +32,7 @@ struct TcParams {
   int32_t num_m_tiles, num_n_tiles;
   int64_t num_tiles;
   int32_t k_blocks;
+  int32_t tma_store;   // the single-store epilogue writes through the output tensor map
   int32_t transposed;  // multi-store epilogues on short-K problems go through shared memory (see tc_transposed_epilogue)
   int32_t group_m;     // m-tiles per raster group: a group's A slab stays in L2 while its n-tiles stream by
   uint32_t idesc;
@@ -74,25 +76,47 @@ __host__ __device__ constexpr bool tc_transposed_epilogue() {
   else return vm_static_stores<ID>() >= 2;
 }
 
+// Single-store programs writing 16- or 32-bit elements put their result tile into shared memory and let the TMA engine
+// store it: the load/store unit then sees one shared-memory pass (a few wavefronts per warp) instead of 32 cache lines
+// per warp-wide store, and ragged M / N edges are clipped by the tensor map.
+template <int ID>
+__host__ __device__ constexpr bool tc_tma_store_epilogue() {
+  if constexpr (ID == 0) return false;
+  else if constexpr (vm_static_stores<ID>() != 1) return false;
+  else {
+    const uint8_t e = VmStatic<ID>::elem(vm_static_store_tensor<ID>());
+    return e == EL_BF16 || e == EL_F16 || e == EL_F32 || e == EL_S32 || e == EL_U32 || e == EL_S16 || e == EL_U16;
+  }
+}
+template <int ID>
+__host__ __device__ constexpr int tc_store_elem_size() {
+  if constexpr (!tc_tma_store_epilogue<ID>()) return 0;
+  else {
+    const uint8_t e = VmStatic<ID>::elem(vm_static_store_tensor<ID>());
+    return (e == EL_F32 || e == EL_S32 || e == EL_U32) ? 4 : 2;
+  }
+}
+
 template <int BN, int STAGES, bool TF32, bool STAGING>
 struct TcSmem {
   static constexpr int A_BYTES = TC_BM * 128;   // 128 rows (or k-lines x chunks) of 128 bytes
   static constexpr int B_BYTES = BN * 128;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-  static constexpr int STAGING_OFFSET = BAR_OFFSET + 384;                 // barriers and the tile ring come first
+  static constexpr int STAGING_OFFSET = STAGES * STAGE_BYTES;             // 1024-byte aligned (swizzled store boxes)
   // per epilogue warp 16 rows of 32 f32 columns; only kernels that contain the transposed epilogue pay for it (shared
   // memory a kernel does not ask for stays available to the SM as L1 cache)
   static constexpr int STAGING_BYTES = STAGING ? TC_EPI_WARPS * 2048 : 0;
-  static constexpr int TOTAL = STAGING_OFFSET + STAGING_BYTES + 1024;     // + slack for 1024-byte alignment
+  static constexpr int BAR_OFFSET = STAGING_OFFSET + STAGING_BYTES;       // barriers, TMEM slot, tile ring: 384 bytes
+  static constexpr int TOTAL = BAR_OFFSET + 384 + 1024;                   // + slack for 1024-byte alignment
 };
 
 template <int BN, int STAGES, bool TF32, int ID>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ TcParams p,
+k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmOut,
+          const __grid_constant__ TcParams p,
           const __grid_constant__ B2xVmProgram epi, int32_t* status) {
   using namespace sm100;
-  using SM = TcSmem<BN, STAGES, TF32, tc_transposed_epilogue<ID>()>;
+  using SM = TcSmem<BN, STAGES, TF32, tc_transposed_epilogue<ID>() || tc_tma_store_epilogue<ID>()>;
   constexpr int ES = TF32 ? 4 : 2;
   constexpr int BK = 128 / ES;            // elements per 128-byte line: 64 (16-bit) or 32 (tf32)
   constexpr int UMMA_K = 32 / ES;         // 16 or 8
@@ -283,6 +307,59 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
           continue;
         }
       }
+      if constexpr (tc_tma_store_epilogue<ID>()) {
+        if (p.tma_store) {
+          // Thread = row for the arithmetic; the result goes into this warp's 2 KB staging tile (32 rows of 64 bytes,
+          // 64-byte swizzle: the 16-byte piece index is XORed with bits 1..2 of the row, which also keeps the 16-byte
+          // shared stores of a quarter warp on distinct banks) and from there to global memory with one bulk tensor
+          // store per 64-byte-wide column strip.
+          constexpr int OES = tc_store_elem_size<ID>();
+          constexpr int STRIP = 64 / OES;                   // columns per strip: 32 (16-bit) or 16 (32-bit)
+          const uint32_t stg = smem_base + SM::STAGING_OFFSET + (uint32_t)(warp - 2) * 2048u;
+          const uint32_t my = stg + (uint32_t)lane * 64u;
+          const uint32_t sw = (uint32_t)((lane >> 1) & 3);
+          VmRow vrow;
+          vm_row_begin(epi, rplan, (uint64_t)((int64_t)b * p.M + (row_ok ? row : 0)), (uint32_t)p.N, vrow);
+          const bool row_vec = __all_sync(0xffffffffu, vrow.vec);
+          if (row_vec) {
+#pragma unroll 1
+            for (int c = part; c < BN / 32; c += TC_COL_PARTS) {
+              uint32_t r[32];
+              tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32), r);
+              tc_wait_ld();
+#pragma unroll
+              for (int strip = 0; strip < 32 / STRIP; strip++) {
+                // the previous strip's store must have read the staging tile before it is overwritten
+                if (lane == 0) bulk_wait_read();
+                __syncwarp();
+#pragma unroll
+                for (int v = strip * (STRIP / 8); v < (strip + 1) * (STRIP / 8); v++) {
+                  const int col = n0 + c * 32 + v * 8;
+                  if (row_ok && col < p.N) {
+                    uint32_t a0[8], out[8];
+#pragma unroll
+                    for (int j = 0; j < 8; j++) a0[j] = r[v * 8 + j];
+                    // pieces of this vector inside the 64-byte row: 16-bit -> piece v, 32-bit -> pieces 2 (v & 1), + 1
+                    const uint32_t p0 = OES == 2 ? (uint32_t)(v & 3) : (uint32_t)((v & 1) * 2);
+                    vm_run_row_stage<ID>(epi, vrow, (uint32_t)col, my + ((p0 ^ sw) << 4), my + (((p0 + 1) ^ sw) << 4), a0, out);
+                  }
+                }
+                fence_async_shared();
+                __syncwarp();
+                if (lane == 0 && n0 + c * 32 + strip * STRIP < p.N && m0 + quad * 32 < p.M) {
+                  tma_store_3d(&tmOut, stg, n0 + c * 32 + strip * STRIP, m0 + quad * 32, b);
+                  bulk_commit();
+                }
+              }
+            }
+            if (lane == 0) bulk_wait_read();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+            continue;
+          }
+        }
+      }
       // Thread = row.
       VmRow vrow;
       vm_row_begin(epi, rplan, (uint64_t)((int64_t)b * p.M + (row_ok ? row : 0)), (uint32_t)p.N, vrow);
@@ -330,6 +407,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
     }
   }
 
+  if constexpr (tc_tma_store_epilogue<ID>()) {
+    if (warp >= 2 && lane == 0) bulk_wait_all();   // this thread's result stores are complete before the CTA retires
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -352,7 +432,23 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcPar
   TcParams p = p_in;
   p.sched = sched_slot();
   if (!p.sched) return (int)cudaErrorUnknown;
-  using SM = TcSmem<BN, STAGES, TF32, tc_transposed_epilogue<ID>()>;
+  using SM = TcSmem<BN, STAGES, TF32, tc_transposed_epilogue<ID>() || tc_tma_store_epilogue<ID>()>;
+  CUtensorMap tmOut;
+  memset(&tmOut, 0, sizeof(tmOut));
+  p.tma_store = 0;
+  if constexpr (tc_tma_store_epilogue<ID>()) {
+    // the stored tensor must be the dense row-major [batch, M, N] result
+    constexpr int T = vm_static_store_tensor<ID>();
+    constexpr int OES = tc_store_elem_size<ID>();
+    const B2xVmTensor& o = epi.tensors[T];
+    bool dense = o.stride[epi.n_dims - 1] == 1;
+    int64_t total = 1;
+    for (int d = epi.n_dims - 1; d >= 0; d--) { dense = dense && o.stride[d] == total; total *= epi.dim[d]; }
+    dense = dense && total == p.batch * p.M * p.N && ((uintptr_t)o.ptr & 15) == 0 && (p.N * OES) % 16 == 0;
+    if (dense && encode_3d(&tmOut, OES == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, OES, o.ptr, (uint64_t)p.N, (uint64_t)p.M,
+                           (uint64_t)p.batch, (uint64_t)p.N, (uint64_t)(p.M * p.N), 64 / OES, 32, CU_TENSOR_MAP_SWIZZLE_64B))
+      p.tma_store = 1;
+  }
   auto kern = k_gemm_tc<BN, STAGES, TF32, ID>;
   {
     // per device: the attribute belongs to the function on the current device
@@ -366,7 +462,7 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcPar
     }
   }
   int64_t grid = p.num_tiles < kNumSms ? p.num_tiles : kNumSms;
-  kern<<<(unsigned)grid, TC_THREADS, SM::TOTAL, stream>>>(tmA, tmB, p, epi, status);
+  kern<<<(unsigned)grid, TC_THREADS, SM::TOTAL, stream>>>(tmA, tmB, tmOut, p, epi, status);
   count_launch();
   return (int)cudaGetLastError();
 }

@@ -68,6 +68,20 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
       : "memory");
 }
 
+// 3-D tiled store of a box from this CTA's shared memory; part of the issuing thread's current bulk group.  Boxes are
+// clipped at the tensor's extents, so ragged edges need no predication.  c0 times the element size must be a multiple
+// of 16 bytes and no coordinate may be negative.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, uint32_t src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"((uint64_t)m), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// until the issuing thread's bulk stores have finished reading shared memory / have completed
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 // ---- tcgen05 --------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
@@ -186,9 +200,11 @@ inline PFN_encodeTiled get_encode_tiled() {
   }();
   return fn;
 }
-// 3-D map over a [dim2][dim1][dim0] tensor (dim0 contiguous) with a 128-byte-swizzled box {box0, box1, 1}.
+// 3-D map over a [dim2][dim1][dim0] tensor (dim0 contiguous) with a swizzled box {box0, box1, 1} (128-byte swizzle
+// unless told otherwise).
 inline bool encode_3d(CUtensorMap* m, CUtensorMapDataType dt, int es, const void* base, uint64_t dim0, uint64_t dim1, uint64_t dim2,
-                      uint64_t stride1_elems, uint64_t stride2_elems, uint32_t box0, uint32_t box1) {
+                      uint64_t stride1_elems, uint64_t stride2_elems, uint32_t box0, uint32_t box1,
+                      CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   PFN_encodeTiled fn = get_encode_tiled();
   if (!fn) return false;
   cuuint64_t dims[3] = {dim0, dim1, dim2};
@@ -199,7 +215,7 @@ inline bool encode_3d(CUtensorMap* m, CUtensorMapDataType dt, int es, const void
   cuuint64_t strides[2] = {s1, s2};
   cuuint32_t box[3] = {box0, box1, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(m, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+  CUresult r = fn(m, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }

@@ -256,7 +256,32 @@ __device__ __forceinline__ void vm_put_row(char* p, const uint8_t elem, const ui
 struct VmRowAddr {
   const char* rp[B2X_VM_MAX_TENSORS];
   int32_t cs[B2X_VM_MAX_TENSORS];
+  uint32_t stage[2];   // staged stores only: shared-memory addresses of the vector's first and second 16-byte piece
 };
+__device__ __forceinline__ void vm_sts16(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+// Staged store of 8 elements (16-bit: one piece, 32-bit: two pieces) for kernels that write their result tile with a
+// bulk tensor store from shared memory.
+__device__ __forceinline__ void vm_put_stage(const VmRowAddr& RA, const uint8_t elem, const uint32_t (&a)[8]) {
+  if (vm_elem_size(elem) == 4) {
+    vm_sts16(RA.stage[0], vm_encode(a[0], elem), vm_encode(a[1], elem), vm_encode(a[2], elem), vm_encode(a[3], elem));
+    vm_sts16(RA.stage[1], vm_encode(a[4], elem), vm_encode(a[5], elem), vm_encode(a[6], elem), vm_encode(a[7], elem));
+  } else {
+    uint32_t raw[4];
+    if (elem == EL_BF16) {
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(u2f(a[2 * j]), u2f(a[2 * j + 1]));
+        raw[j] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; j++) raw[j] = vm_encode(a[2 * j], elem) | (vm_encode(a[2 * j + 1], elem) << 16);
+    }
+    vm_sts16(RA.stage[0], raw[0], raw[1], raw[2], raw[3]);
+  }
+}
 
 __device__ __forceinline__ float vm_fmax(float x, float y) { return (x != x) ? x : ((y != y) ? y : fmaxf(x, y)); }
 __device__ __forceinline__ float vm_fmin(float x, float y) { return (x != x) ? x : ((y != y) ? y : fminf(x, y)); }
@@ -414,7 +439,7 @@ __device__ __forceinline__ int64_t vm_offset(const B2xVmTensor& T, const int64_t
 // constants (specialised programs) the switches below fold away and only the selected op's code remains.
 // `off[t]` is tensor t's element offset for this vector without the part contributed by `col` along the innermost dim
 // (callers that have no separate column pass col = 0 and fold everything into off).
-template <int V, bool RF = false>
+template <int V, bool RF = false, bool STG = false>
 __device__ __forceinline__ void vm_exec(const B2xVmProgram& P, const int64_t (&coord)[B2X_VM_MAX_DIMS], const int nd,
                                         const int64_t (&off)[B2X_VM_MAX_TENSORS], const VmRowAddr& RA, const int64_t col, const uint8_t op,
                                         const uint8_t src_kind, const uint8_t src_idx, const uint8_t aux, const uint8_t tc, const uint8_t rnd,
@@ -475,7 +500,12 @@ __device__ __forceinline__ void vm_exec(const B2xVmProgram& P, const int64_t (&c
       narrow = false;
       break;
     case VM_STORE: {
-      if constexpr (RF) {
+      if constexpr (STG) {
+        static_assert(V == 8, "staged stores are 8 elements wide");
+        vm_put_stage(RA, elem, S.acc);
+        narrow = false;
+        break;
+      } else if constexpr (RF) {
         const char* rp = nullptr; int32_t cs = 0;
 #pragma unroll
         for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) if (t == src_idx) { rp = RA.rp[t]; cs = RA.cs[t]; }
@@ -602,19 +632,19 @@ __host__ __device__ constexpr int vm_static_stores() {
   return k;
 }
 
-template <int V, int ID, bool RF, int PC>
+template <int V, int ID, bool RF, bool STG, int PC>
 __device__ __forceinline__ void vm_unroll(const B2xVmProgram& P, const int64_t (&coord)[B2X_VM_MAX_DIMS], const int nd,
                                           const int64_t (&off)[B2X_VM_MAX_TENSORS], const VmRowAddr& RA, const int64_t col,
                                           const uint32_t (&acc0)[V], VmState<V>& S) {
   if constexpr (PC < VmStatic<ID>::n) {
     constexpr VmSig G = VmStatic<ID>::at(PC);
     constexpr uint8_t elem = (G.src_kind == VM_SRC_TENSOR) ? VmStatic<ID>::elem(G.src_idx) : (uint8_t)0;
-    vm_exec<V, RF>(P, coord, nd, off, RA, col, G.op, G.src_kind, G.src_idx, G.aux, G.tc, G.rnd, P.code[PC].imm, elem, acc0, S);
-    vm_unroll<V, ID, RF, PC + 1>(P, coord, nd, off, RA, col, acc0, S);
+    vm_exec<V, RF, STG>(P, coord, nd, off, RA, col, G.op, G.src_kind, G.src_idx, G.aux, G.tc, G.rnd, P.code[PC].imm, elem, acc0, S);
+    vm_unroll<V, ID, RF, STG, PC + 1>(P, coord, nd, off, RA, col, acc0, S);
   }
 }
 
-template <int V, int ID, bool RF = false>
+template <int V, int ID, bool RF = false, bool STG = false>
 __device__ __forceinline__ void vm_run_core(const B2xVmProgram& P, const int64_t (&coord)[B2X_VM_MAX_DIMS], const int64_t (&off)[B2X_VM_MAX_TENSORS],
                                             const VmRowAddr& RA, const int64_t col, const uint32_t (&acc0)[V], uint32_t (&acc)[V]) {
   const int nd = P.n_dims;
@@ -629,7 +659,7 @@ __device__ __forceinline__ void vm_run_core(const B2xVmProgram& P, const int64_t
       vm_exec<V, RF>(P, coord, nd, off, RA, col, I.op, I.src_kind, I.src_idx, I.aux, I.tc, I.rnd, I.imm, elem, acc0, S);
     }
   } else {
-    vm_unroll<V, ID, RF, 0>(P, coord, nd, off, RA, col, acc0, S);
+    vm_unroll<V, ID, RF, STG, 0>(P, coord, nd, off, RA, col, acc0, S);
   }
 #pragma unroll
   for (int j = 0; j < V; j++) acc[j] = S.acc[j];
@@ -793,6 +823,22 @@ __device__ __forceinline__ void vm_run_block_row(const B2xVmProgram& P, const Vm
 #pragma unroll
   for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) { off[t] = 0; ra.rp[t] = B.base[t] + (int64_t)r * B.step[t]; ra.cs[t] = B.cs[t]; }
   vm_run_core<V, ID, true>(P, coord, off, ra, (int64_t)col, acc0, acc);
+}
+
+// Index of the tensor a specialised program's (single) store writes, or -1.
+template <int ID>
+__host__ __device__ constexpr int vm_static_store_tensor() {
+  int t = -1;
+  for (int i = 0; i < VmStatic<ID>::n; i++) if (VmStatic<ID>::at(i).op == VM_STORE) t = VmStatic<ID>::at(i).src_idx;
+  return t;
+}
+// Row-wise run whose store goes to the staging addresses in `stage` instead of global memory.
+template <int ID>
+__device__ __forceinline__ void vm_run_row_stage(const B2xVmProgram& P, const VmRow& R, uint32_t col, uint32_t stage0, uint32_t stage1,
+                                                 const uint32_t (&acc0)[8], uint32_t (&acc)[8]) {
+  VmRowAddr ra = R.addr;
+  ra.stage[0] = stage0; ra.stage[1] = stage1;
+  vm_run_core<8, ID, true, true>(P, R.coord, R.off, ra, (int64_t)col, acc0, acc);
 }
 
 // Signature hash of a program (structure only: ops, operand kinds, classes, rounding, tensor element types).

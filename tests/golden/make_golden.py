@@ -26,7 +26,7 @@ def cases():
     yield "c2_matmul_bias_tanh", configs.c2_program(2, 128, 64, 64), [configs.c2_inputs(2, 128, 64, 64)]
     yield "c3_attention_causal", configs.c3_program(1, 2, 256, 64), [configs.c3_inputs(1, 2, 256, 64)]
     yield "c3_attention_full", configs.c3_program(1, 1, 128, 128, causal=False), [configs.c3_inputs(1, 1, 128, 128)]
-    yield "c4_mlp_gradients", configs.c4_program(256, 128, 256), [configs.c4_inputs(256, 128, 256)]
+    yield "c4_mlp_gradients", configs.c4_program(256, 128, 384), [configs.c4_inputs(256, 128, 384)]
     yield "c5_mlp_gradients_2_replicas", configs.c4_program(64, 64, 128, replicas=2), \
         [configs.c4_inputs(64, 64, 128, seed=4, replica=r) for r in range(2)]
 

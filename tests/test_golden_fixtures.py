@@ -40,7 +40,7 @@ def test_oracle_reproduces_the_fixture(name):
 
 def test_fixture_programs_are_what_the_builders_emit_today():
     assert load("c2_matmul_bias_tanh")[0] == configs.c2_program(2, 128, 64, 64)
-    assert load("c4_mlp_gradients")[0] == configs.c4_program(256, 128, 256)
+    assert load("c4_mlp_gradients")[0] == configs.c4_program(256, 128, 384)
     q, k, v = configs.c3_inputs(1, 2, 256, 64)
     assert np.array_equal(load("c3_attention_causal")[1][0][0].view(np.uint16), q.view(np.uint16))
 
