@@ -694,6 +694,12 @@ struct VmRowPlan {
   bool fast;      // the innermost program dim is a whole number of rows
   bool small;     // row numbers and all outer dims fit in 32 bits: the row is decomposed with 32-bit divisions
   uint64_t per;   // rows folded into the innermost program dim
+  // The usual case (the program's dims merged down to [rows * N] or [rows, N]): every tensor's offset is row * step,
+  // so a row needs one multiply-add per tensor instead of a coordinate decomposition.
+  bool affine, affine_vec;
+  int64_t coord_mul;                           // coord[0] = row * coord_mul
+  int64_t rowstep[B2X_VM_MAX_TENSORS];         // elements per row
+  int32_t cs[B2X_VM_MAX_TENSORS];              // bytes per column
 };
 __device__ __forceinline__ VmRowPlan vm_row_plan(const B2xVmProgram& P, uint32_t N) {
   VmRowPlan L;
@@ -708,6 +714,21 @@ __device__ __forceinline__ VmRowPlan vm_row_plan(const B2xVmProgram& P, uint32_t
     if (d < nd - 1) { const uint64_t n = (uint64_t)P.dim[d]; small = small && n <= 0x7fffffffull && rows <= 0x7fffffffull; rows *= n; }
   }
   L.small = small && rows <= 0x7fffffffull;
+  L.affine = L.fast && (nd == 1 || (nd == 2 && L.per == 1));
+  L.coord_mul = nd == 1 ? (int64_t)N : 1;
+  bool vec = (uint64_t)N * 8 < 0x7fffffffull;
+#pragma unroll
+  for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) {
+    L.rowstep[t] = 0; L.cs[t] = 0;
+    if (t < P.n_tensors && L.affine) {
+      const int es = vm_elem_size(P.tensors[t].elem);
+      const int64_t istride = nd == 1 ? P.tensors[t].stride[0] : P.tensors[t].stride[1];
+      L.rowstep[t] = nd == 1 ? (int64_t)N * P.tensors[t].stride[0] : P.tensors[t].stride[0];
+      L.cs[t] = (int32_t)istride * es;
+      vec = vec && es <= 4 && (istride == 0 || (istride == 1 && ((uintptr_t)P.tensors[t].ptr & 15) == 0 && ((L.rowstep[t] * es) & 15) == 0));
+    }
+  }
+  L.affine_vec = vec;
   return L;
 }
 __device__ __forceinline__ void vm_row_begin(const B2xVmProgram& P, const VmRowPlan& L, uint64_t row, uint32_t N, VmRow& R) {
@@ -720,6 +741,19 @@ __device__ __forceinline__ void vm_row_begin(const B2xVmProgram& P, const VmRowP
 #pragma unroll
   for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) { R.off[t] = 0; R.addr.rp[t] = nullptr; R.addr.cs[t] = 0; }
   if (!R.fast) return;
+  if (L.affine) {
+    R.coord[0] = (int64_t)row * L.coord_mul;
+#pragma unroll
+    for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) {
+      if (t < P.n_tensors) {
+        R.off[t] = (int64_t)row * L.rowstep[t];
+        R.addr.rp[t] = (const char*)P.tensors[t].ptr + R.off[t] * vm_elem_size(P.tensors[t].elem);
+        R.addr.cs[t] = L.cs[t];
+      }
+    }
+    R.vec = L.affine_vec;
+    return;
+  }
   int64_t inner_base;
   if (L.small) {
     const uint32_t per = (uint32_t)L.per, r32 = (uint32_t)row;
