@@ -42,7 +42,11 @@ struct TcParams {
 constexpr int TC_BM = 128;
 constexpr int TC_EPI_WARPS = 16;                    // four per TMEM lane quarter, i.e. four per warp scheduler
 constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;
-constexpr int TC_COL_PARTS = TC_EPI_WARPS / 4;
+// The epilogue warps form two groups of eight, one per TMEM accumulator: group g finishes tiles g, g + 2, ... of the CTA
+// on its own.  The groups drift out of phase (one reads TMEM or stores while the other is in its MUFU-heavy part), and
+// each warp's per-tile set-up is amortised over twice as many columns as with all sixteen warps on every tile.
+constexpr int TC_EPI_GROUP = TC_EPI_WARPS / 2;
+constexpr int TC_COL_PARTS = TC_EPI_GROUP / 4;
 
 // Tile order: batches outermost; inside a batch, groups of `group_m` m-tiles, and inside a group m fastest.  Tiles that
 // run at the same time then share a few rows of A and a few columns of B, and consecutive waves reuse the group's A
@@ -142,9 +146,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-    for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, TC_EPI_WARPS); }
+    for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, TC_EPI_GROUP); }
     mbar_init(bar_drain, 1);
-    for (int r = 0; r < RING; r++) { mbar_init(bar_sfull + 8 * r, 1); mbar_init(bar_sempty + 8 * r, TC_EPI_WARPS + 1); }
+    for (int r = 0; r < RING; r++) { mbar_init(bar_sfull + 8 * r, 1); mbar_init(bar_sempty + 8 * r, TC_EPI_GROUP + 1); }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -173,7 +177,16 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         if (t >= p.num_tiles) t = -1;
         tile_ring[slot] = (int32_t)t;
         mbar_arrive(bar_sfull + 8 * slot);
-        if (t < 0) break;
+        if (t < 0) {
+          // the other epilogue group reads the ring entry after this one: it gets its own end marker
+          const int64_t nxt = local + 1;
+          const int slot2 = (int)(nxt & (RING - 1));
+          if (mbar_wait(bar_sempty + 8 * slot2, (uint32_t)(((nxt / RING) & 1) ^ 1), abort_flag, status, 5)) {
+            tile_ring[slot2] = -1;
+            mbar_arrive(bar_sfull + 8 * slot2);
+          }
+          break;
+        }
         int b, m0, n0;
         tc_tile_coords(p, t, BN, &b, &m0, &n0);
         for (int kb = 0; kb < p.k_blocks; kb++) {
@@ -245,10 +258,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   } else {
     // ------------------------------------------------ epilogue ------------------------------------------------------
     const int quad = warp & 3;              // TMEM lanes [32*quad, 32*quad + 32)
-    const int part = (warp - 2) >> 2;       // column chunks part, part + TC_COL_PARTS, ...
+    const int group = (warp - 2) / TC_EPI_GROUP;                 // accumulator this warp serves
+    const int part = ((warp - 2) % TC_EPI_GROUP) >> 2;           // column chunks part, part + TC_COL_PARTS, ...
     bool ok = true;
     const VmRowPlan rplan = vm_row_plan(epi, (uint32_t)p.N);
-    for (int64_t local = 0; ok; local++) {
+    for (int64_t local = group; ok; local += 2) {
       const int slot = (int)(local & (RING - 1));
       if (!mbar_wait(bar_sfull + 8 * slot, (uint32_t)((local / RING) & 1), abort_flag, status, 7)) { ok = false; break; }
       const int64_t t = tile_ring[slot];
