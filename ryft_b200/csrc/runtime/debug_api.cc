@@ -1,5 +1,6 @@
 // Host-only helpers exported from libb2x_kernels.so: compile a module and return the launch plan as text.  Needs
 // no GPU, so the front end and the planner can be checked anywhere.
+#include <cstdlib>
 #include <cstring>
 #include <string>
 
@@ -13,6 +14,10 @@ extern "C" __attribute__((visibility("default"))) int b2x_plan_dump(const char* 
     auto m = b2x::parse_module(std::string(mlir, mlir_size));
     b2x::PlanOptions o;
     o.num_replicas = num_replicas > 0 ? num_replicas : 1;
+    // the same switches the plugin reads at compile time, so that a dump shows the plan that would run
+    if (const char* f = getenv("B2X_FUSED_ATTENTION")) o.allow_fused_attention = strcmp(f, "0") != 0;
+    if (const char* f = getenv("B2X_EPILOGUE_FUSION")) o.allow_epilogue_fusion = strcmp(f, "0") != 0;
+    if (const char* g = getenv("B2X_GEMM")) o.allow_tensor_core = strcmp(g, "simt") != 0;
     text = b2x::build_plan(*m, o, 0).dump();
   } catch (const b2x::CompileError& e) {
     code = e.code;
