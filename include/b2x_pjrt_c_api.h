@@ -687,6 +687,46 @@ typedef struct PJRT_Stream_Extension {
   PJRT_Error* (*wait_stream)(PJRT_Wait_Until_Buffer_Ready_On_Stream_Args*);
 } PJRT_Stream_Extension;
 
+/* Layouts extension (crates/ryft-pjrt/src/extensions/layouts.rs:596-807, version 4).  Every buffer of this plugin is
+ * dense and major-to-minor, so a layout is just the minor_to_major permutation {n-1, ..., 0}; it serializes to the
+ * rendered text form the reference parses (`SerializedLayout::proto`, layouts.rs:401-550), e.g. "{2,1,0}".
+ * Layouts returned by Client_GetDefaultLayout and Buffer_MemoryLayout are owned by the caller (MemoryLayout_Destroy);
+ * those returned by the Executable_Get*Layouts calls are borrowed from the executable (layouts.rs:247-283). */
+#define PJRT_Extension_Type_Layouts 4
+typedef struct PJRT_Layouts_MemoryLayout PJRT_Layouts_MemoryLayout;
+typedef struct PJRT_Layouts_SerializedLayout PJRT_Layouts_SerializedLayout;
+typedef struct { size_t struct_size; PJRT_Extension_Base* extension_start; PJRT_Buffer* buffer; PJRT_Layouts_MemoryLayout* layout; /* out */ }
+    PJRT_Layouts_PJRT_Buffer_MemoryLayout_Args;
+typedef struct { size_t struct_size; PJRT_Extension_Base* extension_start; PJRT_Layouts_MemoryLayout* layout; } PJRT_Layouts_MemoryLayout_Destroy_Args;
+typedef struct {
+  size_t struct_size; PJRT_Extension_Base* extension_start; PJRT_Layouts_MemoryLayout* layout;
+  const char* serialized_bytes; size_t serialized_bytes_size;          /* out, valid while serialized_layout lives */
+  PJRT_Layouts_SerializedLayout* serialized_layout;                     /* out */
+  void (*serialized_layout_deleter)(PJRT_Layouts_SerializedLayout*);    /* out */
+} PJRT_Layouts_MemoryLayout_Serialize_Args;
+typedef struct {
+  size_t struct_size; PJRT_Extension_Base* extension_start; PJRT_Client* client; PJRT_Buffer_Type element_type;
+  const int64_t* dims; size_t num_dims; PJRT_Layouts_MemoryLayout* layout; /* out */
+} PJRT_Layouts_PJRT_Client_GetDefaultLayout_Args;
+typedef struct {
+  size_t struct_size; PJRT_Extension_Base* extension_start; void* topology_description; PJRT_Buffer_Type element_type;
+  const int64_t* dims; size_t num_dims; PJRT_Layouts_MemoryLayout* layout; /* out */
+} PJRT_Layouts_PJRT_Topology_GetDefaultLayout_Args;
+typedef struct { size_t struct_size; PJRT_Extension_Base* extension_start; PJRT_Executable* executable; size_t num_parameters; /* out */
+                 PJRT_Layouts_MemoryLayout** layouts; /* out */ } PJRT_Layouts_PJRT_Executable_GetParameterLayouts_Args;
+typedef struct { size_t struct_size; PJRT_Extension_Base* extension_start; PJRT_Executable* executable; size_t num_outputs; /* out */
+                 PJRT_Layouts_MemoryLayout** layouts; /* out */ } PJRT_Layouts_PJRT_Executable_GetOutputLayouts_Args;
+typedef struct PJRT_Layouts_Extension {
+  PJRT_Extension_Base base;
+  PJRT_Error* (*PJRT_Layouts_MemoryLayout_Destroy)(PJRT_Layouts_MemoryLayout_Destroy_Args*);
+  PJRT_Error* (*PJRT_Layouts_MemoryLayout_Serialize)(PJRT_Layouts_MemoryLayout_Serialize_Args*);
+  PJRT_Error* (*PJRT_Layouts_PJRT_Client_GetDefaultLayout)(PJRT_Layouts_PJRT_Client_GetDefaultLayout_Args*);
+  PJRT_Error* (*PJRT_Layouts_PJRT_Buffer_MemoryLayout)(PJRT_Layouts_PJRT_Buffer_MemoryLayout_Args*);
+  PJRT_Error* (*PJRT_Layouts_PJRT_Topology_GetDefaultLayout)(PJRT_Layouts_PJRT_Topology_GetDefaultLayout_Args*);   /* NULL: no topologies */
+  PJRT_Error* (*PJRT_Layouts_PJRT_Executable_GetOutputLayouts)(PJRT_Layouts_PJRT_Executable_GetOutputLayouts_Args*);
+  PJRT_Error* (*PJRT_Layouts_PJRT_Executable_GetParameterLayouts)(PJRT_Layouts_PJRT_Executable_GetParameterLayouts_Args*);
+} PJRT_Layouts_Extension;
+
 /* Step-timing extension (no counterpart in the reference; private type id).  When enabled for a loaded executable,
  * every later execution brackets each plan step with CUDA events on the stream the step runs on.  `collect` waits
  * for the recorded executions, sums the device time per step and resets the record.  Arrays are borrowed from the

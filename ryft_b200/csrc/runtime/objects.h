@@ -110,6 +110,13 @@ struct PJRT_Buffer {
   PJRT_Buffer_Type pjrt_type = PJRT_Buffer_Type_INVALID;
 };
 
+struct PJRT_Layouts_MemoryLayout {
+  std::vector<int64_t> minor_to_major;   // always {rank-1, ..., 0}: every buffer is dense, major to minor
+};
+struct PJRT_Layouts_SerializedLayout {
+  std::string text;                      // rendered form, e.g. "{2,1,0}"
+};
+
 struct PJRT_Executable {
   std::shared_ptr<struct b2x_ExecutableCore> core;
 };
@@ -129,6 +136,8 @@ struct b2x_ExecutableCore {
   std::vector<size_t> out_ranks;
   std::vector<const char*> out_kinds, param_kinds;
   std::vector<size_t> out_kind_sizes, param_kind_sizes;
+  std::vector<PJRT_Layouts_MemoryLayout> param_layouts, out_layouts;        // lent out by the layouts extension
+  std::vector<PJRT_Layouts_MemoryLayout*> param_layout_ptrs, out_layout_ptrs;
   std::vector<PJRT_NamedValue> cost_props;
   std::vector<std::string> cost_names;
   const b2x::Plan& plan_for(int replica) const { return plans.size() == 1 ? plans[0] : plans[replica]; }

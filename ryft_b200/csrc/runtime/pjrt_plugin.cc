@@ -1280,16 +1280,86 @@ static PJRT_Error* Ext_StepTiming(B2X_StepTiming_Args* a) {
   return nullptr;
 }
 
+// ---- layouts extension ------------------------------------------------------------------------------------------------
+// crates/ryft-pjrt/src/extensions/layouts.rs: default layout of a buffer / executable parameter / result.
+
+static PJRT_Layouts_MemoryLayout descending_layout(size_t rank) {
+  PJRT_Layouts_MemoryLayout l;
+  for (size_t i = 0; i < rank; i++) l.minor_to_major.push_back((int64_t)(rank - 1 - i));
+  return l;
+}
+static PJRT_Error* Layouts_Destroy(PJRT_Layouts_MemoryLayout_Destroy_Args* a) {
+  delete a->layout;
+  return nullptr;
+}
+static void Layouts_DeleteSerialized(PJRT_Layouts_SerializedLayout* s) { delete s; }
+static PJRT_Error* Layouts_Serialize(PJRT_Layouts_MemoryLayout_Serialize_Args* a) {
+  if (!a->layout) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "null layout");
+  auto* s = new PJRT_Layouts_SerializedLayout();
+  s->text = "{";
+  for (size_t i = 0; i < a->layout->minor_to_major.size(); i++) s->text += (i ? "," : "") + std::to_string(a->layout->minor_to_major[i]);
+  s->text += "}";
+  a->serialized_bytes = s->text.data();
+  a->serialized_bytes_size = s->text.size();
+  a->serialized_layout = s;
+  a->serialized_layout_deleter = Layouts_DeleteSerialized;
+  return nullptr;
+}
+static PJRT_Error* Layouts_ClientDefault(PJRT_Layouts_PJRT_Client_GetDefaultLayout_Args* a) {
+  if (from_pjrt_type(a->element_type) == DType::INVALID) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "unsupported element type");
+  a->layout = new PJRT_Layouts_MemoryLayout(descending_layout(a->num_dims));
+  return nullptr;
+}
+static PJRT_Error* Layouts_BufferLayout(PJRT_Layouts_PJRT_Buffer_MemoryLayout_Args* a) {
+  if (!a->buffer) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "null buffer");
+  a->layout = new PJRT_Layouts_MemoryLayout(descending_layout(a->buffer->dims.size()));
+  return nullptr;
+}
+static void fill_executable_layouts(b2x_ExecutableCore& c) {
+  if (!c.param_layout_ptrs.empty() || !c.out_layout_ptrs.empty() || c.plans.empty()) return;
+  const b2x::Plan& p = c.plans[0];
+  for (auto& t : p.arg_types) c.param_layouts.push_back(descending_layout(t.dims.size()));
+  for (size_t r : c.out_ranks) c.out_layouts.push_back(descending_layout(r));
+  for (auto& l : c.param_layouts) c.param_layout_ptrs.push_back(&l);
+  for (auto& l : c.out_layouts) c.out_layout_ptrs.push_back(&l);
+}
+static std::mutex g_layouts_mu;
+static PJRT_Error* Layouts_ExecutableOutputs(PJRT_Layouts_PJRT_Executable_GetOutputLayouts_Args* a) {
+  std::lock_guard<std::mutex> lk(g_layouts_mu);
+  fill_executable_layouts(*a->executable->core);
+  a->num_outputs = a->executable->core->out_layout_ptrs.size();
+  a->layouts = a->executable->core->out_layout_ptrs.data();
+  return nullptr;
+}
+static PJRT_Error* Layouts_ExecutableParameters(PJRT_Layouts_PJRT_Executable_GetParameterLayouts_Args* a) {
+  std::lock_guard<std::mutex> lk(g_layouts_mu);
+  fill_executable_layouts(*a->executable->core);
+  a->num_parameters = a->executable->core->param_layout_ptrs.size();
+  a->layouts = a->executable->core->param_layout_ptrs.data();
+  return nullptr;
+}
+
 // ---- table ----------------------------------------------------------------------------------------------------------------
 
 static PJRT_Api make_api() {
   static PJRT_Stream_Extension stream_ext;
   static B2X_StepTiming_Extension timing_ext;
+  static PJRT_Layouts_Extension layouts_ext;
+  memset(&layouts_ext, 0, sizeof(layouts_ext));
+  layouts_ext.base.struct_size = sizeof(layouts_ext);
+  layouts_ext.base.extension_type = PJRT_Extension_Type_Layouts;
+  layouts_ext.base.next = nullptr;
+  layouts_ext.PJRT_Layouts_MemoryLayout_Destroy = Layouts_Destroy;
+  layouts_ext.PJRT_Layouts_MemoryLayout_Serialize = Layouts_Serialize;
+  layouts_ext.PJRT_Layouts_PJRT_Client_GetDefaultLayout = Layouts_ClientDefault;
+  layouts_ext.PJRT_Layouts_PJRT_Buffer_MemoryLayout = Layouts_BufferLayout;
+  layouts_ext.PJRT_Layouts_PJRT_Executable_GetOutputLayouts = Layouts_ExecutableOutputs;
+  layouts_ext.PJRT_Layouts_PJRT_Executable_GetParameterLayouts = Layouts_ExecutableParameters;
   memset(&stream_ext, 0, sizeof(stream_ext));
   memset(&timing_ext, 0, sizeof(timing_ext));
   timing_ext.base.struct_size = sizeof(timing_ext);
   timing_ext.base.extension_type = B2X_Extension_Type_StepTiming;
-  timing_ext.base.next = nullptr;
+  timing_ext.base.next = &layouts_ext.base;
   timing_ext.step_timing = Ext_StepTiming;
   stream_ext.base.struct_size = sizeof(stream_ext);
   stream_ext.base.extension_type = PJRT_Extension_Type_Stream;

@@ -79,6 +79,7 @@ def _args(name: str, fields):
 
 
 EXTENSION_TYPE_STREAM = 3          # crates/ryft-pjrt/src/lib.rs:183
+EXTENSION_TYPE_LAYOUTS = 4         # crates/ryft-pjrt/src/lib.rs:184
 EXTENSION_TYPE_STEP_TIMING = 0x62327801
 
 
@@ -523,6 +524,13 @@ class Buffer:
     def __init__(self, client: "Client", handle: int, keep=None):
         self.client, self.api, self.handle, self._keep = client, client.api, handle, keep
 
+    def layout(self) -> "Layout":
+        """Memory layout of this buffer through the layouts extension (crates/ryft-pjrt/src/extensions/layouts.rs:610-629)."""
+        a = _args("LayoutBuffer", [("buffer", _vp), ("layout", _vp)])()
+        a.buffer = self.handle
+        Layout._call(self.client.api, Layout._BUFFER, a)
+        return Layout(self.client.api, a.layout, borrowed=False)
+
     def element_type(self) -> BufferType:
         a = A["Buffer_ElementType"](); a.buffer = self.handle
         self.api.call("Buffer_ElementType", a)
@@ -641,6 +649,24 @@ class Executable:
         a = A[name](); a.executable = self.handle
         self.api.call(name, a)
         return a
+
+    def _layouts(self, slot: int) -> List["Layout"]:
+        a = _args("LayoutExecutable", [("executable", _vp), ("count", _sz), ("layouts", _vp)])()
+        a.executable = self.handle
+        Layout._call(self.api, slot, a)
+        ptrs = (C.c_void_p * a.count).from_address(a.layouts) if a.count else []
+        keep = [Layout(self.api, ptrs[i], borrowed=True) for i in range(a.count)]
+        for l in keep:
+            l._owner = self          # borrowed from the executable: keep it alive
+        return keep
+
+    def input_layouts(self) -> List["Layout"]:
+        """`Executable::input_layouts` (crates/ryft-pjrt/src/extensions/layouts.rs:247-263)."""
+        return self._layouts(Layout._EXE_PARAMETERS)
+
+    def output_layouts(self) -> List["Layout"]:
+        """`Executable::output_layouts` (crates/ryft-pjrt/src/extensions/layouts.rs:266-283)."""
+        return self._layouts(Layout._EXE_OUTPUTS)
 
     def name(self) -> str:
         a = self._get("Executable_Name"); return _str(a.executable_name, a.executable_name_size)
@@ -803,6 +829,68 @@ class LoadedExecutable:
             pass
 
 
+class Layout:
+    """`Layout` of the layouts extension (crates/ryft-pjrt/src/extensions/layouts.rs:94-190): an opaque memory layout
+    handle that renders as its minor-to-major order, e.g. "{2,1,0}".  Borrowed layouts (those an executable lends out)
+    are not destroyed."""
+
+    # slots of PJRT_Layouts_Extension after the 24-byte base (layouts.rs:798-807)
+    _DESTROY, _SERIALIZE, _CLIENT_DEFAULT, _BUFFER, _TOPOLOGY_DEFAULT, _EXE_OUTPUTS, _EXE_PARAMETERS = range(7)
+
+    def __init__(self, api: "Api", handle: int, borrowed: bool):
+        self.api, self.handle, self.borrowed = api, handle, borrowed
+
+    @staticmethod
+    def _fn(api: "Api", slot: int):
+        ext = api.extension(EXTENSION_TYPE_LAYOUTS)
+        if not ext:
+            raise PjrtError(12, "the plugin has no layouts extension")
+        fp = C.c_void_p.from_address(ext + 24 + 8 * slot).value
+        if not fp:
+            raise PjrtError(12, "this function of the layouts extension is not implemented by the plugin")
+        return _FN(fp)
+
+    @staticmethod
+    def _call(api: "Api", slot: int, args) -> None:
+        args.struct_size = C.sizeof(args)
+        err = Layout._fn(api, slot)(C.addressof(args))
+        if err:
+            raise api._take_error(err)
+
+    def serialize(self) -> str:
+        a = _args("LayoutSerialize", [("layout", _vp), ("serialized_bytes", _vp), ("serialized_bytes_size", _sz), ("serialized_layout", _vp),
+                                      ("serialized_layout_deleter", _vp)])()
+        a.layout = self.handle
+        Layout._call(self.api, Layout._SERIALIZE, a)
+        text = C.string_at(a.serialized_bytes, a.serialized_bytes_size).decode()
+        if a.serialized_layout_deleter:
+            C.CFUNCTYPE(None, _vp)(a.serialized_layout_deleter)(a.serialized_layout)
+        return text
+
+    def minor_to_major(self) -> List[int]:
+        body = self.serialize().strip("{}").split(":")[0]
+        return [int(x) for x in body.split(",")] if body else []
+
+    def __str__(self) -> str:
+        return self.serialize()
+
+    def __repr__(self) -> str:
+        return f"Layout[{self.serialize()}]"
+
+    def __eq__(self, other) -> bool:
+        return isinstance(other, Layout) and self.serialize() == other.serialize()
+
+    def __del__(self):
+        if not self.borrowed and self.handle:
+            try:
+                a = _args("LayoutDestroy", [("layout", _vp)])()
+                a.layout = self.handle
+                Layout._call(self.api, Layout._DESTROY, a)
+            except Exception:
+                pass
+            self.handle = None
+
+
 class KeyValueStore:
     """Interface of the store behind the client's kv callbacks (crates/ryft-pjrt/src/clients.rs:575-640)."""
 
@@ -917,6 +1005,14 @@ class Client:
         self._kv = KvCallbacks(store)
         a.kv_get_callback = self._kv.get_ptr
         a.kv_put_callback = self._kv.put_ptr
+
+    def default_layout(self, element_type: int, dims) -> "Layout":
+        """`Client::default_layout` (crates/ryft-pjrt/src/extensions/layouts.rs:198-219)."""
+        arr = (_i64 * max(len(dims), 1))(*dims)
+        a = _args("LayoutClientDefault", [("client", _vp), ("element_type", _i), ("dims", _vp), ("num_dims", _sz), ("layout", _vp)])()
+        a.client = self.handle; a.element_type = int(element_type); a.dims = C.cast(arr, _vp); a.num_dims = len(dims)
+        Layout._call(self.api, Layout._CLIENT_DEFAULT, a)
+        return Layout(self.api, a.layout, borrowed=False)
 
     def platform_name(self) -> str:
         a = A["Client_PlatformName"](); a.client = self.handle

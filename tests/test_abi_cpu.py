@@ -134,3 +134,26 @@ def test_client_create_without_gpu_fails_without_fallback(plugin):
     with pytest.raises(pjrt.PjrtError) as e:
         plugin.client()
     assert e.value.code_name == "FAILED_PRECONDITION" and "no CPU execution path" in e.value.message
+
+
+def test_layouts_extension_default_layout_and_serialization(plugin):
+    """crates/ryft-pjrt/src/extensions/layouts.rs:829-841: the default layout of an f32 [2,3,4] buffer renders as
+    "{2,1,0}".  The extension answers from the dimensions alone, so this runs without a device."""
+    import ctypes as C
+    api = plugin.api
+    ext = api.extension(pjrt.EXTENSION_TYPE_LAYOUTS)
+    assert ext, "layouts extension missing from the extension chain"
+    slots = [bool(C.c_void_p.from_address(ext + 24 + 8 * i).value) for i in range(7)]
+    assert slots == [True, True, True, True, False, True, True]      # no topology objects in this plugin
+
+    class _NoClient:
+        handle = None
+    fake = pjrt.Client.__new__(pjrt.Client)
+    fake.api, fake.handle = api, None
+    layout = fake.default_layout(pjrt.BufferType.F32, [2, 3, 4])
+    assert str(layout) == "{2,1,0}" and repr(layout) == "Layout[{2,1,0}]" and layout.minor_to_major() == [2, 1, 0]
+    assert str(fake.default_layout(pjrt.BufferType.BF16, [5, 7])) == "{1,0}"
+    assert str(fake.default_layout(pjrt.BufferType.S32, [])) == "{}"
+    assert layout == fake.default_layout(pjrt.BufferType.F32, [9, 9, 9])
+    with pytest.raises(pjrt.PjrtError):
+        fake.default_layout(0, [1])                                   # PJRT_Buffer_Type_INVALID

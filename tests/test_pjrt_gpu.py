@@ -219,3 +219,15 @@ module {
     exe = client.compile(pjrt.Program.mlir(text))
     out = exe.execute([pjrt.ExecutionDeviceInputs([client.buffer(x)])])[0].outputs[0].to_numpy()
     assert np.array_equal(out, 2 * x)
+
+
+def test_layouts_extension_on_executables_and_buffers(client):
+    """crates/ryft-pjrt/src/extensions/layouts.rs:944-990: both inputs and the output of the i32 add program have
+    layout "{1,0}"; a buffer reports the same layout as the client's default for its shape."""
+    exe = client.compile(pjrt.Program.mlir(ADD_PROGRAM))
+    e = exe.executable()
+    ins, outs = e.input_layouts(), e.output_layouts()
+    assert [str(l) for l in ins] == ["{1,0}", "{1,0}"]
+    assert len(outs) == e.num_outputs() and [str(l) for l in outs] == ["{1,0}"]
+    buf = client.buffer(np.zeros((2, 3, 4), dtype=np.float32))
+    assert buf.layout() == client.default_layout(pjrt.BufferType.F32, [2, 3, 4]) and str(buf.layout()) == "{2,1,0}"
