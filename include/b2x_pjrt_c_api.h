@@ -727,6 +727,24 @@ typedef struct PJRT_Layouts_Extension {
   PJRT_Error* (*PJRT_Layouts_PJRT_Executable_GetParameterLayouts)(PJRT_Layouts_PJRT_Executable_GetParameterLayouts_Args*);
 } PJRT_Layouts_Extension;
 
+/* Memory-descriptions extension (crates/ryft-pjrt/src/extensions/memory_descriptions.rs:215-285, version 1): the memory
+ * kinds a described device offers.  Every device of this plugin has one, "device" (HBM), which is also its default. */
+#define PJRT_Extension_Type_MemoryDescriptions 6
+typedef struct PJRT_MemoryDescription PJRT_MemoryDescription;
+typedef struct {
+  size_t struct_size; PJRT_Extension_Base* extension_start; PJRT_DeviceDescription* device_description;
+  const PJRT_MemoryDescription* const* memory_descriptions; size_t num_memory_descriptions; ptrdiff_t default_memory_index;  /* out */
+} PJRT_DeviceDescription_MemoryDescriptions_Args;
+typedef struct {
+  size_t struct_size; PJRT_Extension_Base* extension_start; const PJRT_MemoryDescription* memory_description;
+  const char* kind; size_t kind_size; int kind_id;  /* out */
+} PJRT_MemoryDescription_Kind_Args;
+typedef struct PJRT_MemoryDescriptions_Extension {
+  PJRT_Extension_Base base;
+  PJRT_Error* (*PJRT_DeviceDescription_MemoryDescriptions)(PJRT_DeviceDescription_MemoryDescriptions_Args*);
+  PJRT_Error* (*PJRT_MemoryDescription_Kind)(PJRT_MemoryDescription_Kind_Args*);
+} PJRT_MemoryDescriptions_Extension;
+
 /* Step-timing extension (no counterpart in the reference; private type id).  When enabled for a loaded executable,
  * every later execution brackets each plan step with CUDA events on the stream the step runs on.  `collect` waits
  * for the recorded executions, sums the device time per step and resets the record.  Arrays are borrowed from the

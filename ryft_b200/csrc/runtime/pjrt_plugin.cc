@@ -479,7 +479,10 @@ static PJRT_Error* DeviceDescription_ToString(PJRT_DeviceDescription_ToString_Ar
   a->to_string = a->device_description->to_string.data(); a->to_string_size = a->device_description->to_string.size(); return nullptr;
 }
 static PJRT_Error* Memory_Id(PJRT_Memory_Id_Args* a) { a->id = a->memory->id; return nullptr; }
-static PJRT_Error* Memory_Kind_Id(PJRT_Memory_Kind_Id_Args* a) { a->kind_id = 0; return nullptr; }
+// One memory kind, "device"; its id is a fixed non-zero number (FNV-1a of the kind name, 31 bits), as kind ids are
+// compared for equality and tested for being non-zero by ryft (crates/ryft-pjrt/src/memories.rs:136-138, 354).
+static constexpr int kDeviceMemoryKindId = 0x1b3c5a71;
+static PJRT_Error* Memory_Kind_Id(PJRT_Memory_Kind_Id_Args* a) { a->kind_id = kDeviceMemoryKindId; return nullptr; }
 static PJRT_Error* Memory_Kind(PJRT_Memory_Kind_Args* a) { a->kind = a->memory->kind.data(); a->kind_size = a->memory->kind.size(); return nullptr; }
 static PJRT_Error* Memory_DebugString(PJRT_Memory_DebugString_Args* a) {
   a->debug_string = a->memory->debug_string.data(); a->debug_string_size = a->memory->debug_string.size(); return nullptr;
@@ -1339,16 +1342,42 @@ static PJRT_Error* Layouts_ExecutableParameters(PJRT_Layouts_PJRT_Executable_Get
   return nullptr;
 }
 
+// ---- memory-descriptions extension ------------------------------------------------------------------------------------
+struct PJRT_MemoryDescription { const char* kind; size_t kind_size; int kind_id; };
+static const PJRT_MemoryDescription kDeviceMemoryDescription = {"device", 6, kDeviceMemoryKindId};
+static const PJRT_MemoryDescription* const kMemoryDescriptions[1] = {&kDeviceMemoryDescription};
+static PJRT_Error* MemDesc_ForDevice(PJRT_DeviceDescription_MemoryDescriptions_Args* a) {
+  if (!a->device_description) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "null device description");
+  a->memory_descriptions = kMemoryDescriptions;
+  a->num_memory_descriptions = 1;
+  a->default_memory_index = 0;
+  return nullptr;
+}
+static PJRT_Error* MemDesc_Kind(PJRT_MemoryDescription_Kind_Args* a) {
+  if (!a->memory_description) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "null memory description");
+  a->kind = a->memory_description->kind;
+  a->kind_size = a->memory_description->kind_size;
+  a->kind_id = a->memory_description->kind_id;
+  return nullptr;
+}
+
 // ---- table ----------------------------------------------------------------------------------------------------------------
 
 static PJRT_Api make_api() {
   static PJRT_Stream_Extension stream_ext;
   static B2X_StepTiming_Extension timing_ext;
   static PJRT_Layouts_Extension layouts_ext;
+  static PJRT_MemoryDescriptions_Extension memdesc_ext;
+  memset(&memdesc_ext, 0, sizeof(memdesc_ext));
+  memdesc_ext.base.struct_size = sizeof(memdesc_ext);
+  memdesc_ext.base.extension_type = PJRT_Extension_Type_MemoryDescriptions;
+  memdesc_ext.base.next = nullptr;
+  memdesc_ext.PJRT_DeviceDescription_MemoryDescriptions = MemDesc_ForDevice;
+  memdesc_ext.PJRT_MemoryDescription_Kind = MemDesc_Kind;
   memset(&layouts_ext, 0, sizeof(layouts_ext));
   layouts_ext.base.struct_size = sizeof(layouts_ext);
   layouts_ext.base.extension_type = PJRT_Extension_Type_Layouts;
-  layouts_ext.base.next = nullptr;
+  layouts_ext.base.next = &memdesc_ext.base;
   layouts_ext.PJRT_Layouts_MemoryLayout_Destroy = Layouts_Destroy;
   layouts_ext.PJRT_Layouts_MemoryLayout_Serialize = Layouts_Serialize;
   layouts_ext.PJRT_Layouts_PJRT_Client_GetDefaultLayout = Layouts_ClientDefault;

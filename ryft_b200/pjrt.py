@@ -80,6 +80,7 @@ def _args(name: str, fields):
 
 EXTENSION_TYPE_STREAM = 3          # crates/ryft-pjrt/src/lib.rs:183
 EXTENSION_TYPE_LAYOUTS = 4         # crates/ryft-pjrt/src/lib.rs:184
+EXTENSION_TYPE_MEMORY_DESCRIPTIONS = 6   # crates/ryft-pjrt/src/lib.rs:186
 EXTENSION_TYPE_STEP_TIMING = 0x62327801
 
 
@@ -466,6 +467,29 @@ class Device:
         return int(a.process_index)
 
     @property
+    def memory_descriptions(self):
+        """Memory-descriptions extension (crates/ryft-pjrt/src/extensions/memory_descriptions.rs): the memory kinds of
+        this device's description as (kind, kind_id) pairs, and the index of the default one."""
+        ext = self.api.extension(EXTENSION_TYPE_MEMORY_DESCRIPTIONS)
+        if not ext:
+            raise PjrtError(12, "the plugin has no memory-descriptions extension")
+        a = _args("MemoryDescriptions", [("device_description", _vp), ("memory_descriptions", _vp), ("num_memory_descriptions", _sz),
+                                         ("default_memory_index", C.c_ssize_t)])()
+        a.struct_size = C.sizeof(a); a.device_description = self._desc
+        err = _FN(C.c_void_p.from_address(ext + 24).value)(C.addressof(a))
+        if err:
+            raise self.api._take_error(err)
+        out = []
+        ptrs = (C.c_void_p * a.num_memory_descriptions).from_address(a.memory_descriptions) if a.num_memory_descriptions else []
+        for i in range(a.num_memory_descriptions):
+            k = _args("MemoryDescriptionKind", [("memory_description", _vp), ("kind", _vp), ("kind_size", _sz), ("kind_id", _i)])()
+            k.struct_size = C.sizeof(k); k.memory_description = ptrs[i]
+            err = _FN(C.c_void_p.from_address(ext + 32).value)(C.addressof(k))
+            if err:
+                raise self.api._take_error(err)
+            out.append((_str(k.kind, k.kind_size), int(k.kind_id)))
+        return out, int(a.default_memory_index)
+
     def kind(self) -> str: return self._desc_call("DeviceDescription_Kind", "device_kind", "device_kind_size")
     def to_string(self) -> str: return self._desc_call("DeviceDescription_ToString", "to_string", "to_string_size")
     def debug_string(self) -> str: return self._desc_call("DeviceDescription_DebugString", "debug_string", "debug_string_size")

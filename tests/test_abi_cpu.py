@@ -143,6 +143,7 @@ def test_layouts_extension_default_layout_and_serialization(plugin):
     api = plugin.api
     ext = api.extension(pjrt.EXTENSION_TYPE_LAYOUTS)
     assert ext, "layouts extension missing from the extension chain"
+    assert api.extension(pjrt.EXTENSION_TYPE_MEMORY_DESCRIPTIONS) and api.extension(pjrt.EXTENSION_TYPE_STREAM)
     slots = [bool(C.c_void_p.from_address(ext + 24 + 8 * i).value) for i in range(7)]
     assert slots == [True, True, True, True, False, True, True]      # no topology objects in this plugin
 

@@ -231,3 +231,12 @@ def test_layouts_extension_on_executables_and_buffers(client):
     assert len(outs) == e.num_outputs() and [str(l) for l in outs] == ["{1,0}"]
     buf = client.buffer(np.zeros((2, 3, 4), dtype=np.float32))
     assert buf.layout() == client.default_layout(pjrt.BufferType.F32, [2, 3, 4]) and str(buf.layout()) == "{2,1,0}"
+
+
+def test_memory_descriptions_extension(client):
+    """crates/ryft-pjrt/src/extensions/memory_descriptions.rs:297-318: every memory description has a non-empty kind
+    and a non-zero kind id; the default one is among them and matches the device's default memory."""
+    dev = client.addressable_devices()[0]
+    descs, default = dev.memory_descriptions()
+    assert descs and all(kind and kind_id != 0 for kind, kind_id in descs)
+    assert 0 <= default < len(descs) and descs[default][0] == "device"
