@@ -466,8 +466,7 @@ class Device:
         self.api.call("DeviceDescription_ProcessIndex", a)
         return int(a.process_index)
 
-    @property
-    def memory_descriptions(self):
+        def memory_descriptions(self):
         """Memory-descriptions extension (crates/ryft-pjrt/src/extensions/memory_descriptions.rs): the memory kinds of
         this device's description as (kind, kind_id) pairs, and the index of the default one."""
         ext = self.api.extension(EXTENSION_TYPE_MEMORY_DESCRIPTIONS)
@@ -490,6 +489,7 @@ class Device:
             out.append((_str(k.kind, k.kind_size), int(k.kind_id)))
         return out, int(a.default_memory_index)
 
+    @property
     def kind(self) -> str: return self._desc_call("DeviceDescription_Kind", "device_kind", "device_kind_size")
     def to_string(self) -> str: return self._desc_call("DeviceDescription_ToString", "to_string", "to_string_size")
     def debug_string(self) -> str: return self._desc_call("DeviceDescription_DebugString", "debug_string", "debug_string_size")
