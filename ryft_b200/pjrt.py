@@ -466,7 +466,7 @@ class Device:
         self.api.call("DeviceDescription_ProcessIndex", a)
         return int(a.process_index)
 
-        def memory_descriptions(self):
+    def memory_descriptions(self):
         """Memory-descriptions extension (crates/ryft-pjrt/src/extensions/memory_descriptions.rs): the memory kinds of
         this device's description as (kind, kind_id) pairs, and the index of the default one."""
         ext = self.api.extension(EXTENSION_TYPE_MEMORY_DESCRIPTIONS)
