@@ -529,6 +529,40 @@ typedef struct {
 } PJRT_LoadedExecutable_Execute_Args;
 
 /* ---- function table: order of crates/ryft-pjrt/src/lib.rs:222-363 ---------------------- */
+/* Asynchronous host-to-device transfer manager (crates/ryft-pjrt/src/transfers.rs:537-850): device buffers are created
+ * first and filled later in chunks; a buffer becomes ready when its last chunk (or a whole-buffer literal) has arrived,
+ * or carries the error set on it. */
+typedef struct PJRT_AsyncHostToDeviceTransferManager PJRT_AsyncHostToDeviceTransferManager;
+typedef struct { size_t struct_size; PJRT_Extension_Base* extension_start; const int64_t* dims; size_t num_dims; PJRT_Buffer_Type element_type; } PJRT_ShapeSpec;
+typedef struct {
+  size_t struct_size; PJRT_Extension_Base* extension_start; PJRT_Client* client; PJRT_ShapeSpec* shape_specs; size_t num_shape_specs;
+  PJRT_Buffer_MemoryLayout** device_layouts; size_t num_device_layouts; PJRT_Memory* memory;
+  PJRT_AsyncHostToDeviceTransferManager* transfer_manager;  /* out */
+} PJRT_Client_CreateBuffersForAsyncHostToDevice_Args;
+typedef struct { size_t struct_size; PJRT_Extension_Base* extension_start; PJRT_AsyncHostToDeviceTransferManager* transfer_manager; PJRT_Device* device_out; }
+    PJRT_AsyncHostToDeviceTransferManager_Device_Args;
+typedef struct { size_t struct_size; PJRT_Extension_Base* extension_start; PJRT_AsyncHostToDeviceTransferManager* transfer_manager; size_t buffer_count; }
+    PJRT_AsyncHostToDeviceTransferManager_BufferCount_Args;
+typedef struct { size_t struct_size; PJRT_Extension_Base* extension_start; PJRT_AsyncHostToDeviceTransferManager* transfer_manager; int buffer_index;
+                 size_t buffer_size; } PJRT_AsyncHostToDeviceTransferManager_BufferSize_Args;
+typedef struct { size_t struct_size; PJRT_Extension_Base* extension_start; PJRT_AsyncHostToDeviceTransferManager* transfer_manager; int buffer_index;
+                 PJRT_Buffer* buffer_out; } PJRT_AsyncHostToDeviceTransferManager_RetrieveBuffer_Args;
+typedef struct {
+  size_t struct_size; PJRT_Extension_Base* extension_start; PJRT_AsyncHostToDeviceTransferManager* transfer_manager; int buffer_index;
+  const void* data; int64_t offset; int64_t transfer_size; bool is_last_transfer; PJRT_Event* done_with_h2d_transfer;  /* out */
+} PJRT_AsyncHostToDeviceTransferManager_TransferData_Args;
+typedef struct {
+  size_t struct_size; PJRT_Extension_Base* extension_start; PJRT_AsyncHostToDeviceTransferManager* transfer_manager; int buffer_index;
+  const void* data; const int64_t* shape_dims; size_t shape_num_dims; PJRT_Buffer_Type shape_element_type; PJRT_Buffer_MemoryLayout* shape_layout;
+  PJRT_Event* done_with_h2d_transfer;  /* out */
+} PJRT_AsyncHostToDeviceTransferManager_TransferLiteral_Args;
+typedef struct { size_t struct_size; PJRT_Extension_Base* extension_start; PJRT_AsyncHostToDeviceTransferManager* transfer_manager; int buffer_index;
+                 PJRT_Error_Code error_code; const char* error_message; size_t error_message_size; } PJRT_AsyncHostToDeviceTransferManager_SetBufferError_Args;
+typedef struct { size_t struct_size; PJRT_Extension_Base* extension_start; PJRT_AsyncHostToDeviceTransferManager* transfer_manager;
+                 const PJRT_NamedValue* transfer_metadata; size_t num_metadata; } PJRT_AsyncHostToDeviceTransferManager_AddMetadata_Args;
+typedef struct { size_t struct_size; PJRT_Extension_Base* extension_start; PJRT_AsyncHostToDeviceTransferManager* transfer_manager; }
+    PJRT_AsyncHostToDeviceTransferManager_Destroy_Args;
+
 typedef PJRT_Error* (*PJRT_Fn)(void* args); /* placeholder type for entries this plugin leaves NULL */
 #define B2X_PJRT_FN(name) PJRT_Error* (*name)(name##_Args*)
 typedef struct PJRT_Api {
@@ -636,15 +670,15 @@ typedef struct PJRT_Api {
   B2X_PJRT_FN(PJRT_ExecuteContext_Create);
   B2X_PJRT_FN(PJRT_ExecuteContext_Destroy);
   B2X_PJRT_FN(PJRT_Buffer_CopyRawToHost);
-  PJRT_Fn PJRT_AsyncHostToDeviceTransferManager_Destroy;
-  PJRT_Fn PJRT_AsyncHostToDeviceTransferManager_TransferData;
-  PJRT_Fn PJRT_Client_CreateBuffersForAsyncHostToDevice;
-  PJRT_Fn PJRT_AsyncHostToDeviceTransferManager_RetrieveBuffer;
-  PJRT_Fn PJRT_AsyncHostToDeviceTransferManager_Device;
-  PJRT_Fn PJRT_AsyncHostToDeviceTransferManager_BufferCount;
-  PJRT_Fn PJRT_AsyncHostToDeviceTransferManager_BufferSize;
-  PJRT_Fn PJRT_AsyncHostToDeviceTransferManager_SetBufferError;
-  PJRT_Fn PJRT_AsyncHostToDeviceTransferManager_AddMetadata;
+  B2X_PJRT_FN(PJRT_AsyncHostToDeviceTransferManager_Destroy);
+  B2X_PJRT_FN(PJRT_AsyncHostToDeviceTransferManager_TransferData);
+  B2X_PJRT_FN(PJRT_Client_CreateBuffersForAsyncHostToDevice);
+  B2X_PJRT_FN(PJRT_AsyncHostToDeviceTransferManager_RetrieveBuffer);
+  B2X_PJRT_FN(PJRT_AsyncHostToDeviceTransferManager_Device);
+  B2X_PJRT_FN(PJRT_AsyncHostToDeviceTransferManager_BufferCount);
+  B2X_PJRT_FN(PJRT_AsyncHostToDeviceTransferManager_BufferSize);
+  B2X_PJRT_FN(PJRT_AsyncHostToDeviceTransferManager_SetBufferError);
+  B2X_PJRT_FN(PJRT_AsyncHostToDeviceTransferManager_AddMetadata);
   B2X_PJRT_FN(PJRT_Client_DmaMap);
   B2X_PJRT_FN(PJRT_Client_DmaUnmap);
   B2X_PJRT_FN(PJRT_Client_CreateUninitializedBuffer);
@@ -654,7 +688,7 @@ typedef struct PJRT_Api {
   PJRT_Fn PJRT_Client_FulfillAliasBuffer;
   B2X_PJRT_FN(PJRT_LoadedExecutable_GetDeviceAssignment);
   B2X_PJRT_FN(PJRT_Client_CreateErrorBuffer);
-  PJRT_Fn PJRT_AsyncHostToDeviceTransferManager_TransferLiteral;
+  B2X_PJRT_FN(PJRT_AsyncHostToDeviceTransferManager_TransferLiteral);
   PJRT_Fn PJRT_Buffer_CopyRawToHostFuture;
   B2X_PJRT_FN(PJRT_Device_PoisonExecution);
   PJRT_Fn PJRT_Device_CreateAsyncTrackingEvent;

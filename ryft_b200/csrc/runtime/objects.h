@@ -89,7 +89,17 @@ struct PJRT_Device {
   std::mutex launch_mu;  // serialises enqueues of whole executions on this device
 };
 
+// Definition of a buffer that is filled after it was created (asynchronous host-to-device transfers): consumers that
+// need the contents block until the last chunk has been enqueued (or an error set); ready events register as waiters.
+struct b2x_Definition {
+  std::mutex mu;
+  std::condition_variable cv;
+  bool done = false;
+  std::vector<struct PJRT_Event*> waiters;
+};
+
 struct PJRT_Buffer {
+  std::shared_ptr<b2x_Definition> pending;   // null for buffers that are defined when they are created
   PJRT_Client* client = nullptr;
   PJRT_Device* device = nullptr;
   b2x::TensorType type;

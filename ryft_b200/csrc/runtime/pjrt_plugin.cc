@@ -164,11 +164,20 @@ static PJRT_Error* alloc_buffer(PJRT_Device* dev, const TensorType& type, cudaSt
   return nullptr;
 }
 
+// Blocks until a late-defined buffer has had its last transfer enqueued (then `ready` covers it) or an error set.
+static void await_definition(PJRT_Buffer* b) {
+  std::shared_ptr<b2x_Definition> d = b->pending;
+  if (!d) return;
+  std::unique_lock<std::mutex> lk(d->mu);
+  d->cv.wait(lk, [&] { return d->done; });
+}
+
 static void release_buffer_memory(PJRT_Buffer* b) {
   if (!b->ptr) return;
   PJRT_Device* d = b->device;
   cudaSetDevice(d->cuda_ordinal);
   if (b->owns) {
+    await_definition(b);
     // every use of the memory was enqueued on the compute stream, or on a transfer stream with a recorded event
     for (auto ev : b->pending_reads) { cudaStreamWaitEvent(d->compute, ev, 0); cudaEventDestroy(ev); }
     b->pending_reads.clear();
@@ -667,6 +676,10 @@ static PJRT_Error* Buffer_ReadyEvent(PJRT_Buffer_ReadyEvent_Args* a) {
   PJRT_Buffer* b = a->buffer;
   std::lock_guard<std::mutex> lk(b->mu);
   PJRT_Event* ev = new PJRT_Event();
+  if (b->pending) {
+    std::lock_guard<std::mutex> dl(b->pending->mu);
+    if (!b->pending->done) { ev->ref(); b->pending->waiters.push_back(ev); a->event = ev; return nullptr; }
+  }
   if (b->err_code != PJRT_Error_Code_OK) { ev->set(b->err_code, b->err_msg); a->event = ev; return nullptr; }
   if (b->deleted) { delete ev; return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "the buffer has been deleted"); }
   if (!b->ready) { ev->set(PJRT_Error_Code_OK, ""); a->event = ev; return nullptr; }
@@ -682,6 +695,7 @@ static PJRT_Error* Buffer_ReadyEvent(PJRT_Buffer_ReadyEvent_Args* a) {
 }
 
 static PJRT_Error* copy_to_host(PJRT_Buffer* b, void* dst, size_t offset, size_t size, PJRT_Event** event) {
+  await_definition(b);
   PJRT_Device* d = b->device;
   B2X_CUDA(cudaSetDevice(d->cuda_ordinal));
   if (b->ready) B2X_CUDA(cudaStreamWaitEvent(d->d2h, b->ready, 0));
@@ -730,6 +744,7 @@ static PJRT_Error* copy_to_device_impl(PJRT_Buffer* b, PJRT_Device* dst_dev, PJR
   std::lock_guard<std::mutex> lk(b->mu);
   B2X_RETURN_IF_ERROR(check_live(b));
   if (!dst_dev->addressable) return make_error(PJRT_Error_Code_UNIMPLEMENTED, "copies to devices of other processes are not supported");
+  await_definition(b);
   PJRT_Buffer* nb;
   B2X_RETURN_IF_ERROR(alloc_buffer(dst_dev, b->type, dst_dev->compute, &nb));
   cudaSetDevice(dst_dev->cuda_ordinal);
@@ -1087,6 +1102,7 @@ static PJRT_Error* LoadedExecutable_Execute(PJRT_LoadedExecutable_Execute_Args* 
     cudaSetDevice(dev->cuda_ordinal);
     for (size_t i = 0; i < n_args; i++) {
       PJRT_Buffer* b = a->argument_lists[k][i];
+      await_definition(b);
       if (b->ready) cudaStreamWaitEvent(dev->compute, b->ready, 0);
       L.args.push_back(b->ptr);
     }
@@ -1222,6 +1238,7 @@ static PJRT_Error* Ext_WaitStream(PJRT_Wait_Until_Buffer_Ready_On_Stream_Args* a
   PJRT_Buffer* b = a->buffer;
   std::lock_guard<std::mutex> lk(b->mu);
   B2X_RETURN_IF_ERROR(check_live(b));
+  await_definition(b);
   B2X_CUDA(cudaSetDevice(b->device->cuda_ordinal));
   if (b->ready) B2X_CUDA(cudaStreamWaitEvent((cudaStream_t)a->stream, b->ready, 0));
   return nullptr;
@@ -1280,6 +1297,167 @@ static PJRT_Error* Ext_StepTiming(B2X_StepTiming_Args* a) {
     pd.timed.clear();
   }
   a->step_ms = pd.step_ms.data();
+  return nullptr;
+}
+
+// ---- asynchronous host-to-device transfer manager --------------------------------------------------------------------
+// crates/ryft-pjrt/src/transfers.rs:39-349.  Buffers are allocated up front and handed out at any time; each carries a
+// pending definition that completes when its last chunk (or a literal) has been enqueued on the transfer stream, or
+// when an error is set on it.
+
+struct PJRT_AsyncHostToDeviceTransferManager {
+  PJRT_Client* client = nullptr;
+  PJRT_Device* device = nullptr;
+  struct Slot { PJRT_Buffer* buffer = nullptr; bool retrieved = false; bool finished = false; };
+  std::vector<Slot> slots;
+  std::mutex mu;
+};
+
+// Completes a buffer's pending definition: `code` OK means its contents are whatever the transfer stream holds now.
+static void finish_definition(PJRT_Buffer* b, PJRT_Error_Code code, const std::string& msg) {
+  std::shared_ptr<b2x_Definition> d = b->pending;
+  if (!d) return;
+  PJRT_Device* dev = b->device;
+  cudaSetDevice(dev->cuda_ordinal);
+  if (code == PJRT_Error_Code_OK) {
+    cudaEventCreateWithFlags(&b->ready, cudaEventDisableTiming);
+    cudaEventRecord(b->ready, dev->h2d);
+  } else {
+    b->err_code = code;
+    b->err_msg = msg;
+  }
+  std::vector<PJRT_Event*> waiters;
+  {
+    std::lock_guard<std::mutex> lk(d->mu);
+    d->done = true;
+    waiters.swap(d->waiters);
+  }
+  d->cv.notify_all();
+  for (PJRT_Event* ev : waiters) {
+    if (code != PJRT_Error_Code_OK) { ev->set(code, msg); ev->unref(); continue; }
+    cudaEvent_t e2;
+    cudaEventCreateWithFlags(&e2, cudaEventDisableTiming);
+    cudaEventRecord(e2, dev->h2d);
+    b->client->post({e2, dev->cuda_ordinal, ev, nullptr});
+    ev->unref();                                              // the waiter list's reference
+  }
+}
+
+static PJRT_Error* Client_CreateBuffersForAsyncHostToDevice(PJRT_Client_CreateBuffersForAsyncHostToDevice_Args* a) {
+  PJRT_Device* dev;
+  B2X_RETURN_IF_ERROR(resolve_device(a->client, nullptr, a->memory, &dev));
+  auto tm = std::make_unique<PJRT_AsyncHostToDeviceTransferManager>();
+  tm->client = a->client;
+  tm->device = dev;
+  for (size_t i = 0; i < a->num_shape_specs; i++) {
+    const PJRT_ShapeSpec& sp = a->shape_specs[i];
+    TensorType t;
+    t.dtype = from_pjrt_type(sp.element_type);
+    PJRT_Error* err = nullptr;
+    if (t.dtype == DType::INVALID) err = make_error(PJRT_Error_Code_UNIMPLEMENTED, "buffer element type " + std::to_string(sp.element_type) + " is not supported");
+    t.dims.assign(sp.dims, sp.dims + sp.num_dims);
+    for (auto d : t.dims) if (!err && d < 0) err = make_error(PJRT_Error_Code_INVALID_ARGUMENT, "negative dimension");
+    PJRT_Buffer* b = nullptr;
+    if (!err) err = alloc_buffer(dev, t, dev->h2d, &b);
+    if (err) {
+      for (auto& s : tm->slots) { s.buffer->pending.reset(); release_buffer_memory(s.buffer); delete s.buffer; }
+      return err;
+    }
+    b->pending = std::make_shared<b2x_Definition>();
+    tm->slots.push_back({b, false, false});
+  }
+  a->transfer_manager = tm.release();
+  return nullptr;
+}
+static PJRT_Error* check_slot(PJRT_AsyncHostToDeviceTransferManager* tm, int index) {
+  if (!tm) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "null transfer manager");
+  if (index < 0 || (size_t)index >= tm->slots.size())
+    return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "buffer index " + std::to_string(index) + " is out of range for a transfer manager with " +
+                                                            std::to_string(tm->slots.size()) + " buffers");
+  return nullptr;
+}
+static PJRT_Error* TransferManager_Device(PJRT_AsyncHostToDeviceTransferManager_Device_Args* a) {
+  if (!a->transfer_manager) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "null transfer manager");
+  a->device_out = a->transfer_manager->device;
+  return nullptr;
+}
+static PJRT_Error* TransferManager_BufferCount(PJRT_AsyncHostToDeviceTransferManager_BufferCount_Args* a) {
+  if (!a->transfer_manager) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "null transfer manager");
+  a->buffer_count = a->transfer_manager->slots.size();
+  return nullptr;
+}
+static PJRT_Error* TransferManager_BufferSize(PJRT_AsyncHostToDeviceTransferManager_BufferSize_Args* a) {
+  B2X_RETURN_IF_ERROR(check_slot(a->transfer_manager, a->buffer_index));
+  a->buffer_size = a->transfer_manager->slots[a->buffer_index].buffer->bytes;
+  return nullptr;
+}
+static PJRT_Error* TransferManager_RetrieveBuffer(PJRT_AsyncHostToDeviceTransferManager_RetrieveBuffer_Args* a) {
+  B2X_RETURN_IF_ERROR(check_slot(a->transfer_manager, a->buffer_index));
+  std::lock_guard<std::mutex> lk(a->transfer_manager->mu);
+  auto& s = a->transfer_manager->slots[a->buffer_index];
+  if (s.retrieved) return make_error(PJRT_Error_Code_FAILED_PRECONDITION, "buffer " + std::to_string(a->buffer_index) + " has already been retrieved");
+  s.retrieved = true;
+  a->buffer_out = s.buffer;
+  return nullptr;
+}
+// Enqueues one copy into slot `index`; `last` completes the buffer.  Host memory must stay valid until `done` fires.
+static PJRT_Error* transfer_into(PJRT_AsyncHostToDeviceTransferManager* tm, int index, const void* data, int64_t offset, int64_t size, bool last,
+                                 PJRT_Event** done) {
+  B2X_RETURN_IF_ERROR(check_slot(tm, index));
+  std::lock_guard<std::mutex> lk(tm->mu);
+  auto& s = tm->slots[index];
+  if (s.finished) return make_error(PJRT_Error_Code_FAILED_PRECONDITION, "buffer " + std::to_string(index) + " has already received its last transfer");
+  PJRT_Buffer* b = s.buffer;
+  if (offset < 0 || size < 0 || (uint64_t)offset + (uint64_t)size > b->bytes)
+    return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "transfer of " + std::to_string(size) + " bytes at offset " + std::to_string(offset) +
+                                                            " exceeds the buffer size of " + std::to_string(b->bytes) + " bytes");
+  PJRT_Device* dev = tm->device;
+  B2X_CUDA(cudaSetDevice(dev->cuda_ordinal));
+  if (size) B2X_CUDA(cudaMemcpyAsync((char*)b->ptr + offset, data, (size_t)size, cudaMemcpyHostToDevice, dev->h2d));
+  PJRT_Event* ev = new PJRT_Event();
+  cudaEvent_t ce;
+  cudaEventCreateWithFlags(&ce, cudaEventDisableTiming);
+  cudaEventRecord(ce, dev->h2d);
+  tm->client->post({ce, dev->cuda_ordinal, ev, nullptr});
+  *done = ev;
+  if (last) { s.finished = true; finish_definition(b, PJRT_Error_Code_OK, ""); }
+  return nullptr;
+}
+static PJRT_Error* TransferManager_TransferData(PJRT_AsyncHostToDeviceTransferManager_TransferData_Args* a) {
+  return transfer_into(a->transfer_manager, a->buffer_index, a->data, a->offset, a->transfer_size, a->is_last_transfer, &a->done_with_h2d_transfer);
+}
+static PJRT_Error* TransferManager_TransferLiteral(PJRT_AsyncHostToDeviceTransferManager_TransferLiteral_Args* a) {
+  B2X_RETURN_IF_ERROR(check_slot(a->transfer_manager, a->buffer_index));
+  PJRT_Buffer* b = a->transfer_manager->slots[a->buffer_index].buffer;
+  // the literal must have the buffer's own shape and element type; it is the buffer's only and last transfer
+  if (from_pjrt_type(a->shape_element_type) != b->type.dtype || a->shape_num_dims != b->dims.size() ||
+      !std::equal(b->dims.begin(), b->dims.end(), a->shape_dims))
+    return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "the literal's shape does not match buffer " + std::to_string(a->buffer_index));
+  return transfer_into(a->transfer_manager, a->buffer_index, a->data, 0, (int64_t)b->bytes, true, &a->done_with_h2d_transfer);
+}
+static PJRT_Error* TransferManager_SetBufferError(PJRT_AsyncHostToDeviceTransferManager_SetBufferError_Args* a) {
+  B2X_RETURN_IF_ERROR(check_slot(a->transfer_manager, a->buffer_index));
+  std::lock_guard<std::mutex> lk(a->transfer_manager->mu);
+  auto& s = a->transfer_manager->slots[a->buffer_index];
+  if (s.finished) return make_error(PJRT_Error_Code_FAILED_PRECONDITION, "buffer " + std::to_string(a->buffer_index) + " is already complete");
+  s.finished = true;
+  finish_definition(s.buffer, a->error_code == PJRT_Error_Code_OK ? PJRT_Error_Code_INTERNAL : a->error_code,
+                    std::string(a->error_message ? a->error_message : "", a->error_message_size));
+  return nullptr;
+}
+static PJRT_Error* TransferManager_AddMetadata(PJRT_AsyncHostToDeviceTransferManager_AddMetadata_Args* a) {
+  if (!a->transfer_manager) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "null transfer manager");
+  return nullptr;   // metadata only annotates profiler traces in XLA; there is nothing to attach it to here
+}
+static PJRT_Error* TransferManager_Destroy(PJRT_AsyncHostToDeviceTransferManager_Destroy_Args* a) {
+  PJRT_AsyncHostToDeviceTransferManager* tm = a->transfer_manager;
+  if (!tm) return nullptr;
+  for (auto& s : tm->slots) {
+    // a buffer that never got its last transfer becomes an error buffer, so that nobody waits for it forever
+    if (!s.finished) finish_definition(s.buffer, PJRT_Error_Code_ABORTED, "the transfer manager was destroyed before the buffer's last transfer");
+    if (!s.retrieved) { release_buffer_memory(s.buffer); delete s.buffer; }
+  }
+  delete tm;
   return nullptr;
 }
 
@@ -1415,6 +1593,15 @@ static PJRT_Api make_api() {
   B2X_SET(Client_AddressableMemories, Client_AddressableMemories); B2X_SET(Client_Compile, Client_Compile);
   B2X_SET(Client_DefaultDeviceAssignment, Client_DefaultDeviceAssignment); B2X_SET(Client_BufferFromHostBuffer, Client_BufferFromHostBuffer);
   B2X_SET(Client_UpdateGlobalProcessInfo, Client_UpdateGlobalProcessInfo); B2X_SET(Client_DmaMap, Client_DmaMap); B2X_SET(Client_DmaUnmap, Client_DmaUnmap);
+  B2X_SET(Client_CreateBuffersForAsyncHostToDevice, Client_CreateBuffersForAsyncHostToDevice);
+  B2X_SET(AsyncHostToDeviceTransferManager_Device, TransferManager_Device); B2X_SET(AsyncHostToDeviceTransferManager_BufferCount, TransferManager_BufferCount);
+  B2X_SET(AsyncHostToDeviceTransferManager_BufferSize, TransferManager_BufferSize);
+  B2X_SET(AsyncHostToDeviceTransferManager_RetrieveBuffer, TransferManager_RetrieveBuffer);
+  B2X_SET(AsyncHostToDeviceTransferManager_TransferData, TransferManager_TransferData);
+  B2X_SET(AsyncHostToDeviceTransferManager_TransferLiteral, TransferManager_TransferLiteral);
+  B2X_SET(AsyncHostToDeviceTransferManager_SetBufferError, TransferManager_SetBufferError);
+  B2X_SET(AsyncHostToDeviceTransferManager_AddMetadata, TransferManager_AddMetadata);
+  B2X_SET(AsyncHostToDeviceTransferManager_Destroy, TransferManager_Destroy);
   B2X_SET(Client_CreateUninitializedBuffer, Client_CreateUninitializedBuffer); B2X_SET(Client_CreateViewOfDeviceBuffer, Client_CreateViewOfDeviceBuffer);
   B2X_SET(Client_CreateErrorBuffer, Client_CreateErrorBuffer); B2X_SET(Client_Load, Client_Load);
   B2X_SET(DeviceDescription_Id, DeviceDescription_Id); B2X_SET(DeviceDescription_ProcessIndex, DeviceDescription_ProcessIndex);

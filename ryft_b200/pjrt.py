@@ -214,6 +214,31 @@ A = {
 }
 
 
+class ShapeSpecC(C.Structure):
+    """PJRT_ShapeSpec (crates/ryft-pjrt/src/transfers.rs:800-812)."""
+    _fields_ = [("struct_size", _sz), ("extension_start", _vp), ("dims", C.POINTER(_i64)), ("num_dims", _sz), ("element_type", _i)]
+
+
+_TM = "AsyncHostToDeviceTransferManager_"
+A.update({
+    "Client_CreateBuffersForAsyncHostToDevice": _args("CreateBuffersForAsyncH2D", [("client", _vp), ("shape_specs", C.POINTER(ShapeSpecC)), ("num_shape_specs", _sz),
+                                                                                   ("device_layouts", _vp), ("num_device_layouts", _sz), ("memory", _vp),
+                                                                                   ("transfer_manager", _vp)]),
+    _TM + "Device": _args("TmDevice", [("transfer_manager", _vp), ("device_out", _vp)]),
+    _TM + "BufferCount": _args("TmBufferCount", [("transfer_manager", _vp), ("buffer_count", _sz)]),
+    _TM + "BufferSize": _args("TmBufferSize", [("transfer_manager", _vp), ("buffer_index", _i), ("buffer_size", _sz)]),
+    _TM + "RetrieveBuffer": _args("TmRetrieveBuffer", [("transfer_manager", _vp), ("buffer_index", _i), ("buffer_out", _vp)]),
+    _TM + "TransferData": _args("TmTransferData", [("transfer_manager", _vp), ("buffer_index", _i), ("data", _vp), ("offset", _i64), ("transfer_size", _i64),
+                                                   ("is_last_transfer", C.c_bool), ("done_with_h2d_transfer", _vp)]),
+    _TM + "TransferLiteral": _args("TmTransferLiteral", [("transfer_manager", _vp), ("buffer_index", _i), ("data", _vp), ("shape_dims", C.POINTER(_i64)),
+                                                         ("shape_num_dims", _sz), ("shape_element_type", _i), ("shape_layout", _vp), ("done_with_h2d_transfer", _vp)]),
+    _TM + "SetBufferError": _args("TmSetBufferError", [("transfer_manager", _vp), ("buffer_index", _i), ("error_code", _i), ("error_message", C.c_char_p),
+                                                       ("error_message_size", _sz)]),
+    _TM + "AddMetadata": _args("TmAddMetadata", [("transfer_manager", _vp), ("transfer_metadata", _vp), ("num_metadata", _sz)]),
+    _TM + "Destroy": _args("TmDestroy", [("transfer_manager", _vp)]),
+})
+
+
 class ProgramC(C.Structure):
     _fields_ = [("struct_size", _sz), ("extension_start", _vp), ("code", _vp), ("code_size", _sz), ("format", _vp), ("format_size", _sz)]
 
@@ -915,6 +940,64 @@ class Layout:
             self.handle = None
 
 
+class HostToDeviceTransferManager:
+    """`HostToDeviceTransferManager` (crates/ryft-pjrt/src/transfers.rs:39-349): device buffers created up front and
+    filled later, chunk by chunk; a buffer becomes ready with its last chunk.  Host data passed to `transfer_data` /
+    `transfer_literal` is kept alive by the returned event until the copy has read it."""
+
+    def __init__(self, client: "Client", handle: int):
+        self.client, self.api, self.handle = client, client.api, handle
+
+    def _call(self, name: str, **fields):
+        a = A[_TM + name](); a.transfer_manager = self.handle
+        for k, v in fields.items():
+            setattr(a, k, v)
+        self.api.call(_TM + name, a)
+        return a
+
+    def device(self) -> "Device":
+        return Device(self.client, self._call("Device").device_out)
+
+    def buffer_count(self) -> int:
+        return int(self._call("BufferCount").buffer_count)
+
+    def buffer_on_device_size_in_bytes(self, index: int) -> int:
+        return int(self._call("BufferSize", buffer_index=index).buffer_size)
+
+    def retrieve_buffer(self, index: int) -> "Buffer":
+        return Buffer(self.client, self._call("RetrieveBuffer", buffer_index=index).buffer_out)
+
+    def transfer_data(self, index: int, data: bytes, offset: int, is_last_transfer: bool) -> "Event":
+        buf = C.create_string_buffer(bytes(data), len(data))
+        a = self._call("TransferData", buffer_index=index, data=C.addressof(buf), offset=offset, transfer_size=len(data), is_last_transfer=is_last_transfer)
+        return Event(self.api, a.done_with_h2d_transfer, keep=buf)
+
+    def transfer_literal(self, index: int, data: bytes, buffer_type: int, dims: Sequence[int]) -> "Event":
+        buf = C.create_string_buffer(bytes(data), len(data))
+        d = (_i64 * max(len(dims), 1))(*dims)
+        a = self._call("TransferLiteral", buffer_index=index, data=C.addressof(buf), shape_dims=C.cast(d, C.POINTER(_i64)), shape_num_dims=len(dims),
+                       shape_element_type=int(buffer_type))
+        return Event(self.api, a.done_with_h2d_transfer, keep=(buf, d))
+
+    def set_error(self, index: int, code: int, message: str) -> None:
+        m = message.encode()
+        self._call("SetBufferError", buffer_index=index, error_code=code, error_message=m, error_message_size=len(m))
+
+    def add_metadata(self, metadata: Dict[str, object]) -> None:
+        self._call("AddMetadata", transfer_metadata=None, num_metadata=0)   # the plugin has nothing to attach metadata to
+
+    def close(self) -> None:
+        if self.handle:
+            self._call("Destroy")
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class KeyValueStore:
     """Interface of the store behind the client's kv callbacks (crates/ryft-pjrt/src/clients.rs:575-640)."""
 
@@ -1138,6 +1221,20 @@ class Client:
         a.element_type = int(buffer_type); a.device = device.handle; a.stream = stream
         self.api.call("Client_CreateViewOfDeviceBuffer", a)
         return Buffer(self, a.buffer, keep=keep)
+
+    def host_to_device_transfer_manager(self, specifications: Sequence[tuple], device: Optional[Device] = None) -> "HostToDeviceTransferManager":
+        """`Client::host_to_device_transfer_manager` (crates/ryft-pjrt/src/transfers.rs:351-420); `specifications` are
+        (buffer type, dims) pairs, the buffers are created in `device`'s default memory."""
+        device = device or self.addressable_devices()[0]
+        specs = (ShapeSpecC * max(len(specifications), 1))()
+        keep = []
+        for i, (bt, dims) in enumerate(specifications):
+            d = (_i64 * max(len(dims), 1))(*dims); keep.append(d)
+            specs[i].struct_size = C.sizeof(ShapeSpecC); specs[i].dims = C.cast(d, C.POINTER(_i64)); specs[i].num_dims = len(dims); specs[i].element_type = int(bt)
+        a = A["Client_CreateBuffersForAsyncHostToDevice"](); a.client = self.handle
+        a.shape_specs = C.cast(specs, C.POINTER(ShapeSpecC)); a.num_shape_specs = len(specifications); a.memory = device.default_memory()
+        self.api.call("Client_CreateBuffersForAsyncHostToDevice", a)
+        return HostToDeviceTransferManager(self, a.transfer_manager)
 
     def error_buffer(self, code: int, message: str, buffer_type: BufferType, dims: Sequence[int], device: Optional[Device] = None) -> Buffer:
         device = device or self.addressable_devices()[0]

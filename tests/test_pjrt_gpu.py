@@ -240,3 +240,64 @@ def test_memory_descriptions_extension(client):
     descs, default = dev.memory_descriptions()
     assert descs and all(kind and kind_id != 0 for kind, kind_id in descs)
     assert 0 <= default < len(descs) and descs[default][0] == "device"
+
+
+def test_host_to_device_transfer_manager(client):
+    """crates/ryft-pjrt/src/transfers.rs:1008-1073: chunked transfers, a failed transfer, and mixed data / literal
+    transfers through `PJRT_Client_CreateBuffersForAsyncHostToDevice`."""
+    device = client.addressable_devices()[0]
+    spec = (pjrt.BufferType.U8, [8])
+
+    # a successful transfer in two chunks
+    manager = client.host_to_device_transfer_manager([spec], device)
+    assert manager.device().id == device.id and manager.buffer_count() == 1 and manager.buffer_on_device_size_in_bytes(0) == 8
+    manager.transfer_data(0, bytes([1, 3, 5, 7]), 0, False)
+    manager.transfer_data(0, bytes([9, 11, 13, 15]), 4, True).await_()
+    manager.add_metadata({"4": "2"})
+    buffer = manager.retrieve_buffer(0)
+    buffer.ready().await_()
+    assert buffer.copy_to_host().await_() == bytes([1, 3, 5, 7, 9, 11, 13, 15])
+
+    # the buffer may be retrieved, and its ready event asked for, before the last chunk is sent
+    manager = client.host_to_device_transfer_manager([spec], device)
+    early = manager.retrieve_buffer(0)
+    ready = early.ready()
+    assert not ready.ready()
+    manager.transfer_data(0, bytes(range(8)), 0, True).await_()
+    ready.await_()
+    assert early.copy_to_host().await_() == bytes(range(8))
+    with pytest.raises(pjrt.PjrtError):
+        manager.retrieve_buffer(0)                      # only once
+    with pytest.raises(pjrt.PjrtError):
+        manager.transfer_data(0, bytes(8), 0, True)     # the buffer is complete
+    with pytest.raises(pjrt.PjrtError):
+        manager.buffer_on_device_size_in_bytes(1)       # out of range
+
+    # a failed transfer
+    manager = client.host_to_device_transfer_manager([spec], device)
+    manager.transfer_data(0, bytes([1, 3, 5, 7]), 0, False)
+    manager.set_error(0, 10, "test error")              # ABORTED
+    buffer = manager.retrieve_buffer(0)
+    with pytest.raises(pjrt.PjrtError) as e:
+        buffer.ready().await_()
+    assert e.value.code == 10 and "test error" in str(e.value)
+
+    # data and literal transfers mixed; a second literal for a complete buffer is refused
+    manager = client.host_to_device_transfer_manager([spec, spec], device)
+    assert manager.buffer_count() == 2 and manager.buffer_on_device_size_in_bytes(1) == 8
+    manager.transfer_data(0, bytes(range(1, 9)), 0, True).await_()
+    manager.transfer_literal(1, bytes(range(20, 28)), *spec).await_()
+    with pytest.raises(pjrt.PjrtError):
+        manager.transfer_literal(1, bytes(range(30, 38)), *spec)
+    b0, b1 = manager.retrieve_buffer(0), manager.retrieve_buffer(1)
+    b0.ready().await_(); b1.ready().await_()
+    assert b0.copy_to_host().await_() == bytes(range(1, 9)) and b1.copy_to_host().await_() == bytes(range(20, 28))
+    with pytest.raises(pjrt.PjrtError):
+        manager.transfer_literal(0, bytes(4), pjrt.BufferType.U8, [4])      # wrong shape
+
+    # a manager destroyed before a buffer's last transfer leaves an error buffer behind, not a waiter
+    manager = client.host_to_device_transfer_manager([spec], device)
+    orphan = manager.retrieve_buffer(0)
+    manager.close()
+    with pytest.raises(pjrt.PjrtError):
+        orphan.ready().await_()
