@@ -337,21 +337,28 @@ def extras(client, peaks, local) -> dict:
     return out
 
 
-def cpu_baseline(config: str, sample_tokens: int = 512) -> dict:
-    """The oracle timed on the host cores on a bounded sample of the workload (tokens cut to `sample_tokens`)."""
+def cpu_baseline(config: str, target_seconds: float = 12.0) -> dict:
+    """The oracle timed on the host cores on a bounded sample of the workload: the token count is cut so that the run
+    takes about `target_seconds` on this host (a 512-token probe sets the rate; the full 8192 tokens if the host is fast
+    enough)."""
     from oracle import stablehlo_eval as ev
     from ryft_b200 import configs
     if config not in ("c5", "c4"):
         return {"value": None, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port", "sample": "not timed for this config"}
-    text = configs.c4_program(sample_tokens, D_FULL, F_FULL)
-    ins = configs.c4_inputs(sample_tokens, D_FULL, F_FULL, seed=4)
-    mod = ev.parse(text)
-    t0 = time.perf_counter()
-    ev.evaluate(mod, [ins], fast_dot=True)
-    dt = time.perf_counter() - t0
-    flops = configs.C4_GEMM_FLOPS(sample_tokens, D_FULL, F_FULL)
+
+    def run(tokens: int) -> float:
+        text = configs.c4_program(tokens, D_FULL, F_FULL)
+        ins = configs.c4_inputs(tokens, D_FULL, F_FULL, seed=4)
+        mod = ev.parse(text)
+        t0 = time.perf_counter()
+        ev.evaluate(mod, [ins], fast_dot=True)
+        return time.perf_counter() - t0
+    probe = run(512)
+    tokens = int(min(T_FULL, max(512, 512 * target_seconds / max(probe, 1e-3)))) // 512 * 512
+    dt = run(tokens) if tokens > 512 else probe
+    flops = configs.C4_GEMM_FLOPS(tokens, D_FULL, F_FULL)
     return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port", "seconds": dt,
-            "sample": f"{sample_tokens} of {T_FULL} tokens, full d={D_FULL} ff={F_FULL}; NumPy oracle, f32 BLAS GEMMs on all host threads"}
+            "sample": f"{tokens} of {T_FULL} tokens, full d={D_FULL} ff={F_FULL}; NumPy oracle, f32 BLAS GEMMs on all host threads"}
 
 
 def run_reference(args) -> dict:
