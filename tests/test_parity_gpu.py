@@ -324,3 +324,51 @@ def test_c4_gradient_matches_finite_difference(client):
     lp = run_oracle(text, [x, w1, w2p])[2]
     fd = (float(lp) - float(loss)) / step
     assert np.sign(fd) == np.sign(dw2[i, j]) and abs(fd - dw2[i, j]) <= 0.35 * abs(dw2[i, j])
+
+
+# ---- ragged edges of the specialised GEMM epilogues, empty tensors, NaN rows ---------------------------------------------
+
+@pytest.mark.parametrize("B,M,K,N", [(3, 200, 72, 264), (1, 130, 128, 72), (2, 129, 64, 8)])
+def test_c2_epilogue_with_ragged_tiles(client, B, M, K, N):
+    """Config 2's program at sizes where neither M nor N is a multiple of the 128 x BN tile: the bulk tensor stores of
+    the single-store epilogue must clip at the end of every batch's rows and at the last columns."""
+    check_program(client, configs.c2_program(B, M, K, N), configs.c2_inputs(B, M, K, N), f"c2 ragged {B}x{M}x{K}x{N}")
+
+
+def test_c4_gradients_with_ragged_tiles(client):
+    """Config 4 with token / feature counts that leave partial tiles in every GEMM (the two-store epilogue then works on
+    row blocks shorter than 32, the f32 gradient stores on partial column strips)."""
+    T, D, F = 200, 136, 264
+    check_program(client, configs.c4_program(T, D, F), configs.c4_inputs(T, D, F), "c4 ragged")
+
+
+def test_fused_attention_propagates_nan_like_the_unfused_program(client):
+    """A NaN key poisons exactly the rows that may attend to it (row >= key index under the causal mask): reduce-max
+    and reduce-add propagate NaN in the program as written, and the fused kernel must give the same rows of NaN."""
+    import ryft_b200
+    B, H, S, D = 1, 1, 256, 128
+    text = configs.c3_program(B, H, S, D)
+    assert "attention " in ryft_b200.plan_dump(text)
+    q, k, v = configs.c3_inputs(B, H, S, D)
+    k = k.copy()
+    k[0, 0, 140, 5] = np.float32("nan")
+    (got,) = run_gpu(client, text, [q, k, v])
+    (want,) = run_oracle(text, [q, k, v])
+    nan_rows_got = np.isnan(got.astype(np.float32)).all(axis=-1)[0, 0]
+    nan_rows_want = np.isnan(want.astype(np.float32)).all(axis=-1)[0, 0]
+    assert np.array_equal(nan_rows_want, np.arange(S) >= 140)
+    assert np.array_equal(nan_rows_got, nan_rows_want)
+    assert np.isfinite(got.astype(np.float32)[0, 0, :140]).all()
+
+
+def test_empty_tensors(client):
+    """Zero-element operands: elementwise ops give empty results, a reduction over an empty dimension gives its init
+    value, and nothing is launched for them."""
+    from ryft_b200.stablehlo import Builder
+    b = Builder()
+    x = b.arg([0, 4], "f32"); y = b.arg([0, 4], "f32")
+    s = b.add(x, y)
+    r = b.reduce(s, b.constant(3.0, [], "f32"), "add", [0])
+    text = b.build(s, r)
+    got = check_program(client, text, [np.zeros((0, 4), np.float32), np.zeros((0, 4), np.float32)], "empty")
+    assert got[0].shape == (0, 4) and got[1].tolist() == [3.0, 3.0, 3.0, 3.0]
