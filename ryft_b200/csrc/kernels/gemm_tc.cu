@@ -93,6 +93,7 @@ extern "C" int b2x_launch_gemm_tc(const B2xGemmArgs* a, const B2xVmProgram* epil
   if (p.num_tiles >= (1ll << 31)) return (int)cudaErrorInvalidValue;
   p.k_blocks = (int)((a->K + BK - 1) / BK);
   p.transposed = a->K <= 8192 ? 1 : 0;
+  p.epi_groups = p.k_blocks <= 8 ? 1 : 2;
   {
     // A slab of a group ~ 32 MiB (a quarter of the 126 MB L2)
     const int64_t slab_per_m_tile = (int64_t)TC_BM * a->K * es;

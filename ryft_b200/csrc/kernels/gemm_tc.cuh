@@ -33,6 +33,7 @@ struct TcParams {
   int64_t num_tiles;
   int32_t k_blocks;
   int32_t tma_store;   // the single-store epilogue writes through the output tensor map
+  int32_t epi_groups;  // 2: one group of eight epilogue warps per accumulator; 1: all sixteen on every tile (short K)
   int32_t transposed;  // multi-store epilogues on short-K problems go through shared memory (see tc_transposed_epilogue)
   int32_t group_m;     // m-tiles per raster group: a group's A slab stays in L2 while its n-tiles stream by
   uint32_t idesc;
@@ -45,8 +46,9 @@ constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;
 // The epilogue warps form two groups of eight, one per TMEM accumulator: group g finishes tiles g, g + 2, ... of the CTA
 // on its own.  The groups drift out of phase (one reads TMEM or stores while the other is in its MUFU-heavy part), and
 // each warp's per-tile set-up is amortised over twice as many columns as with all sixteen warps on every tile.
-constexpr int TC_EPI_GROUP = TC_EPI_WARPS / 2;
-constexpr int TC_COL_PARTS = TC_EPI_GROUP / 4;
+// That holds when a tile's main loop is long.  With a short K (config 2: two k-blocks per tile) the epilogue is the
+// bottleneck and a group would sit idle while the MMA refills its accumulator, so there all sixteen warps finish every
+// tile together and the accumulators alternate (TcParams::epi_groups = 1).
 
 // Tile order: batches outermost; inside a batch, groups of `group_m` m-tiles, and inside a group m fastest.  Tiles that
 // run at the same time then share a few rows of A and a few columns of B, and consecutive waves reuse the group's A
@@ -146,9 +148,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-    for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, TC_EPI_GROUP); }
+    for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, TC_EPI_WARPS / p.epi_groups); }
     mbar_init(bar_drain, 1);
-    for (int r = 0; r < RING; r++) { mbar_init(bar_sfull + 8 * r, 1); mbar_init(bar_sempty + 8 * r, TC_EPI_GROUP + 1); }
+    for (int r = 0; r < RING; r++) { mbar_init(bar_sfull + 8 * r, 1); mbar_init(bar_sempty + 8 * r, TC_EPI_WARPS / p.epi_groups + 1); }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -177,6 +179,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         if (t >= p.num_tiles) t = -1;
         tile_ring[slot] = (int32_t)t;
         mbar_arrive(bar_sfull + 8 * slot);
+        if (t < 0 && p.epi_groups == 1) break;
         if (t < 0) {
           // the other epilogue group reads the ring entry after this one: it gets its own end marker
           const int64_t nxt = local + 1;
@@ -258,11 +261,13 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   } else {
     // ------------------------------------------------ epilogue ------------------------------------------------------
     const int quad = warp & 3;              // TMEM lanes [32*quad, 32*quad + 32)
-    const int group = (warp - 2) / TC_EPI_GROUP;                 // accumulator this warp serves
-    const int part = ((warp - 2) % TC_EPI_GROUP) >> 2;           // column chunks part, part + TC_COL_PARTS, ...
+    const int group_warps = TC_EPI_WARPS / p.epi_groups;
+    const int group = (warp - 2) / group_warps;                  // with two groups: the accumulator this warp serves
+    const int part = ((warp - 2) % group_warps) >> 2;            // column chunks part, part + col_parts, ...
+    const int col_parts = group_warps / 4;
     bool ok = true;
     const VmRowPlan rplan = vm_row_plan(epi, (uint32_t)p.N);
-    for (int64_t local = group; ok; local += 2) {
+    for (int64_t local = group; ok; local += p.epi_groups) {
       const int slot = (int)(local & (RING - 1));
       if (!mbar_wait(bar_sfull + 8 * slot, (uint32_t)((local / RING) & 1), abort_flag, status, 7)) { ok = false; break; }
       const int64_t t = tile_ring[slot];
@@ -289,7 +294,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         if (__all_sync(0xffffffffu, blk.ok)) {
           const uint32_t stg = smem_base + SM::STAGING_OFFSET + (uint32_t)(warp - 2) * 2048u;
 #pragma unroll 1
-          for (int c = part; c < BN / 32; c += TC_COL_PARTS) {
+          for (int c = part; c < BN / 32; c += col_parts) {
             uint32_t r[32];
             tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32), r);
             tc_wait_ld();
@@ -337,7 +342,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
           const bool row_vec = __all_sync(0xffffffffu, vrow.vec);
           if (row_vec) {
 #pragma unroll 1
-            for (int c = part; c < BN / 32; c += TC_COL_PARTS) {
+            for (int c = part; c < BN / 32; c += col_parts) {
               uint32_t r[32];
               tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32), r);
               tc_wait_ld();
@@ -384,7 +389,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         if constexpr (ID != 0) {
           // specialised epilogue: straight-line code, four 8-wide vectors per 32-column TMEM load
 #pragma unroll 1
-          for (int c = part; c < BN / 32; c += TC_COL_PARTS) {
+          for (int c = part; c < BN / 32; c += col_parts) {
             uint32_t r[32];
             tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32), r);
             tc_wait_ld();
@@ -405,7 +410,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         } else {
           // interpreted epilogue: one inlined copy of the interpreter, fed 8 columns at a time
 #pragma unroll 1
-          for (int c = part; c < BN / 8; c += TC_COL_PARTS) {
+          for (int c = part; c < BN / 8; c += col_parts) {
             uint32_t a0[8], out[8];
             tmem_ld_32x8(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 8), a0);
             tc_wait_ld();
