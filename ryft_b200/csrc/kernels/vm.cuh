@@ -868,11 +868,10 @@ __host__ __device__ constexpr int vm_static_store_tensor() {
 }
 // Row-wise run whose store goes to the staging addresses in `stage` instead of global memory.
 template <int ID>
-__device__ __forceinline__ void vm_run_row_stage(const B2xVmProgram& P, const VmRow& R, uint32_t col, uint32_t stage0, uint32_t stage1,
+__device__ __forceinline__ void vm_run_row_stage(const B2xVmProgram& P, VmRow& R, uint32_t col, uint32_t stage0, uint32_t stage1,
                                                  const uint32_t (&acc0)[8], uint32_t (&acc)[8]) {
-  VmRowAddr ra = R.addr;
-  ra.stage[0] = stage0; ra.stage[1] = stage1;
-  vm_run_core<8, ID, true, true>(P, R.coord, R.off, ra, (int64_t)col, acc0, acc);
+  R.addr.stage[0] = stage0; R.addr.stage[1] = stage1;
+  vm_run_core<8, ID, true, true>(P, R.coord, R.off, R.addr, (int64_t)col, acc0, acc);
 }
 
 // Signature hash of a program (structure only: ops, operand kinds, classes, rounding, tensor element types).
