@@ -289,8 +289,7 @@ def run_own(args) -> dict:
         "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "steps_per_s": args.steps / (ms * 1e-3), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16 operands, f32 accumulate", "data": "synthetic (seeded N(0,1) activations, N(0,0.02) weights)",
-        "config": {"workload": {"c5": f"config 5: MLP fwd+bwd gradient step, tokens {T_FULL} x d {D_FULL} x ff {F_FULL} per replica, all_reduce(sum) of "
-                                      f"f32 dW1+dW2 ({2 * D_FULL * F_FULL * 4} B) over {n_rep} replica(s), divide by replica count",
+        "config": {"workload": {"c5": c5_workload(n_rep),
                                 "c4": "config 4: MLP fwd+bwd gradient step on one GPU", "c2": "config 2: batched bf16 dot_general + bias + tanh + convert",
                                 "c3": "config 3: causal attention written out in StableHLO", "c1": "config 1: f32 dot_general 512x768x512",
                                 "ew": "micro: config 2's epilogue chain standalone, tanh(f32[32,2048,2048] + bias) -> bf16",
@@ -335,6 +334,11 @@ def extras(client, peaks, local) -> dict:
         except Exception as e:  # report, never hide
             out[cfg] = {"error": str(e)}
     return out
+
+
+def c5_workload(n_rep: int) -> str:
+    return (f"config 5: MLP fwd+bwd gradient step, tokens {T_FULL} x d {D_FULL} x ff {F_FULL} per replica, all_reduce(sum) of "
+            f"f32 dW1+dW2 ({2 * D_FULL * F_FULL * 4} B) over {n_rep} replica(s), divide by replica count")
 
 
 def cpu_baseline(config: str, target_seconds: float = 12.0) -> dict:
@@ -382,7 +386,9 @@ def run_reference(args) -> dict:
     sample_txt = f"{sample} of {T_FULL} tokens per step, full d={D_FULL} ff={F_FULL}; NumPy oracle (port of StableHLO semantics), f32 BLAS on all host threads"
     return {"impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 operands, f32 accumulate",
-            "data": "synthetic", "config": {"workload": "config 5 / config 4 gradient step (CPU, bounded token sample)", "replicas": 1},
+            "data": "synthetic (seeded N(0,1) activations, N(0,0.02) weights)",
+            "config": {"workload": c5_workload(max(args.gpus, 1)), "replicas": max(args.gpus, 1), "parallelism": f"dp{max(args.gpus, 1)}",
+                       "cpu_sample": "one replica's step on a bounded token sample (see cpu_baseline.sample); rank 0 only"},
             "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port", "sample": sample_txt},
             "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "note": "the reference runs this path inside OpenXLA's CPU PJRT plugin, which cannot be built or fetched in this environment; the CPU oracle is timed instead"}
