@@ -232,22 +232,39 @@ def run_own(args) -> dict:
             return client.buffer(pinned.data_ptr(), pjrt.BufferType.BF16, list(x.shape), device=dev, semantics=1)
 
         def run_steps(n):
-            # the input pipeline a training loop uses: step i+1's tokens are uploaded while step i computes; every step
-            # still uploads its own 64 MiB of tokens and reads its own loss back inside the timed region
+            # the input pipeline of a training loop: step i+1's tokens are uploaded while step i computes, and with
+            # --e2e-depth 2 step i+1 is also enqueued before the host waits for loss i.  Every step uploads its own 64 MiB
+            # of tokens and has its own loss read back inside the timed region.
             xb = upload()
+            pending = None
+            hosts = [np.zeros(4, dtype=np.uint8), np.zeros(4, dtype=np.uint8)]
             for i in range(n):
                 outs = exe.execute([pjrt.ExecutionDeviceInputs([xb, bufs[1], bufs[2]])])
                 if i + 1 < n:
                     xb = upload()
-                outs[0].outputs[2].copy_to_host(loss_host).await_()
+                ev = outs[0].outputs[2].copy_to_host(hosts[i & 1])
+                if args.e2e_depth <= 1:
+                    ev.await_()
+                else:
+                    if pending is not None:
+                        pending.await_()
+                    pending = ev
+            if pending is not None:
+                pending.await_()
+            loss_host[:] = hosts[(n - 1) & 1]
         run_steps(2)
+        # the upload alone, for reading the end-to-end figure: when it takes longer than a step, the host link bounds e2e
+        t_up = time.perf_counter()
+        upload().ready().await_()
+        h2d_ms = (time.perf_counter() - t_up) * 1e3
         _barrier(world)
         w0 = time.perf_counter()
         run_steps(e2e_steps)
         _barrier(world)
         wall = _max_over_ranks(time.perf_counter() - w0, world)
         e2e = {"value": flops_per_replica * n_rep * e2e_steps / wall / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": int(x.nbytes) * n_rep,
-               "d2h_bytes_per_step": 4 * n_rep, "ms_per_step": wall / e2e_steps * 1e3, "loss": float(loss_host.view(np.float32)[0])}
+               "d2h_bytes_per_step": 4 * n_rep, "ms_per_step": wall / e2e_steps * 1e3, "loss": float(loss_host.view(np.float32)[0]),
+               "h2d_alone_ms": h2d_ms, "h2d_alone_gb_per_s": x.nbytes / (h2d_ms * 1e-3) / 1e9}
 
     # ---- roofline of the dominant kernel (tcgen05 GEMM) from the per-step CUDA events of the timed region ----
     peaks = _peaks()
@@ -401,6 +418,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--config", default="c5", choices=["c1", "c2", "c3", "c4", "c5", "ew", "red"])
+    ap.add_argument("--e2e-depth", type=int, default=2, help="steps the end-to-end loop keeps in flight (1 or 2)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
     args = ap.parse_args()
