@@ -779,6 +779,52 @@ typedef struct PJRT_MemoryDescriptions_Extension {
   PJRT_Error* (*PJRT_MemoryDescription_Kind)(PJRT_MemoryDescription_Kind_Args*);
 } PJRT_MemoryDescriptions_Extension;
 
+/* ABI-version extension (crates/ryft-pjrt/src/extensions/abi_version.rs:499-770, version 1): the serialization
+ * generation of the runtime and of an executable, and whether they fit together.  The Args of this extension carry no
+ * `extension_start` field.  The protobuf form is `{1: uint64 platform, 2: bytes version}`
+ * (crates/ryft-xla-sys/src/protos.rs:3812-3838); this plugin's `version` payload is two varints:
+ * serialization generation, SM architecture (100). */
+#define PJRT_Extension_Type_AbiVersion 20
+#define B2X_ABI_PLATFORM_ID 0x6232785f63756461ull /* "b2x_cuda" */
+typedef struct PJRT_RuntimeAbiVersion PJRT_RuntimeAbiVersion;
+typedef struct PJRT_ExecutableAbiVersion PJRT_ExecutableAbiVersion;
+typedef struct PJRT_SerializedProto PJRT_SerializedProto;
+typedef struct { size_t struct_size; PJRT_Client* client; PJRT_RuntimeAbiVersion* abi_version; /* out */ } PJRT_Client_RuntimeAbiVersion_Args;
+typedef struct { size_t struct_size; PJRT_Executable* executable; PJRT_ExecutableAbiVersion* abi_version; /* out */ } PJRT_Executable_GetAbiVersion_Args;
+typedef struct { size_t struct_size; PJRT_RuntimeAbiVersion* abi_version; } PJRT_RuntimeAbiVersion_Destroy_Args;
+typedef struct { size_t struct_size; const PJRT_RuntimeAbiVersion* abi_version; const PJRT_RuntimeAbiVersion* other_abi_version; } PJRT_RuntimeAbiVersion_IsCompatibleWithRuntime_Args;
+typedef struct { size_t struct_size; const PJRT_RuntimeAbiVersion* abi_version; const PJRT_ExecutableAbiVersion* executable_abi_version; } PJRT_RuntimeAbiVersion_IsCompatibleWithExecutable_Args;
+typedef struct {
+  size_t struct_size; const PJRT_RuntimeAbiVersion* abi_version;
+  const char* serialized_proto; size_t serialized_proto_size;                                     /* out */
+  PJRT_SerializedProto* serialized_proto_holder; void (*serialized_proto_deleter)(PJRT_SerializedProto*);  /* out */
+} PJRT_RuntimeAbiVersion_ToProto_Args;
+typedef struct { size_t struct_size; const PJRT_RuntimeAbiVersion* abi_version; uint64_t platform_id; /* out */ } PJRT_RuntimeAbiVersion_PlatformId_Args;
+typedef struct { size_t struct_size; PJRT_ExecutableAbiVersion* abi_version; } PJRT_ExecutableAbiVersion_Destroy_Args;
+typedef struct {
+  size_t struct_size; const PJRT_ExecutableAbiVersion* abi_version;
+  const char* serialized_proto; size_t serialized_proto_size;                                     /* out */
+  PJRT_SerializedProto* serialized_proto_holder; void (*serialized_proto_deleter)(PJRT_SerializedProto*);  /* out */
+} PJRT_ExecutableAbiVersion_ToProto_Args;
+typedef struct { size_t struct_size; const PJRT_ExecutableAbiVersion* abi_version; uint64_t platform_id; /* out */ } PJRT_ExecutableAbiVersion_PlatformId_Args;
+typedef struct { size_t struct_size; const char* serialized_proto; size_t serialized_proto_size; PJRT_RuntimeAbiVersion* abi_version; /* out */ } PJRT_RuntimeAbiVersion_FromProto_Args;
+typedef struct { size_t struct_size; const char* serialized_proto; size_t serialized_proto_size; PJRT_ExecutableAbiVersion* abi_version; /* out */ } PJRT_ExecutableAbiVersion_FromProto_Args;
+typedef struct PJRT_AbiVersion_Extension {
+  PJRT_Extension_Base base;
+  PJRT_Error* (*PJRT_Client_RuntimeAbiVersion)(PJRT_Client_RuntimeAbiVersion_Args*);
+  PJRT_Error* (*PJRT_Executable_GetAbiVersion)(PJRT_Executable_GetAbiVersion_Args*);
+  PJRT_Error* (*PJRT_RuntimeAbiVersion_Destroy)(PJRT_RuntimeAbiVersion_Destroy_Args*);
+  PJRT_Error* (*PJRT_RuntimeAbiVersion_IsCompatibleWithRuntime)(PJRT_RuntimeAbiVersion_IsCompatibleWithRuntime_Args*);
+  PJRT_Error* (*PJRT_RuntimeAbiVersion_IsCompatibleWithExecutable)(PJRT_RuntimeAbiVersion_IsCompatibleWithExecutable_Args*);
+  PJRT_Error* (*PJRT_RuntimeAbiVersion_ToProto)(PJRT_RuntimeAbiVersion_ToProto_Args*);
+  PJRT_Error* (*PJRT_RuntimeAbiVersion_PlatformId)(PJRT_RuntimeAbiVersion_PlatformId_Args*);
+  PJRT_Error* (*PJRT_ExecutableAbiVersion_Destroy)(PJRT_ExecutableAbiVersion_Destroy_Args*);
+  PJRT_Error* (*PJRT_ExecutableAbiVersion_ToProto)(PJRT_ExecutableAbiVersion_ToProto_Args*);
+  PJRT_Error* (*PJRT_ExecutableAbiVersion_PlatformId)(PJRT_ExecutableAbiVersion_PlatformId_Args*);
+  PJRT_Error* (*PJRT_RuntimeAbiVersion_FromProto)(PJRT_RuntimeAbiVersion_FromProto_Args*);
+  PJRT_Error* (*PJRT_ExecutableAbiVersion_FromProto)(PJRT_ExecutableAbiVersion_FromProto_Args*);
+} PJRT_AbiVersion_Extension;
+
 /* Step-timing extension (no counterpart in the reference; private type id).  When enabled for a loaded executable,
  * every later execution brackets each plan step with CUDA events on the stream the step runs on.  `collect` waits
  * for the recorded executions, sums the device time per step and resets the record.  Arrays are borrowed from the

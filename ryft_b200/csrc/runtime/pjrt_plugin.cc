@@ -1539,6 +1539,116 @@ static PJRT_Error* MemDesc_Kind(PJRT_MemoryDescription_Kind_Args* a) {
   return nullptr;
 }
 
+// ---- ABI-version extension -----------------------------------------------------------------------------------------------
+// A version is (platform id, serialization generation, SM architecture).  The runtime reads executables of its own
+// generation or older, built for its own architecture.
+static constexpr uint64_t kSerializationGeneration = 1;  // the "B2XE1" container written by serialize_core
+static constexpr uint64_t kSmArchitecture = 100;
+struct AbiVersionValue { uint64_t platform = B2X_ABI_PLATFORM_ID, generation = kSerializationGeneration, sm = kSmArchitecture; };
+struct PJRT_RuntimeAbiVersion { AbiVersionValue v; };
+struct PJRT_ExecutableAbiVersion { AbiVersionValue v; };
+static void abi_put_varint(std::string* s, uint64_t v) { while (v >= 0x80) { s->push_back((char)(v | 0x80)); v >>= 7; } s->push_back((char)v); }
+static bool abi_get_varint(const unsigned char*& p, const unsigned char* end, uint64_t* out) {
+  uint64_t v = 0;
+  for (int shift = 0; shift < 64 && p < end; shift += 7) {
+    unsigned char b = *p++;
+    v |= (uint64_t)(b & 0x7f) << shift;
+    if (!(b & 0x80)) { *out = v; return true; }
+  }
+  return false;
+}
+static std::string abi_to_proto(const AbiVersionValue& v) {
+  std::string payload, s;
+  abi_put_varint(&payload, v.generation); abi_put_varint(&payload, v.sm);
+  abi_put_varint(&s, (1 << 3) | 0); abi_put_varint(&s, v.platform);
+  abi_put_varint(&s, (2 << 3) | 2); abi_put_varint(&s, payload.size()); s += payload;
+  return s;
+}
+static PJRT_Error* abi_from_proto(const char* data, size_t size, AbiVersionValue* out) {
+  if (!data && size) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "null ABI version proto");
+  const unsigned char* p = (const unsigned char*)data; const unsigned char* end = p + size;
+  AbiVersionValue v; v.platform = 0; bool have_payload = false;
+  while (p < end) {
+    uint64_t tag, n;
+    if (!abi_get_varint(p, end, &tag)) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "malformed ABI version proto");
+    int field = (int)(tag >> 3), wire = (int)(tag & 7);
+    if (wire == 0) {
+      if (!abi_get_varint(p, end, &n)) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "malformed ABI version proto");
+      if (field == 1) v.platform = n;
+    } else if (wire == 2) {
+      if (!abi_get_varint(p, end, &n) || n > (uint64_t)(end - p)) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "malformed ABI version proto");
+      if (field == 2) {
+        const unsigned char* q = p; const unsigned char* qe = p + n;
+        if (!abi_get_varint(q, qe, &v.generation) || !abi_get_varint(q, qe, &v.sm) || q != qe)
+          return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "the ABI version payload was not written by this plugin");
+        have_payload = true;
+      }
+      p += n;
+    } else if (wire == 1) { if (end - p < 8) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "malformed ABI version proto"); p += 8; }
+    else if (wire == 5) { if (end - p < 4) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "malformed ABI version proto"); p += 4; }
+    else return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "malformed ABI version proto");
+  }
+  if (v.platform != B2X_ABI_PLATFORM_ID) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "the ABI version belongs to another platform");
+  if (!have_payload) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "the ABI version proto has no version payload");
+  *out = v;
+  return nullptr;
+}
+static PJRT_Error* abi_check(const AbiVersionValue& runtime, const AbiVersionValue& other, bool other_is_executable) {
+  if (runtime.platform != other.platform) return make_error(PJRT_Error_Code_FAILED_PRECONDITION, "ABI versions of different platforms");
+  if (runtime.sm != other.sm)
+    return make_error(PJRT_Error_Code_FAILED_PRECONDITION, "built for SM " + std::to_string(other.sm) + ", this runtime drives SM " + std::to_string(runtime.sm));
+  if (other_is_executable ? other.generation > runtime.generation : other.generation != runtime.generation)
+    return make_error(PJRT_Error_Code_FAILED_PRECONDITION, "serialization generation " + std::to_string(other.generation) +
+                                                               " does not fit this runtime's generation " + std::to_string(runtime.generation));
+  return nullptr;
+}
+static void delete_blob_proto(PJRT_SerializedProto* p) { delete (SerializedBlob*)p; }
+template <typename Args> static PJRT_Error* abi_emit_proto(Args* a) {
+  if (!a->abi_version) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "null ABI version");
+  SerializedBlob* b = new SerializedBlob{abi_to_proto(a->abi_version->v)};
+  a->serialized_proto = b->bytes.data(); a->serialized_proto_size = b->bytes.size();
+  a->serialized_proto_holder = (PJRT_SerializedProto*)b; a->serialized_proto_deleter = delete_blob_proto;
+  return nullptr;
+}
+static PJRT_Error* Abi_ClientRuntime(PJRT_Client_RuntimeAbiVersion_Args* a) {
+  if (!a->client) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "null client");
+  a->abi_version = new PJRT_RuntimeAbiVersion(); return nullptr;
+}
+static PJRT_Error* Abi_Executable(PJRT_Executable_GetAbiVersion_Args* a) {
+  if (!a->executable) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "null executable");
+  a->abi_version = new PJRT_ExecutableAbiVersion(); return nullptr;
+}
+static PJRT_Error* Abi_RuntimeDestroy(PJRT_RuntimeAbiVersion_Destroy_Args* a) { delete a->abi_version; return nullptr; }
+static PJRT_Error* Abi_ExecutableDestroy(PJRT_ExecutableAbiVersion_Destroy_Args* a) { delete a->abi_version; return nullptr; }
+static PJRT_Error* Abi_RuntimeWithRuntime(PJRT_RuntimeAbiVersion_IsCompatibleWithRuntime_Args* a) {
+  if (!a->abi_version || !a->other_abi_version) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "null ABI version");
+  return abi_check(a->abi_version->v, a->other_abi_version->v, false);
+}
+static PJRT_Error* Abi_RuntimeWithExecutable(PJRT_RuntimeAbiVersion_IsCompatibleWithExecutable_Args* a) {
+  if (!a->abi_version || !a->executable_abi_version) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "null ABI version");
+  return abi_check(a->abi_version->v, a->executable_abi_version->v, true);
+}
+static PJRT_Error* Abi_RuntimeToProto(PJRT_RuntimeAbiVersion_ToProto_Args* a) { return abi_emit_proto(a); }
+static PJRT_Error* Abi_ExecutableToProto(PJRT_ExecutableAbiVersion_ToProto_Args* a) { return abi_emit_proto(a); }
+static PJRT_Error* Abi_RuntimePlatform(PJRT_RuntimeAbiVersion_PlatformId_Args* a) {
+  if (!a->abi_version) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "null ABI version");
+  a->platform_id = a->abi_version->v.platform; return nullptr;
+}
+static PJRT_Error* Abi_ExecutablePlatform(PJRT_ExecutableAbiVersion_PlatformId_Args* a) {
+  if (!a->abi_version) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "null ABI version");
+  a->platform_id = a->abi_version->v.platform; return nullptr;
+}
+static PJRT_Error* Abi_RuntimeFromProto(PJRT_RuntimeAbiVersion_FromProto_Args* a) {
+  AbiVersionValue v;
+  B2X_RETURN_IF_ERROR(abi_from_proto(a->serialized_proto, a->serialized_proto_size, &v));
+  a->abi_version = new PJRT_RuntimeAbiVersion{v}; return nullptr;
+}
+static PJRT_Error* Abi_ExecutableFromProto(PJRT_ExecutableAbiVersion_FromProto_Args* a) {
+  AbiVersionValue v;
+  B2X_RETURN_IF_ERROR(abi_from_proto(a->serialized_proto, a->serialized_proto_size, &v));
+  a->abi_version = new PJRT_ExecutableAbiVersion{v}; return nullptr;
+}
+
 // ---- table ----------------------------------------------------------------------------------------------------------------
 
 static PJRT_Api make_api() {
@@ -1546,10 +1656,27 @@ static PJRT_Api make_api() {
   static B2X_StepTiming_Extension timing_ext;
   static PJRT_Layouts_Extension layouts_ext;
   static PJRT_MemoryDescriptions_Extension memdesc_ext;
+  static PJRT_AbiVersion_Extension abi_ext;
+  memset(&abi_ext, 0, sizeof(abi_ext));
+  abi_ext.base.struct_size = sizeof(abi_ext);
+  abi_ext.base.extension_type = PJRT_Extension_Type_AbiVersion;
+  abi_ext.base.next = nullptr;
+  abi_ext.PJRT_Client_RuntimeAbiVersion = Abi_ClientRuntime;
+  abi_ext.PJRT_Executable_GetAbiVersion = Abi_Executable;
+  abi_ext.PJRT_RuntimeAbiVersion_Destroy = Abi_RuntimeDestroy;
+  abi_ext.PJRT_RuntimeAbiVersion_IsCompatibleWithRuntime = Abi_RuntimeWithRuntime;
+  abi_ext.PJRT_RuntimeAbiVersion_IsCompatibleWithExecutable = Abi_RuntimeWithExecutable;
+  abi_ext.PJRT_RuntimeAbiVersion_ToProto = Abi_RuntimeToProto;
+  abi_ext.PJRT_RuntimeAbiVersion_PlatformId = Abi_RuntimePlatform;
+  abi_ext.PJRT_ExecutableAbiVersion_Destroy = Abi_ExecutableDestroy;
+  abi_ext.PJRT_ExecutableAbiVersion_ToProto = Abi_ExecutableToProto;
+  abi_ext.PJRT_ExecutableAbiVersion_PlatformId = Abi_ExecutablePlatform;
+  abi_ext.PJRT_RuntimeAbiVersion_FromProto = Abi_RuntimeFromProto;
+  abi_ext.PJRT_ExecutableAbiVersion_FromProto = Abi_ExecutableFromProto;
   memset(&memdesc_ext, 0, sizeof(memdesc_ext));
   memdesc_ext.base.struct_size = sizeof(memdesc_ext);
   memdesc_ext.base.extension_type = PJRT_Extension_Type_MemoryDescriptions;
-  memdesc_ext.base.next = nullptr;
+  memdesc_ext.base.next = &abi_ext.base;
   memdesc_ext.PJRT_DeviceDescription_MemoryDescriptions = MemDesc_ForDevice;
   memdesc_ext.PJRT_MemoryDescription_Kind = MemDesc_Kind;
   memset(&layouts_ext, 0, sizeof(layouts_ext));

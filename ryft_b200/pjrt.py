@@ -81,6 +81,7 @@ def _args(name: str, fields):
 EXTENSION_TYPE_STREAM = 3          # crates/ryft-pjrt/src/lib.rs:183
 EXTENSION_TYPE_LAYOUTS = 4         # crates/ryft-pjrt/src/lib.rs:184
 EXTENSION_TYPE_MEMORY_DESCRIPTIONS = 6   # crates/ryft-pjrt/src/lib.rs:186
+EXTENSION_TYPE_ABI_VERSION = 20    # crates/ryft-pjrt/src/lib.rs:200
 EXTENSION_TYPE_STEP_TIMING = 0x62327801
 
 
@@ -740,6 +741,12 @@ class Executable:
         a = self._get("Executable_OutputMemoryKinds")
         return [_str(a.memory_kinds[i], a.memory_kind_sizes[i]) for i in range(a.num_outputs)]
 
+    def abi_version(self) -> "ExecutableAbiVersion":
+        """`Executable::abi_version` (crates/ryft-pjrt/src/extensions/abi_version.rs:51-62)."""
+        a = _AbiVersion._struct([("executable", _vp), ("abi_version", _vp)]); a.executable = self.handle
+        _AbiVersion._call(self.api, _AbiVersion._EXECUTABLE, a)
+        return ExecutableAbiVersion(self.api, a.abi_version)
+
     def fingerprint(self) -> str:
         a = self._get("Executable_Fingerprint"); return _str(a.executable_fingerprint, a.executable_fingerprint_size)
 
@@ -876,6 +883,128 @@ class LoadedExecutable:
                 self.handle = None
         except Exception:
             pass
+
+
+class _AbiVersion:
+    """Common part of `RuntimeAbiVersion` and `ExecutableAbiVersion` (crates/ryft-pjrt/src/extensions/abi_version.rs:
+    233-416): an owned handle of the ABI-version extension.  The extension's argument structs carry no
+    `extension_start` field (abi_version.rs:525-752)."""
+
+    # slots of PJRT_AbiVersion_Extension after the 24-byte base (abi_version.rs:754-769)
+    (_CLIENT_RUNTIME, _EXECUTABLE, _RT_DESTROY, _RT_WITH_RUNTIME, _RT_WITH_EXECUTABLE, _RT_TO_PROTO, _RT_PLATFORM, _EX_DESTROY,
+     _EX_TO_PROTO, _EX_PLATFORM, _RT_FROM_PROTO, _EX_FROM_PROTO) = range(12)
+    _DESTROY_SLOT = _TO_PROTO_SLOT = _PLATFORM_SLOT = -1
+
+    def __init__(self, api: "Api", handle: int):
+        self.api, self.handle = api, handle
+
+    @staticmethod
+    def _struct(fields):
+        return type("AbiArgs", (C.Structure,), {"_fields_": [("struct_size", _sz)] + list(fields)})()
+
+    @staticmethod
+    def _call(api: "Api", slot: int, args) -> None:
+        ext = api.extension(EXTENSION_TYPE_ABI_VERSION)
+        if not ext:
+            raise PjrtError(12, "the plugin has no ABI-version extension")
+        fp = C.c_void_p.from_address(ext + 24 + 8 * slot).value
+        if not fp:
+            raise PjrtError(12, "this function of the ABI-version extension is not implemented by the plugin")
+        args.struct_size = C.sizeof(args)
+        err = _FN(fp)(C.addressof(args))
+        if err:
+            raise api._take_error(err)
+
+    def platform_id(self) -> int:
+        a = self._struct([("abi_version", _vp), ("platform_id", C.c_uint64)]); a.abi_version = self.handle
+        self._call(self.api, self._PLATFORM_SLOT, a)
+        return a.platform_id
+
+    def serialize(self) -> bytes:
+        """The serialized `{1: platform, 2: version payload}` message (crates/ryft-xla-sys/src/protos.rs:3812-3838)."""
+        a = self._struct([("abi_version", _vp), ("serialized_proto", _vp), ("serialized_proto_size", _sz), ("serialized_proto_holder", _vp),
+                          ("serialized_proto_deleter", _vp)])
+        a.abi_version = self.handle
+        self._call(self.api, self._TO_PROTO_SLOT, a)
+        data = C.string_at(a.serialized_proto, a.serialized_proto_size)
+        if a.serialized_proto_deleter:
+            C.CFUNCTYPE(None, _vp)(a.serialized_proto_deleter)(a.serialized_proto_holder)
+        return data
+
+    def proto(self) -> Dict[str, object]:
+        """The message decoded into `{"platform": int, "version": bytes}`."""
+        data, pos, out = self.serialize(), 0, {"platform": 0, "version": b""}
+
+        def varint():
+            nonlocal pos
+            v = shift = 0
+            while True:
+                b = data[pos]; pos += 1
+                v |= (b & 0x7F) << shift; shift += 7
+                if not b & 0x80:
+                    return v
+        while pos < len(data):
+            tag = varint()
+            if tag == (1 << 3):
+                out["platform"] = varint()
+            elif tag == (2 << 3) | 2:
+                n = varint(); out["version"] = data[pos:pos + n]; pos += n
+            else:
+                raise PjrtError(13, f"unexpected field tag {tag} in an ABI version message")
+        return out
+
+    def __eq__(self, other) -> bool:
+        return type(other) is type(self) and self.serialize() == other.serialize()
+
+    def __hash__(self) -> int:
+        return hash(self.serialize())
+
+    def __del__(self):
+        if getattr(self, "handle", None):
+            try:
+                a = self._struct([("abi_version", _vp)]); a.abi_version = self.handle
+                self._call(self.api, self._DESTROY_SLOT, a)
+            except Exception:
+                pass
+            self.handle = None
+
+
+class ExecutableAbiVersion(_AbiVersion):
+    """`ExecutableAbiVersion` (crates/ryft-pjrt/src/extensions/abi_version.rs:339-416)."""
+    _DESTROY_SLOT, _TO_PROTO_SLOT, _PLATFORM_SLOT = _AbiVersion._EX_DESTROY, _AbiVersion._EX_TO_PROTO, _AbiVersion._EX_PLATFORM
+
+    @staticmethod
+    def deserialize(api: "Api", data: bytes) -> "ExecutableAbiVersion":
+        """`Api::deserialize_executable_abi_version` (abi_version.rs:212-230)."""
+        buf = C.create_string_buffer(data, len(data))
+        a = _AbiVersion._struct([("serialized_proto", _vp), ("serialized_proto_size", _sz), ("abi_version", _vp)])
+        a.serialized_proto = C.cast(buf, _vp); a.serialized_proto_size = len(data)
+        _AbiVersion._call(api, _AbiVersion._EX_FROM_PROTO, a)
+        return ExecutableAbiVersion(api, a.abi_version)
+
+
+class RuntimeAbiVersion(_AbiVersion):
+    """`RuntimeAbiVersion` (crates/ryft-pjrt/src/extensions/abi_version.rs:233-336).  The compatibility checks return
+    None and raise `PjrtError` when the versions do not fit, like the reference's `Result<(), Error>`."""
+    _DESTROY_SLOT, _TO_PROTO_SLOT, _PLATFORM_SLOT = _AbiVersion._RT_DESTROY, _AbiVersion._RT_TO_PROTO, _AbiVersion._RT_PLATFORM
+
+    @staticmethod
+    def deserialize(api: "Api", data: bytes) -> "RuntimeAbiVersion":
+        """`Api::deserialize_runtime_abi_version` (abi_version.rs:184-202)."""
+        buf = C.create_string_buffer(data, len(data))
+        a = _AbiVersion._struct([("serialized_proto", _vp), ("serialized_proto_size", _sz), ("abi_version", _vp)])
+        a.serialized_proto = C.cast(buf, _vp); a.serialized_proto_size = len(data)
+        _AbiVersion._call(api, _AbiVersion._RT_FROM_PROTO, a)
+        return RuntimeAbiVersion(api, a.abi_version)
+
+    def is_compatible_with_runtime(self, other: "RuntimeAbiVersion") -> None:
+        a = self._struct([("abi_version", _vp), ("other_abi_version", _vp)]); a.abi_version = self.handle; a.other_abi_version = other.handle
+        self._call(self.api, self._RT_WITH_RUNTIME, a)
+
+    def is_compatible_with_executable(self, other: ExecutableAbiVersion) -> None:
+        a = self._struct([("abi_version", _vp), ("executable_abi_version", _vp)]); a.abi_version = self.handle
+        a.executable_abi_version = other.handle
+        self._call(self.api, self._RT_WITH_EXECUTABLE, a)
 
 
 class Layout:
@@ -1112,6 +1241,12 @@ class Client:
         self._kv = KvCallbacks(store)
         a.kv_get_callback = self._kv.get_ptr
         a.kv_put_callback = self._kv.put_ptr
+
+    def abi_version(self) -> "RuntimeAbiVersion":
+        """`Client::abi_version` (crates/ryft-pjrt/src/extensions/abi_version.rs:72-83)."""
+        a = _AbiVersion._struct([("client", _vp), ("abi_version", _vp)]); a.client = self.handle
+        _AbiVersion._call(self.api, _AbiVersion._CLIENT_RUNTIME, a)
+        return RuntimeAbiVersion(self.api, a.abi_version)
 
     def default_layout(self, element_type: int, dims) -> "Layout":
         """`Client::default_layout` (crates/ryft-pjrt/src/extensions/layouts.rs:198-219)."""

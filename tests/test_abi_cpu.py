@@ -158,3 +158,51 @@ def test_layouts_extension_default_layout_and_serialization(plugin):
     assert layout == fake.default_layout(pjrt.BufferType.F32, [9, 9, 9])
     with pytest.raises(pjrt.PjrtError):
         fake.default_layout(0, [1])                                   # PJRT_Buffer_Type_INVALID
+
+
+def _proto(platform: int, payload: bytes) -> bytes:
+    def varint(v):
+        out = bytearray()
+        while v >= 0x80:
+            out.append((v & 0x7F) | 0x80); v >>= 7
+        out.append(v)
+        return bytes(out)
+    return varint(1 << 3) + varint(platform) + varint((2 << 3) | 2) + varint(len(payload)) + payload
+
+
+def test_abi_version_extension_round_trip_and_compatibility(plugin):
+    """crates/ryft-pjrt/src/extensions/abi_version.rs:184-230, 262-324: versions deserialize from the
+    `{platform, version}` message, serialize back to the same bytes, report their platform id and are checked against
+    each other.  The reference has no plugin that offers the extension (abi_version.rs:776-782), so the expectations
+    here are this plugin's rules: same platform and SM architecture; a runtime reads executables of its own
+    serialization generation or older, and talks to runtimes of its own generation.  No device is needed."""
+    import ctypes as C
+    api = plugin.api
+    ext = api.extension(pjrt.EXTENSION_TYPE_ABI_VERSION)
+    assert ext, "ABI-version extension missing from the extension chain"
+    assert all(C.c_void_p.from_address(ext + 24 + 8 * i).value for i in range(12))
+    platform = 0x6232785F63756461
+    current = _proto(platform, bytes([1, 100]))
+    rt = pjrt.RuntimeAbiVersion.deserialize(api, current)
+    assert rt.platform_id() == platform and rt.serialize() == current
+    assert rt.proto() == {"platform": platform, "version": bytes([1, 100])}
+    assert rt == pjrt.RuntimeAbiVersion.deserialize(api, current) and hash(rt) == hash(pjrt.RuntimeAbiVersion.deserialize(api, current))
+    ex = pjrt.ExecutableAbiVersion.deserialize(api, current)
+    assert ex.platform_id() == platform and ex.serialize() == current
+    rt.is_compatible_with_runtime(rt)
+    rt.is_compatible_with_executable(ex)
+    older = pjrt.ExecutableAbiVersion.deserialize(api, _proto(platform, bytes([0, 100])))
+    rt.is_compatible_with_executable(older)
+    for payload, what in ((bytes([2, 100]), "generation"), (bytes([1, 90]), "SM 90")):
+        with pytest.raises(pjrt.PjrtError) as e:
+            rt.is_compatible_with_executable(pjrt.ExecutableAbiVersion.deserialize(api, _proto(platform, payload)))
+        assert e.value.code_name == "FAILED_PRECONDITION" and what in e.value.message
+    with pytest.raises(pjrt.PjrtError) as e:
+        rt.is_compatible_with_runtime(pjrt.RuntimeAbiVersion.deserialize(api, _proto(platform, bytes([0, 100]))))
+    assert e.value.code_name == "FAILED_PRECONDITION"
+    for bad in (_proto(platform + 1, bytes([1, 100])), _proto(platform, b""), _proto(platform, bytes([1])), b"\x08", b"\x12\x05ab"):
+        with pytest.raises(pjrt.PjrtError) as e:
+            pjrt.RuntimeAbiVersion.deserialize(api, bad)
+        assert e.value.code_name == "INVALID_ARGUMENT"
+        with pytest.raises(pjrt.PjrtError):
+            pjrt.ExecutableAbiVersion.deserialize(api, bad)

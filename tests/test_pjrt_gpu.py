@@ -242,6 +242,23 @@ def test_memory_descriptions_extension(client):
     assert 0 <= default < len(descs) and descs[default][0] == "device"
 
 
+def test_abi_version_extension_on_client_and_executable(client):
+    """crates/ryft-pjrt/src/extensions/abi_version.rs:51-83: the client's runtime ABI version accepts the ABI version
+    of an executable it compiled, both carry the plugin's platform id, and both survive a serialize / deserialize
+    round trip; an executable deserialized from its serialized form reports the same version."""
+    runtime = client.abi_version()
+    exe = client.compile(pjrt.Program.mlir(ADD_PROGRAM))
+    executable = exe.executable().abi_version()
+    assert runtime.platform_id() == executable.platform_id() != 0
+    runtime.is_compatible_with_runtime(client.abi_version())
+    runtime.is_compatible_with_executable(executable)
+    assert pjrt.RuntimeAbiVersion.deserialize(client.api, runtime.serialize()) == runtime
+    assert pjrt.ExecutableAbiVersion.deserialize(client.api, executable.serialize()) == executable
+    assert runtime.proto()["platform"] == runtime.platform_id() and runtime.proto()["version"]
+    reloaded = client.deserialize_and_load(exe.executable().serialize())
+    assert reloaded.executable().abi_version() == executable
+
+
 def test_host_to_device_transfer_manager(client):
     """crates/ryft-pjrt/src/transfers.rs:1008-1073: chunked transfers, a failed transfer, and mixed data / literal
     transfers through `PJRT_Client_CreateBuffersForAsyncHostToDevice`."""
