@@ -151,8 +151,8 @@ NCU_TRAFFIC_BYTES_PER_LAUNCH = {
     "c4": 1.26e9,
     "c2": 247.7e6,     # profiles/k_gemm_tc__c2_batched_matmul_bias_tanh.md
     "c3": 519.7e6,     # profiles/k_attention__c3_causal_4096x128.md
-    "ew": 774.8e6,     # profiles/k_elementwise__ew_bias_tanh_bf16.md
-    "red": 138.3e6,    # profiles/k_reduce_rows__red_sum_f32.md (first pass)
+    "ew": 768.7e6,     # profiles/k_elementwise__ew_bias_tanh_bf16.md
+    "red": 138.7e6,    # profiles/k_reduce_rows__red_sum_f32.md (first pass)
 }
 
 

@@ -37,6 +37,16 @@ __host__ __device__ inline uint32_t red_identity(int monoid, int cls) {
   }
 }
 
+// MC selects a combine whose monoid and value class are known at compile time (the two that dominate: f32 sum and f32
+// max); 0 = decided at run time.
+template <int MC>
+__device__ __forceinline__ uint32_t red_combine_t(uint32_t a, uint32_t b, int monoid, int cls) {
+  if constexpr (MC == 1) return f2u(u2f(a) + u2f(b));
+  else if constexpr (MC == 2) return f2u(vm_fmax(u2f(a), u2f(b)));
+  else return red_combine(a, b, monoid, cls);
+}
+inline int red_combine_class(int monoid, int cls) { return cls == VM_F32 ? (monoid == 0 ? 1 : (monoid == 2 ? 2 : 0)) : 0; }
+
 struct ReduceKArgs {
   int64_t A, R, B;
   int64_t chunk;       // elements of R per split (multiple of the vector width for row reductions)
@@ -64,7 +74,7 @@ __device__ __forceinline__ void red_write(const ReduceKArgs& K, int64_t index, u
 }
 
 // Row reduction.  T = threads cooperating on one (row, split) piece: 32 or 256.
-template <int V, int T, int ID>
+template <int V, int T, int ID, int MC>
 __global__ void __launch_bounds__(256) k_reduce_rows(const __grid_constant__ B2xVmProgram P, const __grid_constant__ ReduceKArgs K) {
   __shared__ uint32_t smem[8];
   constexpr int PIECES_PER_CTA = 256 / T;
@@ -74,6 +84,8 @@ __global__ void __launch_bounds__(256) k_reduce_rows(const __grid_constant__ B2x
 #pragma unroll
   for (int j = 0; j < V; j++) zero[j] = 0;
   const uint32_t ident = red_identity(K.monoid, K.cls);
+  // the program's dims are [A, R] (or one merged dim): the coordinates of a vector are (a, r) without a division
+  const bool rows2 = P.n_dims == 2 && P.dim[1] == K.R;
   for (int64_t piece0 = (int64_t)blockIdx.x * PIECES_PER_CTA; piece0 < n_pieces; piece0 += (int64_t)gridDim.x * PIECES_PER_CTA) {
     const int64_t piece = piece0 + threadIdx.x / T;
     uint32_t total = ident;
@@ -81,15 +93,32 @@ __global__ void __launch_bounds__(256) k_reduce_rows(const __grid_constant__ B2x
       const int64_t a = piece / K.S, s = piece % K.S;
       const int64_t r0 = s * K.chunk;
       const int64_t r1 = min(K.R, r0 + K.chunk);
-      for (int64_t r = r0 + (int64_t)lane_in_piece * V; r < r1; r += (int64_t)T * V) {
-        uint32_t acc[V];
-        vm_run<V, ID>(P, (uint64_t)(a * K.R + r), zero, acc);
+      int64_t r = r0 + (int64_t)lane_in_piece * V;
+      if constexpr (ID != 0) {
+        // specialised programs are short: two vectors per trip, so that both vectors' loads are in flight together
+        // (the kernel is bound by memory latency, not by issue slots)
+        uint32_t total2 = ident;
+        for (; r + (int64_t)T * V < r1; r += 2 * (int64_t)T * V) {
+          uint32_t acc[V], acc2[V];
+          vm_run_at<V, ID>(P, (uint64_t)(a * K.R + r), rows2, a, r, zero, acc);
+          vm_run_at<V, ID>(P, (uint64_t)(a * K.R + r + (int64_t)T * V), rows2, a, r + (int64_t)T * V, zero, acc2);
 #pragma unroll
-        for (int j = 0; j < V; j++) total = red_combine(total, acc[j], K.monoid, K.cls);
+          for (int j = 0; j < V; j++) {
+            total = red_combine_t<MC>(total, acc[j], K.monoid, K.cls);
+            total2 = red_combine_t<MC>(total2, acc2[j], K.monoid, K.cls);
+          }
+        }
+        total = red_combine_t<MC>(total, total2, K.monoid, K.cls);
+      }
+      for (; r < r1; r += (int64_t)T * V) {
+        uint32_t acc[V];
+        vm_run_at<V, ID>(P, (uint64_t)(a * K.R + r), rows2, a, r, zero, acc);
+#pragma unroll
+        for (int j = 0; j < V; j++) total = red_combine_t<MC>(total, acc[j], K.monoid, K.cls);
       }
     }
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) total = red_combine(total, __shfl_xor_sync(0xffffffffu, total, off), K.monoid, K.cls);
+    for (int off = 16; off > 0; off >>= 1) total = red_combine_t<MC>(total, __shfl_xor_sync(0xffffffffu, total, off), K.monoid, K.cls);
     if (T == 32) {
       if (lane_in_piece == 0 && piece < n_pieces) red_write(K, piece, total);
     } else {
@@ -149,7 +178,7 @@ __global__ void __launch_bounds__(256) k_reduce_cols(const __grid_constant__ B2x
 }
 
 static int launch_one(const B2xVmProgram& P, ReduceKArgs K, int vec, cudaStream_t stream) {
-  const int64_t cap = (int64_t)kNumSms * 16;
+  const int64_t cap = (int64_t)kNumSms * 24;   // at least the split target: one CTA per piece, dealt out by the hardware
   if (K.B == 1) {
     const int64_t pieces = K.A * K.S;
     const int64_t len = (K.chunk < K.R ? K.chunk : K.R);
@@ -159,9 +188,15 @@ static int launch_one(const B2xVmProgram& P, ReduceKArgs K, int vec, cudaStream_
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     dim3 grid((unsigned)blocks), block(256);
+#define B2X_ROWS_MC(VV, II, MM)                                                           \
+    if (warp_rows) k_reduce_rows<VV, 32, II, MM><<<grid, block, 0, stream>>>(P, K);       \
+    else k_reduce_rows<VV, 256, II, MM><<<grid, block, 0, stream>>>(P, K);
+    // specialised programs also get a combine fixed at compile time for f32 sum / f32 max
 #define B2X_ROWS(VV, II)                                                                  \
-    if (warp_rows) k_reduce_rows<VV, 32, II><<<grid, block, 0, stream>>>(P, K);           \
-    else k_reduce_rows<VV, 256, II><<<grid, block, 0, stream>>>(P, K);
+    if (II != 0 && mc == 1) { B2X_ROWS_MC(VV, II, (II != 0 ? 1 : 0)) }                    \
+    else if (II != 0 && mc == 2) { B2X_ROWS_MC(VV, II, (II != 0 ? 2 : 0)) }               \
+    else { B2X_ROWS_MC(VV, II, 0) }
+    const int mc = red_combine_class(K.monoid, K.cls);
     if (vec == 8) {
       switch (vm_static_lookup(vm_signature_hash(P))) {
 #define X(I) case I: B2X_ROWS(8, I) break;
@@ -170,6 +205,7 @@ static int launch_one(const B2xVmProgram& P, ReduceKArgs K, int vec, cudaStream_
         default: B2X_ROWS(8, 0) break;
       }
     } else if (vec == 4) { B2X_ROWS(4, 0) } else { B2X_ROWS(1, 0) }
+#undef B2X_ROWS_MC
 #undef B2X_ROWS
   } else {
     int64_t bvecs = (K.B + vec - 1) / vec;
@@ -192,12 +228,14 @@ static int launch_one(const B2xVmProgram& P, ReduceKArgs K, int vec, cudaStream_
 }  // namespace b2x
 
 extern "C" int b2x_reduce_splits(int64_t A, int64_t R, int64_t B) {
-  // Enough independent pieces to fill 148 SMs without starving each piece of work.
+  // Enough independent pieces to fill 148 SMs without starving each piece of work.  The target, 24 pieces per SM, is a
+  // whole number of rounds for 1, 2, 3, 4, 6 or 8 resident CTAs per SM (the row kernels use 32 to 48 registers), so no
+  // round is left partly filled whichever the kernel's occupancy.
   int64_t outputs = A * ((B + 255) / 256 > 1 ? (B + 255) / 256 : 1);
   if (outputs >= 296 || R < 4096) return 1;
-  int64_t s = (1184 + outputs - 1) / outputs;
+  int64_t s = (3552 + outputs - 1) / outputs;
   if (s > R / 2048) s = R / 2048;
-  if (s > 1024) s = 1024;
+  if (s > 4096) s = 4096;
   return (int)(s < 1 ? 1 : s);
 }
 

@@ -667,15 +667,40 @@ __device__ __forceinline__ void vm_run_core(const B2xVmProgram& P, const int64_t
 
 // Runs the program for the V elements whose first element has linear index `lin` in the root shape.
 // `acc0` feeds VM_SRC_ACC0 operands.  On return `acc` holds the final accumulator (used by reductions).
+// Programs whose dims merged down to one or two (the usual case) take a short route to coordinates and offsets: at
+// most one division and two multiply-adds per tensor.  A caller that already knows the split of `lin` into
+// (c0, c1) over [dim0, dim1] passes it with known = true and saves the division as well.
 template <int V, int ID = 0>
-__device__ __forceinline__ void vm_run(const B2xVmProgram& P, uint64_t lin, const uint32_t (&acc0)[V], uint32_t (&acc)[V]) {
+__device__ __forceinline__ void vm_run_at(const B2xVmProgram& P, uint64_t lin, bool known, int64_t c0, int64_t c1, const uint32_t (&acc0)[V],
+                                          uint32_t (&acc)[V]) {
   int64_t coord[B2X_VM_MAX_DIMS];
-  vm_coords(P, lin, coord);
   int64_t off[B2X_VM_MAX_TENSORS];
+  const int nd = P.n_dims;
+  if (nd <= 2) {
+    if (nd <= 1) { c0 = (int64_t)lin; c1 = 0; }
+    else if (!known) {
+      if (lin <= 0xffffffffull) { const uint32_t n = (uint32_t)P.dim[1], l = (uint32_t)lin, q = l / n; c0 = q; c1 = l - q * n; }
+      else { const uint64_t n = (uint64_t)P.dim[1], q = lin / n; c0 = (int64_t)q; c1 = (int64_t)(lin - q * n); }
+    }
 #pragma unroll
-  for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) off[t] = (t < P.n_tensors) ? vm_offset(P.tensors[t], coord, P.n_dims) : 0;
+    for (int d = 0; d < B2X_VM_MAX_DIMS; d++) coord[d] = 0;
+    coord[0] = c0; coord[1] = c1;
+#pragma unroll
+    for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) {
+      off[t] = 0;
+      if (t < P.n_tensors) off[t] = c0 * P.tensors[t].stride[0] + (nd == 2 ? c1 * P.tensors[t].stride[1] : 0);
+    }
+  } else {
+    vm_coords(P, lin, coord);
+#pragma unroll
+    for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) off[t] = (t < P.n_tensors) ? vm_offset(P.tensors[t], coord, nd) : 0;
+  }
   VmRowAddr ra;      // unused outside the row-wise fast path
   vm_run_core<V, ID>(P, coord, off, ra, 0, acc0, acc);
+}
+template <int V, int ID = 0>
+__device__ __forceinline__ void vm_run(const B2xVmProgram& P, uint64_t lin, const uint32_t (&acc0)[V], uint32_t (&acc)[V]) {
+  vm_run_at<V, ID>(P, lin, false, 0, 0, acc0, acc);
 }
 
 // Row-wise driver for kernels that walk a [rows, N] result one row at a time (GEMM epilogues): the coordinate

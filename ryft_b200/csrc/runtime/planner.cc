@@ -822,11 +822,12 @@ void Planner::emit_group_for_root(const Value* v) {
 }
 
 int reduce_splits_impl(int64_t A, int64_t R, int64_t B) {
-  // Enough independent pieces to fill the machine (148 SMs x a few CTAs) without starving each piece of work.
+  // Enough independent pieces to fill the machine without starving each piece of work: 24 per SM, a whole number of
+  // rounds for 1, 2, 3, 4, 6 or 8 resident CTAs per SM.  Must agree with b2x_reduce_splits of the kernel library.
   int64_t outputs = A * std::max<int64_t>(1, (B + 255) / 256);
   if (outputs >= 296 || R < 4096) return 1;
-  int64_t s = std::min<int64_t>((1184 + outputs - 1) / outputs, R / 2048);
-  return (int)std::max<int64_t>(1, std::min<int64_t>(s, 1024));
+  int64_t s = std::min<int64_t>((3552 + outputs - 1) / outputs, R / 2048);
+  return (int)std::max<int64_t>(1, std::min<int64_t>(s, 4096));
 }
 
 void Planner::emit_reduce(const Op& op) {
