@@ -172,11 +172,15 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // The next tile is drawn one tile ahead: the atomic's round trip to L2 overlaps the loads of the current tile
+      // instead of standing between two tiles (it is a large part of a tile's time when K is one or two blocks).
+      int64_t t_next = (int64_t)atomicAdd(p.sched, 1);
       for (int64_t local = 0; ok; local++) {
         const int slot = (int)(local & (RING - 1));
         if (!mbar_wait(bar_sempty + 8 * slot, (uint32_t)(((local / RING) & 1) ^ 1), abort_flag, status, 5)) { ok = false; break; }
-        int64_t t = (int64_t)atomicAdd(p.sched, 1);
+        int64_t t = t_next;
         if (t >= p.num_tiles) t = -1;
+        else t_next = (int64_t)atomicAdd(p.sched, 1);
         tile_ring[slot] = (int32_t)t;
         mbar_arrive(bar_sfull + 8 * slot);
         if (t < 0 && p.epi_groups == 1) break;
