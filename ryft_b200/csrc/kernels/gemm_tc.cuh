@@ -141,6 +141,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   // Tiles are handed out dynamically: the producer draws the next tile index from a global counter and publishes it
   // to the other roles through this ring, so a CTA that starts late (its SM was busy with another kernel, e.g. a
   // collective) simply takes fewer tiles.
+  // A ring entry is {tile, batch, m0, n0}: the producer decomposes the tile index once for all roles.
   volatile int32_t* tile_ring = (volatile int32_t*)(tmem_slot + 2);
   constexpr int RING = 4;
 
@@ -181,7 +182,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         int64_t t = t_next;
         if (t >= p.num_tiles) t = -1;
         else t_next = (int64_t)atomicAdd(p.sched, 1);
-        tile_ring[slot] = (int32_t)t;
+        int b = 0, m0 = 0, n0 = 0;
+        if (t >= 0) tc_tile_coords(p, t, BN, &b, &m0, &n0);
+        tile_ring[slot * 4 + 0] = (int32_t)t; tile_ring[slot * 4 + 1] = b; tile_ring[slot * 4 + 2] = m0; tile_ring[slot * 4 + 3] = n0;
         mbar_arrive(bar_sfull + 8 * slot);
         if (t < 0 && p.epi_groups == 1) break;
         if (t < 0) {
@@ -189,13 +192,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
           const int64_t nxt = local + 1;
           const int slot2 = (int)(nxt & (RING - 1));
           if (mbar_wait(bar_sempty + 8 * slot2, (uint32_t)(((nxt / RING) & 1) ^ 1), abort_flag, status, 5)) {
-            tile_ring[slot2] = -1;
+            tile_ring[slot2 * 4] = -1;
             mbar_arrive(bar_sfull + 8 * slot2);
           }
           break;
         }
-        int b, m0, n0;
-        tc_tile_coords(p, t, BN, &b, &m0, &n0);
         for (int kb = 0; kb < p.k_blocks; kb++) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, status, 1)) { ok = false; break; }
           const uint32_t full = bar_full + 8 * stage;
@@ -231,7 +232,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       for (int64_t local = 0; ok; local++) {
         const int slot = (int)(local & (RING - 1));
         if (!mbar_wait(bar_sfull + 8 * slot, (uint32_t)((local / RING) & 1), abort_flag, status, 6)) { ok = false; break; }
-        const int32_t t = tile_ring[slot];
+        const int32_t t = tile_ring[slot * 4];
         mbar_arrive(bar_sempty + 8 * slot);
         if (t < 0) break;
         const int acc = (int)(local & 1);
@@ -274,14 +275,13 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
     for (int64_t local = group; ok; local += p.epi_groups) {
       const int slot = (int)(local & (RING - 1));
       if (!mbar_wait(bar_sfull + 8 * slot, (uint32_t)((local / RING) & 1), abort_flag, status, 7)) { ok = false; break; }
-      const int64_t t = tile_ring[slot];
+      const int64_t t = tile_ring[slot * 4];
+      const int b = tile_ring[slot * 4 + 1], m0 = tile_ring[slot * 4 + 2], n0 = tile_ring[slot * 4 + 3];
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_sempty + 8 * slot);
       if (t < 0) break;
       const int acc = (int)(local & 1);
       const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
-      int b, m0, n0;
-      tc_tile_coords(p, t, BN, &b, &m0, &n0);
       if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, status, 4)) { ok = false; break; }
       tc_fence_after();
       const int64_t row = (int64_t)m0 + quad * 32 + lane;
@@ -375,7 +375,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                 }
               }
             }
-            if (lane == 0) bulk_wait_read();
+            // the last strip's store is still reading the staging tile: the next tile waits for it before its first
+            // strip, the kernel's exit waits for all of them
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
