@@ -149,7 +149,7 @@ def inputs_for(config: str, replica: int):
 NCU_TRAFFIC_BYTES_PER_LAUNCH = {
     "c5": 1.26e9,      # profiles/k_gemm_tc__c4_mlp_train_step.md: (1.18 + 1.60 + 1.43 + 0.97 + 1.11) GB / 5
     "c4": 1.26e9,
-    "c2": 247.7e6,     # profiles/k_gemm_tc__c2_batched_matmul_bias_tanh.md
+    "c2": 249.0e6,     # profiles/k_gemm_tc__c2_batched_matmul_bias_tanh.md
     "c3": 519.7e6,     # profiles/k_attention__c3_causal_4096x128.md
     "ew": 768.7e6,     # profiles/k_elementwise__ew_bias_tanh_bf16.md
     "red": 138.7e6,    # profiles/k_reduce_rows__red_sum_f32.md (first pass)
