@@ -844,16 +844,18 @@ class LoadedExecutable:
     def execute(self, inputs: Sequence[ExecutionDeviceInputs], launch_id: int = 0, execute_device: Optional[Device] = None) -> List[ExecutionDeviceOutputs]:
         """`LoadedExecutable::execute` (crates/ryft-pjrt/src/programs.rs:769-963): the same client-side validation
         messages, then PJRT_LoadedExecutable_Execute with pre-allocated output and event slots."""
-        devices = self.addressable_devices()
-        if execute_device is None and len(inputs) != len(devices):
+        # the device count and the output count of a loaded executable never change: asked once, not per launch
+        shape = getattr(self, "_launch_shape", None)
+        if shape is None:
+            shape = self._launch_shape = (len(self.addressable_devices()), self.executable().num_outputs())
+        n_devices, num_outputs = shape
+        if execute_device is None and len(inputs) != n_devices:
             raise PjrtError(3, f"the number of provided execution inputs ({len(inputs)}) does not match the number of addressable "
-                               f"devices of the executable ({len(devices)})")
+                               f"devices of the executable ({n_devices})")
         num_args = len(inputs[0].inputs) if inputs else 0
         for i, di in enumerate(inputs):
             if len(di.inputs) != num_args:
                 raise PjrtError(3, f"device {i} was given {len(di.inputs)} arguments but device 0 was given {num_args}")
-        exe = self.executable()
-        num_outputs = exe.num_outputs()
         nd = len(inputs)
         arg_rows = [(_vp * max(num_args, 1))(*[b.handle for b in di.inputs]) for di in inputs]
         arg_lists = (C.POINTER(_vp) * nd)(*[C.cast(r, C.POINTER(_vp)) for r in arg_rows])
