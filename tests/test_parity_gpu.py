@@ -152,6 +152,21 @@ def test_reduce_with_fused_prologue_and_bf16(client):
     check_program(client, text, [rnd((128, 512), BF16, 15), rnd((128, 512), BF16, 16)], "prologue")
 
 
+def test_loss_reduction_long_pieces(client):
+    """Config 4's loss reduction (sum of squares of an f32 matrix, the `red` micro-configuration) at a size where every
+    piece of the split reduction spans several vectors per thread, so the two-vectors-per-trip loop of the specialised
+    row kernel, its one-vector remainder and the second pass over the partial sums all run."""
+    T, D = 4096, 4096 + 8          # 16.8 M elements: pieces of ~4.7 K elements, not a multiple of the 2048-element trip
+    got = check_program(client, configs.red_program(T, D), configs.red_inputs(T, D), "red long pieces")
+    assert abs(float(got[0]) - 1.0) < 5e-3                       # mean square of N(0,1) samples
+
+
+def test_elementwise_micro_configuration(client):
+    """The `ew` micro-configuration (tanh(x + bias) -> bf16 with the bias broadcast along rows) at a reduced batch:
+    the two-dim short route of the standalone elementwise kernel with a division by the row length."""
+    check_program(client, configs.ew_program(2, 512, 2048), configs.ew_inputs(2, 512, 2048), "ew small")
+
+
 def test_softmax_written_out(client):
     B, S = 6, 200
     b = Builder()
