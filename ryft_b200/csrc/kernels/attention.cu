@@ -11,7 +11,7 @@
 // output accumulator, and keeps its own running (max, sum).  While one stream exponentiates, the tensor pipe works
 // for the other; the two partial results are merged once, at the end.  352 threads:
 //   warp 0      TMA producer: Q once, then K_j and V_j into stage j & 1 as soon as that stage's previous K (after its
-//               Q K^T retired) or V (after its P V retired) is free; per-CTA loads, no multicast
+//               Q K^T retired) or V (after its P V retired) is free; each CTA loads its own tiles
 //   warps 1,10  MMA issuers, one per stream: S_s = Q K_j^T into TMEM score buffer s, O_s += P_s V_j into accumulator s
 //   warps 2-5   softmax stream 0, warps 6-9 stream 1; one query row per thread: the 128 scores of the row are read from
 //               TMEM once and stay in registers (row max, exp2, row sum), P goes as bf16 into 128-byte-swizzled

@@ -5,7 +5,7 @@
 //
 // One CTA per SM (grid = min(tiles, 148)), 64 + 32 * TC_EPI_WARPS threads:
 //   warp 0     TMA producer: per k-block one 128 x BK tile of A and one BN x BK tile of B into a STAGES-deep ring of
-//              128-byte-swizzled shared-memory buffers (cp.async.bulk.tensor, per CTA, no multicast);
+//              128-byte-swizzled shared-memory buffers (cp.async.bulk.tensor, each CTA loads its own tiles);
 //   warp 1     MMA issuer: one elected lane issues tcgen05.mma (128 x BN x 16) over the ring, commits each stage back
 //              to the producer and each finished accumulator to the epilogue; also owns TMEM allocation;
 //   warps 2..  epilogue: tcgen05.ld the 128 x BN f32 accumulator (each warp its 32 lanes and every fourth 32-column

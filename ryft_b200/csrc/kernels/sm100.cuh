@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the Blackwell (sm_100a) primitives the tensor-core kernels use: mbarriers with
-// bounded waits, TMA tiled loads (per CTA, never multicast), tcgen05 MMA / commit / TMEM load, TMEM allocation.
+// bounded waits, TMA tiled loads (each CTA loads its own tiles), tcgen05 MMA / commit / TMEM load, TMEM allocation.
 // Descriptor bit layouts follow the PTX ISA "tcgen05" matrix and instruction descriptor tables.
 #pragma once
 #include <cuda.h>
