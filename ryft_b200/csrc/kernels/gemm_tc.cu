@@ -74,7 +74,13 @@ extern "C" int b2x_launch_gemm_tc(const B2xGemmArgs* a, const B2xVmProgram* epil
   const int64_t a_ld = a_mn ? a->a_k_stride : a->a_row_stride, b_ld = b_mn ? a->b_k_stride : a->b_row_stride;
   if (a_ld % al || b_ld % al || (a->batch > 1 && (a->a_batch_stride % al || a->b_batch_stride % al))) return (int)cudaErrorInvalidValue;
   if (((uintptr_t)a->a & 15) || ((uintptr_t)a->b & 15) || a->N % 8) return (int)cudaErrorInvalidValue;
-  const int BN = a->N >= 256 ? 256 : (a->N >= 128 ? 128 : 64);
+  // widest tile that the result allows; a problem with fewer tiles than half the SMs takes narrower ones, so that
+  // more SMs share the operand traffic (each CTA streams its own A and B tiles)
+  int BN = a->N >= 256 ? 256 : (a->N >= 128 ? 128 : 64);
+  {
+    const int64_t m_tiles = (a->M + TC_BM - 1) / TC_BM;
+    while (BN > 64 && m_tiles * ((a->N + BN - 1) / BN) * a->batch < kNumSms / 2) BN /= 2;
+  }
   CUtensorMapDataType dt = tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : (a->elem == EL_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
   CUtensorMap tmA, tmB;
   bool ok;
