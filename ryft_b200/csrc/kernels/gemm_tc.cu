@@ -26,22 +26,60 @@ int32_t* sched_slot() {
 }
 
 // ---- f32 -> hi/lo TF32 split for the 3xTF32 scheme ------------------------------------------------------------------
-// out rows are K-major with 3K elements: sel 0 -> [hi | hi | lo], sel 1 -> [hi | lo | hi].
-__global__ void __launch_bounds__(256) k_split_f32(const float* __restrict__ src, float* __restrict__ dst, int64_t batch, int64_t rows, int64_t K,
-                                                   int64_t sb, int64_t sr, int64_t sk, int sel) {
-  const int64_t total = batch * rows * K;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    // walk the source along its contiguous dimension for coalescing
-    int64_t b, r, k;
-    if (sk == 1) { k = i % K; r = (i / K) % rows; b = i / (K * rows); }
-    else { r = i % rows; k = (i / rows) % K; b = i / (K * rows); }
-    const float x = __ldg(src + b * sb + r * sr + k * sk);
-    const float hi = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
-    const float lo = __uint_as_float(__float_as_uint(x - hi) & 0xffffe000u);
-    float* o = dst + (b * rows + r) * (3 * K);
-    o[k] = hi;
-    o[K + k] = sel == 0 ? hi : lo;
-    o[2 * K + k] = sel == 0 ? lo : hi;
+// out rows are K-major with 3K elements: sel 0 -> [hi | hi | lo], sel 1 -> [hi | lo | hi].  One launch splits both
+// operands: a CTA takes 32 x 32 (row, k) tiles of either.  A source that is contiguous along k is read and written
+// with lane = k; any other source is read with lane = row and turned through shared memory, so that the writes are
+// contiguous along k as well.
+struct SplitSide {
+  const float* src; float* dst;
+  int64_t rows, K, sb, sr, sk;
+  int64_t tiles_r, tiles_k, n_tiles;
+  int sel;
+};
+__device__ __forceinline__ void split_write(float* o, int64_t K, int64_t k, float x, int sel) {
+  const float hi = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
+  const float lo = __uint_as_float(__float_as_uint(x - hi) & 0xffffe000u);
+  o[k] = hi;
+  o[K + k] = sel == 0 ? hi : lo;
+  o[2 * K + k] = sel == 0 ? lo : hi;
+}
+__global__ void __launch_bounds__(256) k_split_f32(const __grid_constant__ SplitSide A, const __grid_constant__ SplitSide B) {
+  __shared__ float tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t total = A.n_tiles + B.n_tiles;
+  for (int64_t t = blockIdx.x; t < total; t += gridDim.x) {
+    const bool second = t >= A.n_tiles;
+    const SplitSide& S = second ? B : A;
+    int64_t u = second ? t - A.n_tiles : t;
+    const int64_t tk = u % S.tiles_k; u /= S.tiles_k;
+    const int64_t tr = u % S.tiles_r;
+    const int64_t b = u / S.tiles_r;
+    const int64_t r0 = tr * 32, k0 = tk * 32;
+    const float* src = S.src + b * S.sb;
+    float* dst = S.dst + b * S.rows * (3 * S.K);
+    if (S.sk == 1) {
+      const int64_t k = k0 + tx;
+#pragma unroll
+      for (int i = ty; i < 32; i += 8) {
+        const int64_t r = r0 + i;
+        if (r < S.rows && k < S.K) split_write(dst + r * (3 * S.K), S.K, k, __ldg(src + r * S.sr + k), S.sel);
+      }
+    } else {
+      const int64_t r_in = r0 + tx;
+#pragma unroll
+      for (int i = ty; i < 32; i += 8) {
+        const int64_t k = k0 + i;
+        tile[i][tx] = (r_in < S.rows && k < S.K) ? __ldg(src + r_in * S.sr + k * S.sk) : 0.0f;
+      }
+      __syncthreads();
+      const int64_t k = k0 + tx;
+#pragma unroll
+      for (int i = ty; i < 32; i += 8) {
+        const int64_t r = r0 + i;
+        if (r < S.rows && k < S.K) split_write(dst + r * (3 * S.K), S.K, k, tile[tx][i], S.sel);
+      }
+      __syncthreads();
+    }
   }
 }
 
@@ -51,10 +89,19 @@ extern "C" int b2x_launch_split_f32(const B2xGemmArgs* a, float* a_split, float*
   using namespace b2x;
   cudaStream_t stream = (cudaStream_t)stream_;
   if (a->elem != EL_F32) return (int)cudaErrorInvalidValue;
-  const int grid = kNumSms * 8;
-  k_split_f32<<<grid, 256, 0, stream>>>((const float*)a->a, a_split, a->batch, a->M, a->K, a->a_batch_stride, a->a_row_stride, a->a_k_stride, 0);
-  k_split_f32<<<grid, 256, 0, stream>>>((const float*)a->b, b_split, a->batch, a->N, a->K, a->b_batch_stride, a->b_row_stride, a->b_k_stride, 1);
-  count_launch(2);
+  auto side = [&](const void* src, float* dst, int64_t rows, int64_t sb, int64_t sr, int64_t sk, int sel) {
+    SplitSide s{};
+    s.src = (const float*)src; s.dst = dst; s.rows = rows; s.K = a->K; s.sb = sb; s.sr = sr; s.sk = sk; s.sel = sel;
+    s.tiles_r = (rows + 31) / 32; s.tiles_k = (a->K + 31) / 32; s.n_tiles = a->batch * s.tiles_r * s.tiles_k;
+    return s;
+  };
+  const SplitSide A = side(a->a, a_split, a->M, a->a_batch_stride, a->a_row_stride, a->a_k_stride, 0);
+  const SplitSide B = side(a->b, b_split, a->N, a->b_batch_stride, a->b_row_stride, a->b_k_stride, 1);
+  int64_t grid = A.n_tiles + B.n_tiles;
+  if (grid > (int64_t)kNumSms * 8) grid = (int64_t)kNumSms * 8;
+  if (grid < 1) return 0;
+  k_split_f32<<<(unsigned)grid, 256, 0, stream>>>(A, B);
+  count_launch(1);
   return (int)cudaGetLastError();
 }
 

@@ -1248,7 +1248,7 @@ static int step_kernel_launches(const Step& s) {
   switch (s.kind) {
     case StepKind::ELEMENTWISE: return 1;
     case StepKind::REDUCE: return reduce_splits(s.rA, s.rR, s.rB) > 1 ? 2 : 1;
-    case StepKind::GEMM: return s.g_split_f32 ? 3 : 1;
+    case StepKind::GEMM: return s.g_split_f32 ? 2 : 1;
     case StepKind::ATTENTION: return 1;
     default: return 0;
   }
