@@ -158,6 +158,11 @@ extern "C" int b2x_launch_gemm_tc(const B2xGemmArgs* a, const B2xVmProgram* epil
   }
   p.idesc = sm100::make_idesc(tf32 ? 2u : (a->elem == EL_BF16 ? 1u : 0u), a_mn, b_mn, TC_BM, (uint32_t)BN);
   if (tf32) {
+    const int id32 = vm_static_lookup(vm_signature_hash(*epilogue));
+    if (id32) {
+      int rc = launch_tc_static_tf32(id32, BN, tmA, tmB, p, *epilogue, status, stream);
+      if (rc >= 0) return rc;
+    }
     if (BN == 256) return launch_tc<256, 4, true, 0>(tmA, tmB, p, *epilogue, status, stream);
     if (BN == 128) return launch_tc<128, 6, true, 0>(tmA, tmB, p, *epilogue, status, stream);
     return launch_tc<64, 8, true, 0>(tmA, tmB, p, *epilogue, status, stream);

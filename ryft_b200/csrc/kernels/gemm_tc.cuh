@@ -497,4 +497,7 @@ namespace b2x {
 // Launches a build-time specialised epilogue when one exists for (program id, tile width); returns -1 otherwise.
 int launch_tc_static(int id, int BN, const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, const B2xVmProgram& epi, int32_t* status,
                      cudaStream_t stream);
+// Same for f32 operands (3xTF32); only the plain f32 store is specialised there.
+int launch_tc_static_tf32(int id, int BN, const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, const B2xVmProgram& epi, int32_t* status,
+                          cudaStream_t stream);
 }  // namespace b2x
