@@ -343,7 +343,7 @@ static PJRT_Error* Client_Create(PJRT_Client_Create_Args* a) {
         B2X_CUDA(cudaSetDevice(d->cuda_ordinal));
         cudaDeviceProp prop;
         B2X_CUDA(cudaGetDeviceProperties(&prop, d->cuda_ordinal));
-        if (prop.major != 10 && !getenv("B2X_ALLOW_ANY_GPU"))
+        if (prop.major != 10)
           return make_error(PJRT_Error_Code_FAILED_PRECONDITION, std::string("device ") + prop.name + " has compute capability " + std::to_string(prop.major) + "." +
                                 std::to_string(prop.minor) + "; the kernels in this plugin are built for sm_100a only");
         B2X_CUDA(cudaStreamCreateWithFlags(&d->compute, cudaStreamNonBlocking));
