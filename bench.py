@@ -12,6 +12,11 @@ bootstrapped through the PJRT key-value callbacks backed by the torch.distribute
 plugin's compute stream).  `e2e` runs the same step through the same API from pinned host memory: the activations are
 copied host->device and the loss device->host inside the timed region.
 
+Parity.  What was timed is also checked: the gradients and the loss of the last timed step against the CPU oracle at
+full size (rank 0), and for N > 1 the all-reduced gradients against an independent all-reduce of the per-rank gradients,
+bit-identity of the results across ranks, and a small pre-flight data-parallel step against the oracle.  The outcome is
+the `parity` object of the JSON line; a failed check makes the process exit non-zero after printing the line.
+
 Reference arm (--impl reference).  The reference executes these programs in OpenXLA's CPU plugin, which cannot be built
 here, so this arm times the CPU oracle (oracle/stablehlo_eval.py, a NumPy restatement; BLAS on all host cores) on a
 bounded token sample of the same program.
@@ -25,7 +30,14 @@ import subprocess
 import sys
 import threading
 import time
+import zlib
 from pathlib import Path
+
+# The CPU legs (oracle check, CPU baseline, reference arm) run on rank 0 and should use every host core; a multi-process
+# launcher exports OMP_NUM_THREADS=1, which must not leak into them.
+if os.environ.get("RANK", "0") == "0":
+    for _v in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[_v] = str(os.cpu_count() or 1)
 
 import numpy as np
 
@@ -143,16 +155,16 @@ def inputs_for(config: str, replica: int):
     return {"c2": configs.c2_inputs, "c3": configs.c3_inputs, "c1": configs.c1_inputs, "ew": configs.ew_inputs, "red": configs.red_inputs}[config]()
 
 
-# DRAM traffic of the dominant kernel per launch (dram__bytes_read.sum + dram__bytes_write.sum from the ncu captures
-# summarised in profiles/; a profiler cannot run inside a timed bench, so the figures are recorded here).  For c5/c4 it
-# is the mean over the five GEMM launches of one step.
+# DRAM traffic of the dominant kernel per launch: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of that
+# kernel on this workload (a profiler cannot run inside a timed bench, so the measured figures are recorded here and must
+# be re-measured when the kernel changes).  For c5/c4 it is the mean over the five GEMM launches of one step.
 NCU_TRAFFIC_BYTES_PER_LAUNCH = {
-    "c5": 1.26e9,      # profiles/k_gemm_tc__c4_mlp_train_step.md: (1.18 + 1.60 + 1.43 + 0.97 + 1.11) GB / 5
+    "c5": 1.26e9,      # (1.18 + 1.60 + 1.43 + 0.97 + 1.11) GB / 5
     "c4": 1.26e9,
-    "c2": 249.0e6,     # profiles/k_gemm_tc__c2_batched_matmul_bias_tanh.md
-    "c3": 519.7e6,     # profiles/k_attention__c3_causal_4096x128.md
-    "ew": 768.7e6,     # profiles/k_elementwise__ew_bias_tanh_bf16.md
-    "red": 138.7e6,    # profiles/k_reduce_rows__red_sum_f32.md (first pass)
+    "c2": 249.0e6,
+    "c3": 519.7e6,
+    "ew": 768.7e6,
+    "red": 138.7e6,    # first pass
 }
 
 
@@ -182,6 +194,103 @@ def time_device(client, exe, bufs, steps: int, warmup: int, world: int, stream_h
     ms = float(t0.elapsed_time(t1))
     timings = exe.step_timing(enable=0, collect=True)
     return ms, timings, last
+
+
+
+PARITY_TOL = 1e-4          # relative Frobenius error of f32 results, relative error of the scalar loss
+# dW1 sits behind three bf16 roundings (H/A, dY, dH), each of which turns a relative difference d of its input into about
+# sqrt(d * 2^-8): two CPU evaluations of the oracle that differ only in how the contractions accumulate (float32 BLAS
+# against float64) are 4.5e-4 apart on dW1 (1e-5 on dW2, 0 on the loss), and the truncating accumulation of the tensor
+# cores (a relative shift of -1e-9 * K per GEMM) puts this build at 1.1e-3.  Every single GEMM of the step meets 1e-4
+# when it is fed the oracle's inputs (tests/test_parity_gpu.py checks that at full size).
+PARITY_TOL_DW1_CHAIN = 3e-3
+
+
+def _rel_fro(a: np.ndarray, e: np.ndarray) -> float:
+    """Relative Frobenius error, accumulated blockwise in float64 so that 64 M-element gradients need no f64 copy."""
+    a, e = a.reshape(-1), e.reshape(-1)
+    num = den = 0.0
+    step = 1 << 24
+    for i in range(0, e.size, step):
+        x = e[i:i + step].astype(np.float64)
+        d = a[i:i + step].astype(np.float64) - x
+        num += float(d @ d); den += float(x @ x)
+    return float(np.sqrt(num / den)) if den > 0 else float(np.sqrt(num))
+
+
+def _run_to_numpy(exe, bufs):
+    from ryft_b200 import pjrt
+    outs = exe.execute([pjrt.ExecutionDeviceInputs(bufs)])
+    outs[0].done.await_()
+    return [o.to_numpy() for o in outs[0].outputs]
+
+
+def parity_check(client, dev, exe, bufs, host_inputs, n_rep: int, rank: int, world: int) -> tuple:
+    """Checks the results of the timed program.  Returns (parity dict, cpu seconds of the full-size oracle run or None).
+
+    N = 1: the step's dW1, dW2 and loss against the CPU oracle on the same inputs at full size.
+    N > 1: (a) a small data-parallel step (same program text, reduced sizes) on all ranks against the oracle evaluating all
+    replicas, (b) the full-size all-reduced gradients against torch.distributed's all-reduce of the per-rank gradients
+    (computed by the same program without the collective), (c) bit-identity of the all-reduced results across ranks, and
+    (d) rank 0's per-rank gradients and loss against the oracle at full size."""
+    import torch
+    from oracle import stablehlo_eval as ev
+    from ryft_b200 import configs, pjrt
+    res = {"checked": True, "tolerance": PARITY_TOL}
+    rels = []
+    got = _run_to_numpy(exe, bufs)                       # dW1, dW2 (all-reduced and divided when N > 1), loss
+    local = got
+    if world > 1:
+        import torch.distributed as dist
+        # (a) pre-flight: small sizes, every rank its own shard, oracle over all replicas on rank 0
+        t, d, f = 256, 128, 384
+        small = client.compile(pjrt.Program.mlir(configs.c4_program(t, d, f, replicas=n_rep)), pjrt.CompilationOptions(replica_count=n_rep))
+        sm_in = configs.c4_inputs(t, d, f, seed=4, replica=rank)
+        sm_got = _run_to_numpy(small, [client.buffer(x, device=dev) for x in sm_in])
+        if rank == 0:
+            want = ev.evaluate(configs.c4_program(t, d, f, replicas=n_rep), [configs.c4_inputs(t, d, f, seed=4, replica=r) for r in range(n_rep)])[0]
+            pre = max(_rel_fro(sm_got[0], want[0]), _rel_fro(sm_got[1], want[1]))
+            res["preflight_rel"] = pre
+            rels.append(pre)
+        # (b) full size: the plugin's all-reduce against an independent one over the per-rank gradients
+        exe_local = client.compile(pjrt.Program.mlir(configs.c4_program(T_FULL, D_FULL, F_FULL)))
+        local = _run_to_numpy(exe_local, bufs)
+        worst = 0.0
+        for k in (0, 1):
+            ref = torch.from_numpy(local[k]).cuda()
+            dist.all_reduce(ref)
+            ref /= world
+            worst = max(worst, _rel_fro(got[k], ref.cpu().numpy()))
+            del ref
+        res["allreduce_vs_independent_rel"] = _max_over_ranks(worst, world)
+        rels.append(res["allreduce_vs_independent_rel"])
+        # (c) every rank must hold the same bits
+        sums = [zlib.crc32(memoryview(np.ascontiguousarray(got[k])).cast("B")) for k in (0, 1)] + \
+               [zlib.crc32(memoryview(np.ascontiguousarray(sm_got[k])).cast("B")) for k in (0, 1)]
+        all_sums = [None] * world
+        dist.all_gather_object(all_sums, sums)
+        res["ranks_identical"] = all(s == all_sums[0] for s in all_sums)
+    oracle_s = None
+    if rank == 0:
+        # (d) / N = 1: full-size oracle on this rank's inputs (f32 BLAS accumulation on all host threads)
+        threads = ev.use_all_host_threads()
+        text = configs.c4_program(T_FULL, D_FULL, F_FULL)
+        t0 = time.perf_counter()
+        want = ev.evaluate(text, [host_inputs], fast_dot=True)[0]
+        oracle_s = time.perf_counter() - t0
+        res["dw1_rel_frobenius"] = _rel_fro(local[0], want[0])
+        res["dw2_rel_frobenius"] = _rel_fro(local[1], want[1])
+        res["loss"] = float(local[2]); res["loss_oracle"] = float(want[2])
+        res["loss_rel"] = abs(float(local[2]) - float(want[2])) / abs(float(want[2]))
+        res["oracle_seconds"] = oracle_s; res["oracle_threads"] = threads
+        tight = rels + [res["dw2_rel_frobenius"], res["loss_rel"]]
+        res["max_rel"] = max(tight + [res["dw1_rel_frobenius"]])
+        res["tolerance_dw1_behind_three_bf16_roundings"] = PARITY_TOL_DW1_CHAIN
+        res["ok"] = bool(max(tight) <= PARITY_TOL and res["dw1_rel_frobenius"] <= PARITY_TOL_DW1_CHAIN and res.get("ranks_identical", True))
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    return res, oracle_s
 
 
 def run_own(args) -> dict:
@@ -231,24 +340,36 @@ def run_own(args) -> dict:
             # asynchronous copy from pinned host memory on the plugin's transfer stream (ImmutableUntilTransferCompletes)
             return client.buffer(pinned.data_ptr(), pjrt.BufferType.BF16, list(x.shape), device=dev, semantics=1)
 
+        host = {"upload": 0.0, "execute": 0.0, "readback": 0.0, "wait": 0.0}
+
         def run_steps(n):
             # the input pipeline of a training loop: step i+1's tokens are uploaded while step i computes, and with
             # --e2e-depth 2 step i+1 is also enqueued before the host waits for loss i.  Every step uploads its own 64 MiB
-            # of tokens and has its own loss read back inside the timed region.
+            # of tokens and has its own loss read back inside the timed region.  Host time is split by stage: what the
+            # enqueue calls cost (upload, execute, readback) and how long the host then sat waiting for the device.
+            for k in host:
+                host[k] = 0.0
+            c = time.perf_counter
             xb = upload()
             pending = None
             hosts = [np.zeros(4, dtype=np.uint8), np.zeros(4, dtype=np.uint8)]
             for i in range(n):
+                t0 = c()
                 outs = exe.execute([pjrt.ExecutionDeviceInputs([xb, bufs[1], bufs[2]])])
+                t1 = c()
                 if i + 1 < n:
                     xb = upload()
+                t2 = c()
                 ev = outs[0].outputs[2].copy_to_host(hosts[i & 1])
+                t3 = c()
                 if args.e2e_depth <= 1:
                     ev.await_()
                 else:
                     if pending is not None:
                         pending.await_()
                     pending = ev
+                t4 = c()
+                host["execute"] += t1 - t0; host["upload"] += t2 - t1; host["readback"] += t3 - t2; host["wait"] += t4 - t3
             if pending is not None:
                 pending.await_()
             loss_host[:] = hosts[(n - 1) & 1]
@@ -264,7 +385,9 @@ def run_own(args) -> dict:
         wall = _max_over_ranks(time.perf_counter() - w0, world)
         e2e = {"value": flops_per_replica * n_rep * e2e_steps / wall / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": int(x.nbytes) * n_rep,
                "d2h_bytes_per_step": 4 * n_rep, "ms_per_step": wall / e2e_steps * 1e3, "loss": float(loss_host.view(np.float32)[0]),
-               "h2d_alone_ms": h2d_ms, "h2d_alone_gb_per_s": x.nbytes / (h2d_ms * 1e-3) / 1e9}
+               "h2d_alone_ms": h2d_ms, "h2d_alone_gb_per_s": x.nbytes / (h2d_ms * 1e-3) / 1e9,
+               "host_ms_per_step": {k: v / e2e_steps * 1e3 for k, v in host.items()},
+               "results_left_on_device": "dW1 and dW2 (512 MiB of f32 gradients) stay in HBM for the optimiser; only the loss is read back"}
 
     # ---- roofline of the dominant kernel (tcgen05 GEMM) from the per-step CUDA events of the timed region ----
     peaks = _peaks()
@@ -306,12 +429,7 @@ def run_own(args) -> dict:
         "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "steps_per_s": args.steps / (ms * 1e-3), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16 operands, f32 accumulate", "data": "synthetic (seeded N(0,1) activations, N(0,0.02) weights)",
-        "config": {"workload": {"c5": c5_workload(n_rep),
-                                "c4": "config 4: MLP fwd+bwd gradient step on one GPU", "c2": "config 2: batched bf16 dot_general + bias + tanh + convert",
-                                "c3": "config 3: causal attention written out in StableHLO", "c1": "config 1: f32 dot_general 512x768x512",
-                                "ew": "micro: config 2's epilogue chain standalone, tanh(f32[32,2048,2048] + bias) -> bf16",
-                                "red": "micro: config 4's loss reduction standalone, sum of squares of f32[8192,4096]"}[config],
-                   "replicas": n_rep, "parallelism": f"dp{n_rep}", "l2": "inputs (>= 320 MiB per step) exceed the 126 MB L2; no flush needed"},
+        "config": config_for(config, n_rep),
         "gpu_launches": launches_per_exec * args.steps, "clocks": clocks,
         "steps_breakdown": [{"label": t["label"], "ms_per_step": t["ms"] / max(t["executions"], 1)} for t in timings],
     }
@@ -319,8 +437,23 @@ def run_own(args) -> dict:
         line["e2e"] = e2e
     if roofline:
         line["roofline"] = roofline
+    if config == "c5" and world > 1:
+        line["collectives"] = collective_figures(client, dev, timings, world, stream, local)
+    parity, oracle_s = None, None
+    if config == "c5" and not args.no_parity:
+        parity, oracle_s = parity_check(client, dev, exe, bufs, host_inputs, n_rep, rank, world)
+        line["parity"] = parity
+    elif config == "c5":
+        line["parity"] = {"checked": False, "why": "--no-parity"}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline(config)
+        if oracle_s:
+            # the oracle run of the parity check is the CPU baseline: the whole step, all tokens, on the host's cores
+            line["cpu_baseline"] = {"value": flops_per_replica / oracle_s / 1e12, "unit": "TFLOP/s", "cores": parity.get("oracle_threads") or os.cpu_count(),
+                                    "kind": "port", "seconds": oracle_s,
+                                    "sample": f"one full step (all {T_FULL} tokens, d={D_FULL}, ff={F_FULL}); NumPy oracle, f32 BLAS GEMMs on all host threads, "
+                                              "elementwise ops single-threaded"}
+        else:
+            line["cpu_baseline"] = cpu_baseline(config)
     if rank == 0 and world == 1 and config == "c5" and not args.no_extras:
         line["extra"] = extras(client, peaks, local)
     client.close()
@@ -328,6 +461,30 @@ def run_own(args) -> dict:
         import torch.distributed as dist
         dist.destroy_process_group()
     return line if rank == 0 else None
+
+
+def collective_figures(client, dev, timings, world: int, stream_handle: int, local: int) -> dict:
+    """Bus bandwidth of the gradient all-reduce, 2 (n - 1) / n x bytes / time with CUDA events on the communication
+    stream: inside the timed step, where it shares the GPU with the GEMMs it overlaps, and alone (a program that only
+    all-reduces one 256 MiB f32 gradient)."""
+    from ryft_b200 import pjrt
+    from ryft_b200.stablehlo import Builder
+    factor = 2.0 * (world - 1) / world
+    inside = [t for t in timings if t["label"].startswith("collective")]
+    out = {"bytes_per_all_reduce": D_FULL * F_FULL * 4, "ranks": world,
+           "overlapped_ms": [t["ms"] / max(t["executions"], 1) for t in inside]}
+    out["overlapped_bus_gbs"] = [factor * out["bytes_per_all_reduce"] / (ms * 1e-3) / 1e9 for ms in out["overlapped_ms"] if ms > 0]
+    b = Builder()
+    g = b.arg([D_FULL, F_FULL], "f32")
+    (r,) = b.all_reduce([g], [list(range(world))])
+    exe = client.compile(pjrt.Program.mlir(b.build(r)), pjrt.CompilationOptions(replica_count=world))
+    buf = client.buffer(np.zeros((D_FULL, F_FULL), np.float32), device=dev)
+    ms, t2, _ = time_device(client, exe, [buf], 5, 3, world, stream_handle, local)
+    alone = [t["ms"] / max(t["executions"], 1) for t in t2 if t["label"].startswith("collective")]
+    ms_alone = _max_over_ranks(alone[0] if alone else ms / 5, world)
+    out["alone_ms"] = ms_alone
+    out["alone_bus_gbs"] = factor * out["bytes_per_all_reduce"] / (ms_alone * 1e-3) / 1e9
+    return out
 
 
 def extras(client, peaks, local) -> dict:
@@ -351,6 +508,16 @@ def extras(client, peaks, local) -> dict:
         except Exception as e:  # report, never hide
             out[cfg] = {"error": str(e)}
     return out
+
+
+def config_for(config: str, n_rep: int) -> dict:
+    """The `config` object of the JSON line; both arms print the same one."""
+    return {"workload": {"c5": c5_workload(n_rep),
+                         "c4": "config 4: MLP fwd+bwd gradient step on one GPU", "c2": "config 2: batched bf16 dot_general + bias + tanh + convert",
+                         "c3": "config 3: causal attention written out in StableHLO", "c1": "config 1: f32 dot_general 512x768x512",
+                         "ew": "micro: config 2's epilogue chain standalone, tanh(f32[32,2048,2048] + bias) -> bf16",
+                         "red": "micro: config 4's loss reduction standalone, sum of squares of f32[8192,4096]"}[config],
+            "replicas": n_rep, "parallelism": f"dp{n_rep}", "l2": "inputs (>= 320 MiB per step) exceed the 126 MB L2; no flush needed"}
 
 
 def c5_workload(n_rep: int) -> str:
@@ -383,12 +550,16 @@ def cpu_baseline(config: str, target_seconds: float = 12.0) -> dict:
 
 
 def run_reference(args) -> dict:
+    """The CPU arm: the oracle on the host's cores, every step a bounded token sample of one replica's program.  With N
+    replicas the reference's CPU plugin would run them on the same host cores, so the whole-job rate on the host equals
+    one replica's rate; that rate is the value."""
     rank, world, _ = _dist()
     if rank != 0:
         return None
     from oracle import stablehlo_eval as ev
     from ryft_b200 import configs
-    sample = 256
+    threads = ev.use_all_host_threads()
+    sample = args.ref_tokens
     text = configs.c4_program(sample, D_FULL, F_FULL)
     ins = configs.c4_inputs(sample, D_FULL, F_FULL, seed=4)
     mod = ev.parse(text)
@@ -400,13 +571,14 @@ def run_reference(args) -> dict:
         ev.evaluate(mod, [ins], fast_dot=True)
     dt = time.perf_counter() - t0
     value = flops * args.steps / dt / 1e12
-    sample_txt = f"{sample} of {T_FULL} tokens per step, full d={D_FULL} ff={F_FULL}; NumPy oracle (port of StableHLO semantics), f32 BLAS on all host threads"
+    n_rep = max(args.gpus, 1)
+    sample_txt = (f"{sample} of {T_FULL} tokens per step, full d={D_FULL} ff={F_FULL}, one replica's program (replicas would share these cores, so the "
+                  f"whole-job rate equals this rate); NumPy oracle (port of StableHLO semantics), f32 BLAS on {threads} host threads; rank 0 only")
     return {"impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 operands, f32 accumulate",
             "data": "synthetic (seeded N(0,1) activations, N(0,0.02) weights)",
-            "config": {"workload": c5_workload(max(args.gpus, 1)), "replicas": max(args.gpus, 1), "parallelism": f"dp{max(args.gpus, 1)}",
-                       "cpu_sample": "one replica's step on a bounded token sample (see cpu_baseline.sample); rank 0 only"},
-            "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port", "sample": sample_txt},
+            "config": config_for("c5", n_rep),
+            "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample_txt},
             "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "note": "the reference runs this path inside OpenXLA's CPU PJRT plugin, which cannot be built or fetched in this environment; the CPU oracle is timed instead"}
 
@@ -420,6 +592,8 @@ def main():
     ap.add_argument("--config", default="c5", choices=["c1", "c2", "c3", "c4", "c5", "ew", "red"])
     ap.add_argument("--e2e-depth", type=int, default=2, help="steps the end-to-end loop keeps in flight (1 or 2)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the timed program (profiling runs)")
+    ap.add_argument("--ref-tokens", type=int, default=2048, help="tokens per step of the CPU reference arm")
     ap.add_argument("--no-extras", action="store_true")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "own":
@@ -432,6 +606,9 @@ def main():
     os.dup2(real_stdout, 1)
     if line is not None:
         print(json.dumps(line), flush=True)
+        if line.get("parity", {}).get("checked") and line["parity"].get("ok") is False:
+            print("parity check failed: " + json.dumps(line["parity"]), file=sys.stderr)
+            sys.exit(3)
 
 
 if __name__ == "__main__":

@@ -34,7 +34,9 @@ B2X_API int b2x_launch_elementwise(const B2xVmProgram* host_prog, int64_t n_elem
 /* stablehlo.reduce over the middle extent of an [A, R, B] view (functional.rs:188-219), with a fused elementwise
  * prologue.  monoid: 0 add, 1 mul, 2 max, 3 min, 4 and, 5 or, 6 xor.  cls: register class of the reduced value
  * (B2xVmClass).  `init_ptr` (device scalar of element type init_elem) is used when non-NULL, else `init_imm`.
- * `scratch` must hold A * b2x_reduce_splits(A,R,B) * B * 4 bytes when that count is > 1. */
+ * `scratch` must hold A * b2x_reduce_splits(A,R,B) * B * 4 bytes when that count is > 1.  `host_post` (may be NULL) is a
+ * fused consumer: a program over the result's [A * B] elements that receives each finished value (combined with init,
+ * rounded to out_elem) as VM_SRC_ACC0 and does all stores itself; `out` is then not written. */
 typedef struct {
   int64_t A, R, B;
   uint8_t monoid, cls, out_elem, init_elem;
@@ -43,8 +45,11 @@ typedef struct {
   void* out;
   void* scratch;
   int vec;
+  const B2xVmProgram* host_post;
 } B2xReduceArgs;
 B2X_API int b2x_reduce_splits(int64_t A, int64_t R, int64_t B);
+/* Kernels one call of b2x_launch_reduce enqueues for this shape: 1, or 2 for a split column reduction (B > 1). */
+B2X_API int b2x_reduce_launches(int64_t A, int64_t R, int64_t B);
 B2X_API int b2x_launch_reduce(const B2xVmProgram* host_prologue, const B2xReduceArgs* host_args, b2x_stream_t stream);
 
 /* The same reduction for callers that must not allocate device memory (an embedding runtime that owns the allocator,
@@ -80,6 +85,12 @@ B2X_API int b2x_launch_gemm_simt(const B2xGemmArgs* host_args, const B2xVmProgra
  * bases and strides, and one unit stride per operand.  `status` is a device int32 that receives a non-zero code if a
  * bounded wait inside the kernel expires. */
 B2X_API int b2x_launch_gemm_tc(const B2xGemmArgs* host_args, const B2xVmProgram* host_epilogue, int32_t* status, b2x_stream_t stream);
+/* Host-only: what b2x_launch_gemm_tc would do for this problem and epilogue program, without touching a device (tests use
+ * it to assert that a case runs the same kernel variant as another).  out[0] tile width BN, [1] id of the build-time
+ * specialised epilogue (0 = interpreted), [2] epilogue groups (1 or 2), [3] 1 if the multi-store epilogue goes through
+ * shared memory (transposed), [4] m-tiles per raster group, [5] m-tiles, [6] n-tiles, [7] k-blocks per tile, [8] stores of
+ * the specialised program, [9] CTAs launched. */
+B2X_API int b2x_gemm_tc_route(const B2xGemmArgs* host_args, const B2xVmProgram* host_epilogue, int32_t out[10]);
 /* Splits f32 operands for the 3xTF32 scheme: writes A' = [hi | hi | lo] and B' = [hi | lo | hi] along K into scratch
  * (K-major rows of 3K elements), so that one TF32 GEMM over K' = 3K yields hi*hi + hi*lo + lo*hi. */
 B2X_API int b2x_launch_split_f32(const B2xGemmArgs* host_args, float* a_split, float* b_split, b2x_stream_t stream);

@@ -301,13 +301,37 @@ def evaluate(text_or_module, inputs_per_replica: Sequence[Sequence[np.ndarray]],
             assert tuple(arr.shape) == t.dims and arr.dtype == t.np, (name, arr.shape, arr.dtype, t)
             e[name] = arr
         env.append(e)
-    for op in mod.ops:
+    # a value is dropped after its last use, so that a full-size program does not hold every intermediate at once
+    last_use: Dict[str, int] = {}
+    for i, op in enumerate(mod.ops):
+        for o in op.operands:
+            last_use[o] = i
+    keep = set(mod.returns)
+    for i, op in enumerate(mod.ops):
         outs_per_rep = [_eval_op(op, [env[r][o] for o in op.operands], r, fast_dot) for r in range(nrep)] if op.name not in ("all_reduce", "all_gather") else \
             _eval_collective(op, [[env[r][o] for o in op.operands] for r in range(nrep)])
         for r in range(nrep):
             for n, v in zip(op.results, outs_per_rep[r]):
                 env[r][n] = v
+        for o in set(op.operands):
+            if last_use.get(o) == i and o not in keep:
+                for r in range(nrep):
+                    env[r].pop(o, None)
     return [[env[r][n] for n in mod.returns] for r in range(nrep)]
+
+
+def use_all_host_threads() -> int:
+    """Lets the BLAS behind NumPy use every host core, whatever OMP_NUM_THREADS the launcher exported (torchrun sets it to
+    1 for multi-process runs).  Returns the number of threads now in use (1 when the pool cannot be inspected)."""
+    import os
+    n = os.cpu_count() or 1
+    try:
+        import threadpoolctl
+        threadpoolctl.threadpool_limits(limits=n)
+        pools = [p.get("num_threads", 1) for p in threadpoolctl.threadpool_info() if p.get("user_api") == "blas"]
+        return max(pools) if pools else 1
+    except Exception:
+        return 1
 
 
 def _eval_collective(op: OpRec, ins: List[List[np.ndarray]]) -> List[List[np.ndarray]]:

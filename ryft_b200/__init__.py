@@ -29,3 +29,31 @@ def plan_dump(mlir_text: str, num_replicas: int = 1) -> str:
     if code:
         raise PjrtError(code, text)
     return text
+
+
+def plan_routes(mlir_text: str, num_replicas: int = 1) -> list:
+    """For every tensor-core GEMM step of the program's launch plan, the kernel variant the launcher will pick (no GPU
+    needed): a list of dicts with the problem size, tile width `bn`, the id of the build-time specialised epilogue
+    (`static_id`, 0 = interpreted), `epi_groups`, `transposed`, `group_m`, tile counts, `stores` and `ctas`."""
+    import ctypes as C
+    from .pjrt import PjrtError
+    if not KERNELS_PATH.exists():
+        raise FileNotFoundError(f"{KERNELS_PATH} is missing: run `python -m ryft_b200.build`")
+    lib = C.CDLL(str(KERNELS_PATH))
+    data = mlir_text.encode() if isinstance(mlir_text, str) else bytes(mlir_text)
+    cap = 1 << 20
+    out = C.create_string_buffer(cap)
+    n = C.c_size_t(0)
+    lib.b2x_plan_routes.argtypes = [C.c_char_p, C.c_size_t, C.c_int, C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t)]
+    code = lib.b2x_plan_routes(data, len(data), num_replicas, out, cap, C.byref(n))
+    text = out.value.decode("utf-8", "replace")
+    if code:
+        raise PjrtError(code, text)
+    keys = ("M", "N", "K", "batch", "bn", "static_id", "epi_groups", "transposed", "group_m", "m_tiles", "n_tiles", "k_blocks", "stores", "ctas")
+    rows = []
+    for line in text.splitlines():
+        parts = line.split("|")
+        row = {"label": parts[0]}
+        row.update({k: int(v) for k, v in zip(keys, parts[1:])})
+        rows.append(row)
+    return rows

@@ -119,10 +119,11 @@ def _gelu_tanh_grad(b: Builder, h: Value) -> Value:
     return b.add(left, right)
 
 
-def c4_program(T=8192, D=4096, F=16384, replicas: int = 0) -> str:
+def c4_program(T=8192, D=4096, F=16384, replicas: int = 0, trace: bool = False) -> str:
     """Forward H = X W1, A = gelu(H), Y = A W2, loss = mean(Y^2); backward dW2 = A^T dY, dA = dY W2^T,
     dH = dA * gelu'(H), dW1 = X^T dH.  With replicas > 0 the gradients go through stablehlo.all_reduce over
-    all replicas and are divided by the replica count (config 5)."""
+    all replicas and are divided by the replica count (config 5).  With `trace` the intermediates that pass between the
+    GEMMs are returned as well: (dW1, dW2, loss, H, A, Y, dY, dH)."""
     b = Builder()
     x = b.arg([T, D], "bf16")
     w1 = b.arg([D, F], "bf16")
@@ -146,7 +147,38 @@ def c4_program(T=8192, D=4096, F=16384, replicas: int = 0) -> str:
         inv = 1.0 / replicas
         dw1 = b.multiply(dw1, b.splat(inv, dw1))
         dw2 = b.multiply(dw2, b.splat(inv, dw2))
+    if trace:
+        return b.build(dw1, dw2, loss, h, a, y, dy, dh)
     return b.build(dw1, dw2, loss)
+
+
+def c4_stage_programs(T=8192, D=4096, F=16384) -> dict:
+    """The five GEMMs of config 4, each with the elementwise work that the planner fuses into it, as programs of their own:
+    name -> (text, argument names, result names), the names being those of `c4_program(trace=True)`.  Feeding every stage
+    the expected values of its inputs checks each kernel at the benchmark's size without the compounding of rounding
+    differences along the chain of bf16 intermediates."""
+    n = float(T) * float(D)
+    out = {}
+    b = Builder()
+    x = b.arg([T, D], "bf16"); w1 = b.arg([D, F], "bf16")
+    hf = b.dot_general(x, w1, ([], []), ([1], [0]), out_dtype="f32")
+    g, _ = _gelu_tanh(b, hf)
+    out["forward 1"] = (b.build(b.convert(hf, "bf16"), b.convert(g, "bf16")), ("x", "w1"), ("h", "a"))
+    b = Builder()
+    a = b.arg([T, F], "bf16"); w2 = b.arg([F, D], "bf16")
+    y = b.dot_general(a, w2, ([], []), ([1], [0]), out_dtype="f32")
+    out["forward 2"] = (b.build(y, b.convert(b.multiply(y, b.splat(2.0 / n, y)), "bf16")), ("a", "w2"), ("y", "dy"))
+    b = Builder()
+    a = b.arg([T, F], "bf16"); dy = b.arg([T, D], "bf16")
+    out["dW2"] = (b.build(b.dot_general(a, dy, ([], []), ([0], [0]), out_dtype="f32")), ("a", "dy"), ("dw2",))
+    b = Builder()
+    dy = b.arg([T, D], "bf16"); w2 = b.arg([F, D], "bf16"); h = b.arg([T, F], "bf16")
+    da = b.dot_general(dy, w2, ([], []), ([1], [1]), out_dtype="f32")
+    out["dH"] = (b.build(b.convert(b.multiply(da, _gelu_tanh_grad(b, b.convert(h, "f32"))), "bf16")), ("dy", "w2", "h"), ("dh",))
+    b = Builder()
+    x = b.arg([T, D], "bf16"); dh = b.arg([T, F], "bf16")
+    out["dW1"] = (b.build(b.dot_general(x, dh, ([], []), ([0], [0]), out_dtype="f32")), ("x", "dh"), ("dw1",))
+    return out
 
 
 def c4_inputs(T=8192, D=4096, F=16384, seed=3, replica: int | None = None):

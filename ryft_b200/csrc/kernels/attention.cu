@@ -20,6 +20,7 @@
 // Causal tiles above the diagonal are skipped; the diagonal block and ragged key tails are masked in registers.
 // Bound: tensor pipe / MUFU (exp2), about equal for D = 128; algorithmic FLOPs = 4 * BH * D * (unmasked scores).
 // Every wait is bounded; on expiry the CTA unwinds, frees TMEM and reports through `status`.
+#include <atomic>
 #include "../../../include/b2x_kernels.h"
 #include "common.cuh"
 #include "sm100.cuh"
@@ -167,7 +168,7 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
           }
         }
         if (progress) { idle = 0; continue; }
-        if (++idle > (1u << 22)) { *abort_flag = 1; atomicCAS(status, 0, 11); ok = false; break; }
+        if (++idle > (1u << 22)) { *abort_flag = 1; if (status) atomicCAS(status, 0, 11); ok = false; break; }
         if (idle > 16) { if (*abort_flag) { ok = false; break; } __nanosleep(idle > 4096 ? 256 : 32); }
       }
       if (!ok) {
@@ -412,11 +413,11 @@ static int launch_attention(const B2xAttentionArgs* a, int32_t* status, cudaStre
   {
     int dev = 0;
     cudaGetDevice(&dev);
-    static bool configured[64] = {};
-    if (dev < 0 || dev >= 64 || !configured[dev]) {
+    static std::atomic<bool> configured[64];
+    if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL);
       if (e != cudaSuccess) return (int)e;
-      if (dev >= 0 && dev < 64) configured[dev] = true;
+      if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
     }
   }
   const int64_t grid = (int64_t)p.n_q_tiles * a->BH;

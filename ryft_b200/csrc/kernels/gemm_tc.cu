@@ -2,18 +2,21 @@
 #include "gemm_tc.cuh"
 
 #include <atomic>
+#include <map>
 #include <mutex>
 
 namespace b2x {
 
 static __device__ int32_t g_sched[kSchedSlots * 2];
 
-// Next scheduler pair for the current device (round robin).  Only the address of the array is taken here; device
-// code reads and resets it.
-int32_t* sched_slot() {
+// Scheduler pair for launches on `stream` of the current device.  Launches on one stream run in order, and a pair is
+// back at zero when its launch retires, so every stream can keep one pair for good; launches that may overlap (different
+// streams) never share a tile counter.  Only the address of the array is taken here; device code reads and resets it.
+// Returns nullptr when more than kSchedSlots different streams have launched GEMMs on this device.
+int32_t* sched_slot(cudaStream_t stream) {
   static std::mutex mu;
   static int32_t* base[64] = {};
-  static unsigned next[64] = {};
+  static std::map<cudaStream_t, int> slot_of[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
   std::lock_guard<std::mutex> lk(mu);
@@ -22,7 +25,12 @@ int32_t* sched_slot() {
     if (cudaGetSymbolAddress(&p, g_sched) != cudaSuccess) return nullptr;
     base[dev] = (int32_t*)p;
   }
-  return base[dev] + 2 * (next[dev]++ % kSchedSlots);
+  auto it = slot_of[dev].find(stream);
+  if (it == slot_of[dev].end()) {
+    if ((int)slot_of[dev].size() >= kSchedSlots) return nullptr;
+    it = slot_of[dev].emplace(stream, (int)slot_of[dev].size()).first;
+  }
+  return base[dev] + 2 * it->second;
 }
 
 // ---- f32 -> hi/lo TF32 split for the 3xTF32 scheme ------------------------------------------------------------------
@@ -105,22 +113,32 @@ extern "C" int b2x_launch_split_f32(const B2xGemmArgs* a, float* a_split, float*
   return (int)cudaGetLastError();
 }
 
-extern "C" int b2x_launch_gemm_tc(const B2xGemmArgs* a, const B2xVmProgram* epilogue, int32_t* status, b2x_stream_t stream_) {
-  using namespace b2x;
-  cudaStream_t stream = (cudaStream_t)stream_;
+namespace b2x {
+// Everything the launcher decides from the problem's shape and the epilogue program, before any device work.
+struct TcRoute {
+  bool tf32 = false, a_mn = false, b_mn = false;
+  int es = 2, BK = 64, CHUNK = 64, BN = 256;
+  int64_t a_ld = 0, b_ld = 0;
+  int static_id = 0;        // build-time specialised epilogue that will run (0: the interpreter)
+  TcParams p{};
+};
+
+static int tc_route(const B2xGemmArgs* a, const B2xVmProgram* epilogue, TcRoute* r) {
   if (a->batch <= 0 || a->M <= 0 || a->N <= 0 || a->K <= 0) return (int)cudaErrorInvalidValue;
-  const bool tf32 = a->elem == EL_F32;
-  if (!tf32 && a->elem != EL_BF16 && a->elem != EL_F16) return (int)cudaErrorInvalidValue;
-  const int es = tf32 ? 4 : 2;
-  const int BK = 128 / es, CHUNK = 128 / es;
+  r->tf32 = a->elem == EL_F32;
+  if (!r->tf32 && a->elem != EL_BF16 && a->elem != EL_F16) return (int)cudaErrorInvalidValue;
+  const int es = r->es = r->tf32 ? 4 : 2;
+  const int BK = r->BK = 128 / es;
+  r->CHUNK = 128 / es;
   const int64_t al = 16 / es;
-  const bool a_mn = !(a->a_k_stride == 1) && a->a_row_stride == 1;
-  const bool b_mn = !(a->b_k_stride == 1) && a->b_row_stride == 1;
-  if (!a_mn && a->a_k_stride != 1) return (int)cudaErrorInvalidValue;
-  if (!b_mn && a->b_k_stride != 1) return (int)cudaErrorInvalidValue;
-  const int64_t a_ld = a_mn ? a->a_k_stride : a->a_row_stride, b_ld = b_mn ? a->b_k_stride : a->b_row_stride;
-  if (a_ld % al || b_ld % al || (a->batch > 1 && (a->a_batch_stride % al || a->b_batch_stride % al))) return (int)cudaErrorInvalidValue;
-  if (((uintptr_t)a->a & 15) || ((uintptr_t)a->b & 15) || a->N % 8) return (int)cudaErrorInvalidValue;
+  r->a_mn = !(a->a_k_stride == 1) && a->a_row_stride == 1;
+  r->b_mn = !(a->b_k_stride == 1) && a->b_row_stride == 1;
+  if (!r->a_mn && a->a_k_stride != 1) return (int)cudaErrorInvalidValue;
+  if (!r->b_mn && a->b_k_stride != 1) return (int)cudaErrorInvalidValue;
+  r->a_ld = r->a_mn ? a->a_k_stride : a->a_row_stride;
+  r->b_ld = r->b_mn ? a->b_k_stride : a->b_row_stride;
+  if (r->a_ld % al || r->b_ld % al || (a->batch > 1 && (a->a_batch_stride % al || a->b_batch_stride % al))) return (int)cudaErrorInvalidValue;
+  if (a->N % 8) return (int)cudaErrorInvalidValue;
   // widest tile that the result allows; a problem with fewer tiles than half the SMs takes narrower ones, so that
   // more SMs share the operand traffic (each CTA streams its own A and B tiles)
   int BN = a->N >= 256 ? 256 : (a->N >= 128 ? 128 : 64);
@@ -128,18 +146,10 @@ extern "C" int b2x_launch_gemm_tc(const B2xGemmArgs* a, const B2xVmProgram* epil
     const int64_t m_tiles = (a->M + TC_BM - 1) / TC_BM;
     while (BN > 64 && m_tiles * ((a->N + BN - 1) / BN) * a->batch < kNumSms / 2) BN /= 2;
   }
-  CUtensorMapDataType dt = tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : (a->elem == EL_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
-  CUtensorMap tmA, tmB;
-  bool ok;
-  if (!a_mn) ok = encode_3d(&tmA, dt, es, a->a, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->batch, (uint64_t)a_ld, (uint64_t)a->a_batch_stride, BK, TC_BM);
-  else ok = encode_3d(&tmA, dt, es, a->a, (uint64_t)a->M, (uint64_t)a->K, (uint64_t)a->batch, (uint64_t)a_ld, (uint64_t)a->a_batch_stride, CHUNK, BK);
-  if (!ok) return (int)cudaErrorInvalidValue;
-  if (!b_mn) ok = encode_3d(&tmB, dt, es, a->b, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->batch, (uint64_t)b_ld, (uint64_t)a->b_batch_stride, BK, BN);
-  else ok = encode_3d(&tmB, dt, es, a->b, (uint64_t)a->N, (uint64_t)a->K, (uint64_t)a->batch, (uint64_t)b_ld, (uint64_t)a->b_batch_stride, CHUNK, BK);
-  if (!ok) return (int)cudaErrorInvalidValue;
-  TcParams p{};
+  r->BN = BN;
+  TcParams& p = r->p;
   p.batch = a->batch; p.M = a->M; p.N = a->N; p.K = a->K;
-  p.a_mn_major = a_mn; p.b_mn_major = b_mn;
+  p.a_mn_major = r->a_mn; p.b_mn_major = r->b_mn;
   p.num_m_tiles = (int)((a->M + TC_BM - 1) / TC_BM);
   p.num_n_tiles = (int)((a->N + BN - 1) / BN);
   p.num_tiles = (int64_t)p.num_m_tiles * p.num_n_tiles * a->batch;
@@ -156,20 +166,57 @@ extern "C" int b2x_launch_gemm_tc(const B2xGemmArgs* a, const B2xVmProgram* epil
     if (gm > p.num_m_tiles) gm = p.num_m_tiles;
     p.group_m = (int)gm;
   }
-  p.idesc = sm100::make_idesc(tf32 ? 2u : (a->elem == EL_BF16 ? 1u : 0u), a_mn, b_mn, TC_BM, (uint32_t)BN);
+  p.idesc = sm100::make_idesc(r->tf32 ? 2u : (a->elem == EL_BF16 ? 1u : 0u), r->a_mn, r->b_mn, TC_BM, (uint32_t)BN);
+  const int id = vm_static_lookup(vm_signature_hash(*epilogue));
+  r->static_id = (id && (r->tf32 ? tc_static_has_tf32(id, BN) : tc_static_has(id, BN))) ? id : 0;
+  return 0;
+}
+}  // namespace b2x
+
+extern "C" int b2x_gemm_tc_route(const B2xGemmArgs* a, const B2xVmProgram* epilogue, int32_t out[10]) {
+  using namespace b2x;
+  TcRoute r;
+  int rc = tc_route(a, epilogue, &r);
+  if (rc) return rc;
+  out[0] = r.BN; out[1] = r.static_id; out[2] = r.p.epi_groups;
+  out[3] = (r.static_id && r.p.transposed && tc_static_stores(r.static_id) >= 2) ? 1 : 0;
+  out[4] = r.p.group_m; out[5] = r.p.num_m_tiles; out[6] = r.p.num_n_tiles; out[7] = r.p.k_blocks;
+  out[8] = r.static_id ? tc_static_stores(r.static_id) : 0;
+  out[9] = (int32_t)(r.p.num_tiles < kNumSms ? r.p.num_tiles : kNumSms);
+  return 0;
+}
+
+extern "C" int b2x_launch_gemm_tc(const B2xGemmArgs* a, const B2xVmProgram* epilogue, int32_t* status, b2x_stream_t stream_) {
+  using namespace b2x;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  TcRoute r;
+  int rc = tc_route(a, epilogue, &r);
+  if (rc) return rc;
+  if (((uintptr_t)a->a & 15) || ((uintptr_t)a->b & 15)) return (int)cudaErrorInvalidValue;
+  const bool tf32 = r.tf32, a_mn = r.a_mn, b_mn = r.b_mn;
+  const int es = r.es, BK = r.BK, CHUNK = r.CHUNK, BN = r.BN;
+  const int64_t a_ld = r.a_ld, b_ld = r.b_ld;
+  CUtensorMapDataType dt = tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : (a->elem == EL_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+  CUtensorMap tmA, tmB;
+  bool ok;
+  if (!a_mn) ok = encode_3d(&tmA, dt, es, a->a, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->batch, (uint64_t)a_ld, (uint64_t)a->a_batch_stride, BK, TC_BM);
+  else ok = encode_3d(&tmA, dt, es, a->a, (uint64_t)a->M, (uint64_t)a->K, (uint64_t)a->batch, (uint64_t)a_ld, (uint64_t)a->a_batch_stride, CHUNK, BK);
+  if (!ok) return (int)cudaErrorInvalidValue;
+  if (!b_mn) ok = encode_3d(&tmB, dt, es, a->b, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->batch, (uint64_t)b_ld, (uint64_t)a->b_batch_stride, BK, BN);
+  else ok = encode_3d(&tmB, dt, es, a->b, (uint64_t)a->N, (uint64_t)a->K, (uint64_t)a->batch, (uint64_t)b_ld, (uint64_t)a->b_batch_stride, CHUNK, BK);
+  if (!ok) return (int)cudaErrorInvalidValue;
+  const TcParams& p = r.p;
   if (tf32) {
-    const int id32 = vm_static_lookup(vm_signature_hash(*epilogue));
-    if (id32) {
-      int rc = launch_tc_static_tf32(id32, BN, tmA, tmB, p, *epilogue, status, stream);
+    if (r.static_id) {
+      rc = launch_tc_static_tf32(r.static_id, BN, tmA, tmB, p, *epilogue, status, stream);
       if (rc >= 0) return rc;
     }
     if (BN == 256) return launch_tc<256, 4, true, 0>(tmA, tmB, p, *epilogue, status, stream);
     if (BN == 128) return launch_tc<128, 6, true, 0>(tmA, tmB, p, *epilogue, status, stream);
     return launch_tc<64, 8, true, 0>(tmA, tmB, p, *epilogue, status, stream);
   }
-  const int id = vm_static_lookup(vm_signature_hash(*epilogue));
-  if (id) {
-    int rc = launch_tc_static(id, BN, tmA, tmB, p, *epilogue, status, stream);
+  if (r.static_id) {
+    rc = launch_tc_static(r.static_id, BN, tmA, tmB, p, *epilogue, status, stream);
     if (rc >= 0) return rc;
   }
   if (BN == 256) return launch_tc<256, 4, false, 0>(tmA, tmB, p, *epilogue, status, stream);

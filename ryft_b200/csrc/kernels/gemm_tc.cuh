@@ -17,7 +17,9 @@
 // Bound: tensor pipe for K >= ~1024 (algorithmic FLOPs = 2*B*M*N*K); HBM (output bytes) for short K.
 // Every mbarrier wait is bounded (sm100.cuh); on expiry the CTA unwinds, frees TMEM and reports through `status`.
 #pragma once
+#include <atomic>
 #include <type_traits>
+#include <cstdlib>
 #include <cstring>
 #include "../../../include/b2x_kernels.h"
 #include "common.cuh"
@@ -38,6 +40,7 @@ struct TcParams {
   int32_t group_m;     // m-tiles per raster group: a group's A slab stays in L2 while its n-tiles stream by
   uint32_t idesc;
   int32_t* sched;      // [0] next tile to hand out, [1] CTAs that have finished (the last one resets both)
+  int32_t withhold;    // test switch: CTA 0 never announces its first tile, so that the waits of its other roles run out
 };
 
 constexpr int TC_BM = 128;
@@ -185,7 +188,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         int b = 0, m0 = 0, n0 = 0;
         if (t >= 0) tc_tile_coords(p, t, BN, &b, &m0, &n0);
         tile_ring[slot * 4 + 0] = (int32_t)t; tile_ring[slot * 4 + 1] = b; tile_ring[slot * 4 + 2] = m0; tile_ring[slot * 4 + 3] = n0;
-        mbar_arrive(bar_sfull + 8 * slot);
+        if (!(p.withhold && local == 0 && blockIdx.x == 0)) mbar_arrive(bar_sfull + 8 * slot);
         if (t < 0 && p.epi_groups == 1) break;
         if (t < 0) {
           // the other epilogue group reads the ring entry after this one: it gets its own end marker
@@ -446,16 +449,22 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   }
 }
 
-// Scheduler counters: a ring of (next tile, finished CTAs) pairs in device memory, one pair per launch in flight.
+// Scheduler counters: (next tile, finished CTAs) pairs in device memory, one pair per stream that launches GEMMs.
 // A pair returns to zero when its launch retires, so no memset is needed between launches.
 constexpr int kSchedSlots = 256;
-int32_t* sched_slot();   // defined in gemm_tc.cu
+int32_t* sched_slot(cudaStream_t stream);   // defined in gemm_tc.cu
 
 template <int BN, int STAGES, bool TF32, int ID>
 static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p_in, const B2xVmProgram& epi, int32_t* status, cudaStream_t stream) {
   TcParams p = p_in;
-  p.sched = sched_slot();
-  if (!p.sched) return (int)cudaErrorUnknown;
+  p.sched = sched_slot(stream);
+  if (!p.sched) return (int)cudaErrorLaunchOutOfResources;
+  // B2X_DEBUG_WITHHOLD_ARRIVE=1 (tests of the bounded waits): one arrival is left out, the kernel gives up after about a
+  // second, reports through `status` and returns by itself
+  {
+    const char* w = getenv("B2X_DEBUG_WITHHOLD_ARRIVE");
+    p.withhold = (w && w[0] == '1') ? 1 : 0;
+  }
   using SM = TcSmem<BN, STAGES, TF32, tc_transposed_epilogue<ID>() || tc_tma_store_epilogue<ID>()>;
   CUtensorMap tmOut;
   memset(&tmOut, 0, sizeof(tmOut));
@@ -478,11 +487,11 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcPar
     // per device: the attribute belongs to the function on the current device
     int dev = 0;
     cudaGetDevice(&dev);
-    static bool configured[64] = {};
-    if (dev < 0 || dev >= 64 || !configured[dev]) {
+    static std::atomic<bool> configured[64];
+    if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL);
       if (e != cudaSuccess) return (int)e;
-      if (dev >= 0 && dev < 64) configured[dev] = true;
+      if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
     }
   }
   int64_t grid = p.num_tiles < kNumSms ? p.num_tiles : kNumSms;
@@ -500,4 +509,8 @@ int launch_tc_static(int id, int BN, const CUtensorMap& tmA, const CUtensorMap& 
 // Same for f32 operands (3xTF32); only the plain f32 store is specialised there.
 int launch_tc_static_tf32(int id, int BN, const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, const B2xVmProgram& epi, int32_t* status,
                           cudaStream_t stream);
+// Whether a specialised kernel exists for (program id, tile width), and how many stores that program has.
+bool tc_static_has(int id, int BN);
+bool tc_static_has_tf32(int id, int BN);
+int tc_static_stores(int id);
 }  // namespace b2x

@@ -38,4 +38,26 @@ int launch_tc_static_tf32(int id, int BN, const CUtensorMap& tmA, const CUtensor
   return -1;
 }
 
+bool tc_static_has(int id, int BN) {
+#define X(I, W) if (id == I && BN == W) return true;
+  B2X_VM_STATIC_GEMM(X)
+#undef X
+  (void)id; (void)BN;
+  return false;
+}
+bool tc_static_has_tf32(int id, int BN) {
+#define X(I, W) if (id == I && BN == W) return tc_plain_f32_store<I>();
+  B2X_VM_STATIC_GEMM(X)
+#undef X
+  (void)id; (void)BN;
+  return false;
+}
+int tc_static_stores(int id) {
+#define X(I, W) if (id == I) return vm_static_stores<I>();
+  B2X_VM_STATIC_GEMM(X)
+#undef X
+  (void)id;
+  return 0;
+}
+
 }  // namespace b2x

@@ -5,9 +5,13 @@
 //     128-bit vector loads, folds lanes in registers, then warp shuffles and one shared-memory step.
 //   B  > 1 (column reduction): threads are laid out [ry][bx]; each owns V adjacent columns and strides over R, so a
 //     warp reads one contiguous span per row; the ry partials meet in shared memory.
-// Long reductions with few outputs are cut into S splits whose partials land in scratch and are folded by a second
-// launch of the same kernel.  HBM-bound: algorithmic bytes = one read of every operand of the prologue.
+// Long reductions with few outputs are cut into S splits whose partials land in scratch.  A row reduction folds them in
+// the same launch: every CTA takes a ticket when its partials are written, and the CTA that draws the last ticket folds
+// all of them, in index order, so the result does not depend on which CTA that is.  A column reduction folds them with
+// a second launch.  The final value of each output can be handed to a fused consumer program (its VM_SRC_ACC0), which
+// then does the stores.  HBM-bound: algorithmic bytes = one read of every operand of the prologue.
 #include <cstdio>
+#include <map>
 #include <mutex>
 
 #include "../../../include/b2x_kernels.h"
@@ -56,10 +60,20 @@ struct ReduceKArgs {
   uint32_t init_imm;
   const void* init_ptr;
   void* out;           // final output (S == 1) or partials (S > 1, raw 32-bit)
+  // single-launch split reduction: partials go to `out`, the last CTA folds them into `final_out`
+  void* final_out;
+  int32_t* ticket;     // CTAs that have written their partials; the last one resets it
+  int32_t has_post;    // the final value goes to the consumer program Q instead of (or besides) `final_out`
 };
 
-__device__ __forceinline__ void red_write(const ReduceKArgs& K, int64_t index, uint32_t v) {
-  if (K.S > 1) { ((uint32_t*)K.out)[index] = v; return; }
+// Hands one finished output to the fused consumer program: element `index` of the result, value in ACC0.
+static __device__ __noinline__ void red_post(const B2xVmProgram& Q, int64_t index, uint32_t v) {
+  uint32_t a0[1] = {v}, out[1];
+  vm_run<1, 0>(Q, (uint64_t)index, a0, out);
+}
+
+// Combines a reduced value with the init operand, rounds it to the result element type and stores it (or passes it on).
+__device__ __forceinline__ void red_finish(const ReduceKArgs& K, const B2xVmProgram& Q, void* dst, int64_t index, uint32_t v) {
   uint32_t init = K.init_imm;
   if (K.init_ptr) {
     uint32_t raw;
@@ -69,14 +83,22 @@ __device__ __forceinline__ void red_write(const ReduceKArgs& K, int64_t index, u
   }
   v = red_combine(init, v, K.monoid, K.cls);
   uint32_t enc = vm_encode(v, (uint8_t)K.out_elem);
+  if (K.has_post) { red_post(Q, index, vm_decode(enc, (uint8_t)K.out_elem)); return; }
   const int es = vm_elem_size((uint8_t)K.out_elem);
-  if (es == 4) ((uint32_t*)K.out)[index] = enc; else if (es == 2) ((uint16_t*)K.out)[index] = (uint16_t)enc; else ((uint8_t*)K.out)[index] = (uint8_t)enc;
+  if (es == 4) ((uint32_t*)dst)[index] = enc; else if (es == 2) ((uint16_t*)dst)[index] = (uint16_t)enc; else ((uint8_t*)dst)[index] = (uint8_t)enc;
+}
+
+__device__ __forceinline__ void red_write(const ReduceKArgs& K, const B2xVmProgram& Q, int64_t index, uint32_t v) {
+  if (K.S > 1) { ((uint32_t*)K.out)[index] = v; return; }
+  red_finish(K, Q, K.out, index, v);
 }
 
 // Row reduction.  T = threads cooperating on one (row, split) piece: 32 or 256.
 template <int V, int T, int ID, int MC>
-__global__ void __launch_bounds__(256) k_reduce_rows(const __grid_constant__ B2xVmProgram P, const __grid_constant__ ReduceKArgs K) {
+__global__ void __launch_bounds__(256, ID != 0 ? 4 : 1) k_reduce_rows(const __grid_constant__ B2xVmProgram P, const __grid_constant__ ReduceKArgs K,
+                                                                       const __grid_constant__ B2xVmProgram Q) {
   __shared__ uint32_t smem[8];
+  __shared__ int s_last;
   constexpr int PIECES_PER_CTA = 256 / T;
   const int lane_in_piece = threadIdx.x % T;
   const int64_t n_pieces = K.A * K.S;
@@ -90,27 +112,31 @@ __global__ void __launch_bounds__(256) k_reduce_rows(const __grid_constant__ B2x
     const int64_t piece = piece0 + threadIdx.x / T;
     uint32_t total = ident;
     if (piece < n_pieces) {
+      // The S pieces of a row interleave: piece s takes the blocks s, s + S, s + 2S, ... of T * V elements, so that at
+      // any moment the pieces of a row read neighbouring addresses (the whole grid sweeps the row together, which is what
+      // DRAM likes) instead of S streams that are far apart.  With S == 1 this is the plain walk over the row.
       const int64_t a = piece / K.S, s = piece % K.S;
-      const int64_t r0 = s * K.chunk;
-      const int64_t r1 = min(K.R, r0 + K.chunk);
-      int64_t r = r0 + (int64_t)lane_in_piece * V;
+      constexpr int64_t BLOCK = (int64_t)T * V;
+      const int64_t STEP = BLOCK * K.S;
+      const int64_t r1 = K.R;
+      int64_t r = s * BLOCK + (int64_t)lane_in_piece * V;
       if constexpr (ID != 0) {
-        // specialised programs are short: two vectors per trip, so that both vectors' loads are in flight together
+        // specialised programs are short: four vectors per trip, so that all four vectors' loads are in flight together
         // (the kernel is bound by memory latency, not by issue slots)
-        uint32_t total2 = ident;
-        for (; r + (int64_t)T * V < r1; r += 2 * (int64_t)T * V) {
-          uint32_t acc[V], acc2[V];
-          vm_run_at<V, ID>(P, (uint64_t)(a * K.R + r), rows2, a, r, zero, acc);
-          vm_run_at<V, ID>(P, (uint64_t)(a * K.R + r + (int64_t)T * V), rows2, a, r + (int64_t)T * V, zero, acc2);
+        uint32_t tot[4] = {ident, ident, ident, ident};
+        for (; r + 3 * STEP < r1; r += 4 * STEP) {
+          uint32_t acc[4][V];
+#pragma unroll
+          for (int u = 0; u < 4; u++) vm_run_at<V, ID>(P, (uint64_t)(a * K.R + r + u * STEP), rows2, a, r + u * STEP, zero, acc[u]);
 #pragma unroll
           for (int j = 0; j < V; j++) {
-            total = red_combine_t<MC>(total, acc[j], K.monoid, K.cls);
-            total2 = red_combine_t<MC>(total2, acc2[j], K.monoid, K.cls);
+#pragma unroll
+            for (int u = 0; u < 4; u++) tot[u] = red_combine_t<MC>(tot[u], acc[u][j], K.monoid, K.cls);
           }
         }
-        total = red_combine_t<MC>(total, total2, K.monoid, K.cls);
+        total = red_combine_t<MC>(red_combine_t<MC>(tot[0], tot[1], K.monoid, K.cls), red_combine_t<MC>(tot[2], tot[3], K.monoid, K.cls), K.monoid, K.cls);
       }
-      for (; r < r1; r += (int64_t)T * V) {
+      for (; r < r1; r += STEP) {
         uint32_t acc[V];
         vm_run_at<V, ID>(P, (uint64_t)(a * K.R + r), rows2, a, r, zero, acc);
 #pragma unroll
@@ -120,7 +146,7 @@ __global__ void __launch_bounds__(256) k_reduce_rows(const __grid_constant__ B2x
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) total = red_combine_t<MC>(total, __shfl_xor_sync(0xffffffffu, total, off), K.monoid, K.cls);
     if (T == 32) {
-      if (lane_in_piece == 0 && piece < n_pieces) red_write(K, piece, total);
+      if (lane_in_piece == 0 && piece < n_pieces) red_write(K, Q, piece, total);
     } else {
       __syncthreads();
       if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = total;
@@ -129,15 +155,44 @@ __global__ void __launch_bounds__(256) k_reduce_rows(const __grid_constant__ B2x
         uint32_t t = smem[0];
 #pragma unroll
         for (int w = 1; w < 8; w++) t = red_combine(t, smem[w], K.monoid, K.cls);
-        if (piece < n_pieces) red_write(K, piece, t);
+        if (piece < n_pieces) red_write(K, Q, piece, t);
       }
+    }
+  }
+  if (K.S > 1 && K.ticket != nullptr) {
+    // this CTA's partials are in memory: take a ticket; whoever draws the last one folds all partials
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = (atomicAdd(K.ticket, 1) == (int)gridDim.x - 1) ? 1 : 0;
+    __syncthreads();
+    if (s_last) {
+      __threadfence();
+      const uint32_t* parts = (const uint32_t*)K.out;
+      for (int64_t a = 0; a < K.A; a++) {
+        uint32_t v = ident;
+        for (int64_t i = threadIdx.x; i < K.S; i += 256) v = red_combine(v, __ldcg(parts + a * K.S + i), K.monoid, K.cls);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v = red_combine(v, __shfl_xor_sync(0xffffffffu, v, off), K.monoid, K.cls);
+        __syncthreads();
+        if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = v;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          uint32_t t = smem[0];
+#pragma unroll
+          for (int w = 1; w < 8; w++) t = red_combine(t, smem[w], K.monoid, K.cls);
+          ReduceKArgs F = K;
+          F.S = 1;
+          red_finish(F, Q, K.final_out, a, t);
+        }
+      }
+      if (threadIdx.x == 0) { *K.ticket = 0; __threadfence(); }
     }
   }
 }
 
 // Column reduction.  blockDim = (BX, RY) with BX * RY = 256; thread (bx, ry) owns V adjacent columns.
 template <int V>
-__global__ void __launch_bounds__(256) k_reduce_cols(const __grid_constant__ B2xVmProgram P, const __grid_constant__ ReduceKArgs K, int n_bblocks) {
+__global__ void __launch_bounds__(256) k_reduce_cols(const __grid_constant__ B2xVmProgram P, const __grid_constant__ ReduceKArgs K, const __grid_constant__ B2xVmProgram Q, int n_bblocks) {
   __shared__ uint32_t smem[256 * V];
   const int BX = blockDim.x, RY = blockDim.y;
   const int64_t n_work = K.A * K.S * (int64_t)n_bblocks;
@@ -172,12 +227,12 @@ __global__ void __launch_bounds__(256) k_reduce_cols(const __grid_constant__ B2x
         for (int j = 0; j < V; j++) tot[j] = red_combine(tot[j], smem[(y * BX + threadIdx.x) * V + j], K.monoid, K.cls);
       }
 #pragma unroll
-      for (int j = 0; j < V; j++) red_write(K, (a * K.S + s) * K.B + b0 + j, tot[j]);
+      for (int j = 0; j < V; j++) red_write(K, Q, (a * K.S + s) * K.B + b0 + j, tot[j]);
     }
   }
 }
 
-static int launch_one(const B2xVmProgram& P, ReduceKArgs K, int vec, cudaStream_t stream) {
+static int launch_one(const B2xVmProgram& P, ReduceKArgs K, const B2xVmProgram& Q, int vec, cudaStream_t stream) {
   const int64_t cap = (int64_t)kNumSms * 24;   // at least the split target: one CTA per piece, dealt out by the hardware
   if (K.B == 1) {
     const int64_t pieces = K.A * K.S;
@@ -189,8 +244,8 @@ static int launch_one(const B2xVmProgram& P, ReduceKArgs K, int vec, cudaStream_
     if (blocks < 1) blocks = 1;
     dim3 grid((unsigned)blocks), block(256);
 #define B2X_ROWS_MC(VV, II, MM)                                                           \
-    if (warp_rows) k_reduce_rows<VV, 32, II, MM><<<grid, block, 0, stream>>>(P, K);       \
-    else k_reduce_rows<VV, 256, II, MM><<<grid, block, 0, stream>>>(P, K);
+    if (warp_rows) k_reduce_rows<VV, 32, II, MM><<<grid, block, 0, stream>>>(P, K, Q);    \
+    else k_reduce_rows<VV, 256, II, MM><<<grid, block, 0, stream>>>(P, K, Q);
     // specialised programs also get a combine fixed at compile time for f32 sum / f32 max
 #define B2X_ROWS(VV, II)                                                                  \
     if (II != 0 && mc == 1) { B2X_ROWS_MC(VV, II, (II != 0 ? 1 : 0)) }                    \
@@ -217,9 +272,9 @@ static int launch_one(const B2xVmProgram& P, ReduceKArgs K, int vec, cudaStream_
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     dim3 grid((unsigned)blocks), block(bx, ry);
-    if (vec == 8) k_reduce_cols<8><<<grid, block, 0, stream>>>(P, K, n_bblocks);
-    else if (vec == 4) k_reduce_cols<4><<<grid, block, 0, stream>>>(P, K, n_bblocks);
-    else k_reduce_cols<1><<<grid, block, 0, stream>>>(P, K, n_bblocks);
+    if (vec == 8) k_reduce_cols<8><<<grid, block, 0, stream>>>(P, K, Q, n_bblocks);
+    else if (vec == 4) k_reduce_cols<4><<<grid, block, 0, stream>>>(P, K, Q, n_bblocks);
+    else k_reduce_cols<1><<<grid, block, 0, stream>>>(P, K, Q, n_bblocks);
   }
   count_launch();
   return (int)cudaGetLastError();
@@ -227,16 +282,49 @@ static int launch_one(const B2xVmProgram& P, ReduceKArgs K, int vec, cudaStream_
 
 }  // namespace b2x
 
+// Ticket counters of the single-launch split reduction: one per stream that launches reductions, in device memory that
+// is part of the library image.  A counter is back at zero when its launch retires (the last CTA resets it), and
+// launches on one stream run in order, so a stream keeps its counter for good and launches that may overlap never
+// share one.
+namespace b2x {
+constexpr int kTicketSlots = 256;
+static __device__ int32_t g_reduce_tickets[kTicketSlots];
+static int32_t* ticket_slot(cudaStream_t stream) {
+  static std::mutex mu;
+  static int32_t* base[64] = {};
+  static std::map<cudaStream_t, int> slot_of[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lk(mu);
+  if (!base[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_reduce_tickets) != cudaSuccess) return nullptr;
+    base[dev] = (int32_t*)p;
+  }
+  auto it = slot_of[dev].find(stream);
+  if (it == slot_of[dev].end()) {
+    if ((int)slot_of[dev].size() >= kTicketSlots) return nullptr;
+    it = slot_of[dev].emplace(stream, (int)slot_of[dev].size()).first;
+  }
+  return base[dev] + it->second;
+}
+}  // namespace b2x
+
 extern "C" int b2x_reduce_splits(int64_t A, int64_t R, int64_t B) {
-  // Enough independent pieces to fill 148 SMs without starving each piece of work.  The target, 24 pieces per SM, is a
-  // whole number of rounds for 1, 2, 3, 4, 6 or 8 resident CTAs per SM (the row kernels use 32 to 48 registers), so no
-  // round is left partly filled whichever the kernel's occupancy.
+  // Enough independent pieces to fill 148 SMs in one wave of four resident CTAs per SM (the specialised row kernels are
+  // built for at most 64 registers), each piece long enough to keep several vectors per thread in flight for several
+  // trips.
   int64_t outputs = A * ((B + 255) / 256 > 1 ? (B + 255) / 256 : 1);
-  if (outputs >= 296 || R < 4096) return 1;
-  int64_t s = (3552 + outputs - 1) / outputs;
+  if (outputs <= 0 || outputs >= 296 || R < 4096) return 1;   // an empty result has nothing to split
+  int64_t s = (592 + outputs - 1) / outputs;
   if (s > R / 2048) s = R / 2048;
   if (s > 4096) s = 4096;
   return (int)(s < 1 ? 1 : s);
+}
+
+extern "C" int b2x_reduce_launches(int64_t A, int64_t R, int64_t B) {
+  if (A <= 0 || B <= 0) return 0;
+  return (b2x_reduce_splits(A, R, B) > 1 && R > 0 && B != 1) ? 2 : 1;
 }
 
 extern "C" int b2x_launch_reduce(const B2xVmProgram* prologue, const B2xReduceArgs* a, b2x_stream_t stream_) {
@@ -251,15 +339,27 @@ extern "C" int b2x_launch_reduce(const B2xVmProgram* prologue, const B2xReduceAr
   K.monoid = a->monoid; K.cls = a->cls;
   K.out_elem = a->out_elem; K.init_elem = a->init_elem;
   K.init_imm = a->init_imm; K.init_ptr = a->init_ptr;
+  K.has_post = a->host_post != nullptr ? 1 : 0;
+  static const B2xVmProgram kNoPost{};
+  const B2xVmProgram& Q = a->host_post ? *a->host_post : kNoPost;
   if (S <= 1 || a->R == 0) {
     K.S = 1; K.chunk = a->R > 0 ? a->R : 1; K.out = a->out;
-    return launch_one(*prologue, K, vec, stream);
+    return launch_one(*prologue, K, Q, vec, stream);
   }
   if (!a->scratch) return (int)cudaErrorInvalidValue;
   int64_t chunk = (a->R + S - 1) / S;
   chunk = (chunk + vec - 1) / vec * vec;
   K.S = S; K.chunk = chunk; K.out = a->scratch;
-  int rc = launch_one(*prologue, K, vec, stream);
+  if (a->B == 1) {
+    // row reduction: the launch folds its own partials (see k_reduce_rows)
+    K.final_out = a->out;
+    K.ticket = ticket_slot(stream);
+    if (!K.ticket) return (int)cudaErrorLaunchOutOfResources;
+    return launch_one(*prologue, K, Q, vec, stream);
+  }
+  ReduceKArgs K1 = K;
+  K1.has_post = 0;
+  int rc = launch_one(*prologue, K1, kNoPost, vec, stream);
   if (rc) return rc;
   // fold the [A, S, B] partials
   B2xVmProgram F{};
@@ -271,8 +371,8 @@ extern "C" int b2x_launch_reduce(const B2xVmProgram* prologue, const B2xReduceAr
   F.code[0].op = VM_LOAD; F.code[0].src_kind = VM_SRC_TENSOR; F.code[0].src_idx = 0; F.code[0].tc = a->cls;
   ReduceKArgs K2 = K;
   K2.R = S; K2.S = 1; K2.chunk = S; K2.out = a->out;
-  int v2 = (a->B == 1) ? ((S % 8 == 0) ? 8 : (S % 4 == 0 ? 4 : 1)) : ((a->B % 8 == 0) ? 8 : (a->B % 4 == 0 ? 4 : 1));
-  return launch_one(F, K2, v2, stream);
+  int v2 = (a->B % 8 == 0) ? 8 : (a->B % 4 == 0 ? 4 : 1);
+  return launch_one(F, K2, Q, v2, stream);
 }
 
 // ---- reduction entry point that allocates nothing ---------------------------------------------------------------------
@@ -312,6 +412,7 @@ extern "C" int b2x_launch_reduce_noalloc(const B2xVmProgram* prologue, const B2x
     return code;
   };
   if (err && err_cap) err[0] = 0;
+  if (a->A <= 0 || a->B <= 0) return 0;   // empty result: nothing to launch
   const int S = b2x_reduce_splits(a->A, a->R, a->B);
   const long long need = S > 1 ? (long long)a->A * S * a->B : 0;
   if (need > B2X_REDUCE_NOALLOC_MAX_PARTIALS)

@@ -6,18 +6,24 @@
 
 #include "plan.h"
 
+// The switches the plugin reads at compile time, so that the host-only helpers below show the plan that would run.
+static b2x::PlanOptions options_from_environment(int num_replicas) {
+  b2x::PlanOptions o;
+  o.num_replicas = num_replicas > 0 ? num_replicas : 1;
+  if (const char* f = getenv("B2X_FUSED_ATTENTION")) o.allow_fused_attention = strcmp(f, "0") != 0;
+  if (const char* f = getenv("B2X_EPILOGUE_FUSION")) o.allow_epilogue_fusion = strcmp(f, "0") != 0;
+  if (const char* g = getenv("B2X_GEMM")) o.allow_tensor_core = strcmp(g, "simt") != 0;
+  if (const char* f = getenv("B2X_PRECISE_MATH")) o.precise_math = strcmp(f, "0") != 0;
+  return o;
+}
+
 extern "C" __attribute__((visibility("default"))) int b2x_plan_dump(const char* mlir, size_t mlir_size, int num_replicas, char* out, size_t out_cap,
                                                                      size_t* out_size) {
   std::string text;
   int code = 0;
   try {
     auto m = b2x::parse_module(std::string(mlir, mlir_size));
-    b2x::PlanOptions o;
-    o.num_replicas = num_replicas > 0 ? num_replicas : 1;
-    // the same switches the plugin reads at compile time, so that a dump shows the plan that would run
-    if (const char* f = getenv("B2X_FUSED_ATTENTION")) o.allow_fused_attention = strcmp(f, "0") != 0;
-    if (const char* f = getenv("B2X_EPILOGUE_FUSION")) o.allow_epilogue_fusion = strcmp(f, "0") != 0;
-    if (const char* g = getenv("B2X_GEMM")) o.allow_tensor_core = strcmp(g, "simt") != 0;
+    b2x::PlanOptions o = options_from_environment(num_replicas);
     text = b2x::build_plan(*m, o, 0).dump();
   } catch (const b2x::CompileError& e) {
     code = e.code;
@@ -88,6 +94,49 @@ extern "C" __attribute__((visibility("default"))) int b2x_plan_signatures(const 
       for (int t = 0; t < P.n_tensors; t++) { mix(P.tensors[t].elem); if (t) elems += ","; elems += std::to_string(P.tensors[t].elem); }
       text += std::string(role) + "|" + std::to_string(bn) + "|" + std::to_string(s.vm.vec) + "|" + std::to_string(h) + "|" + std::to_string(P.n_instr) + "|" + code_s +
               "|" + elems + "|" + s.label + "\n";
+    }
+  } catch (const b2x::CompileError& e) {
+    code = e.code;
+    text = e.what();
+  }
+  if (out_size) *out_size = text.size();
+  if (out && out_cap) {
+    size_t n = text.size() < out_cap - 1 ? text.size() : out_cap - 1;
+    memcpy(out, text.data(), n);
+    out[n] = 0;
+  }
+  return code;
+}
+
+#include "../../../include/b2x_kernels.h"
+
+// Lists, one line per tensor-core GEMM step of the module's plan, the kernel variant the launcher will pick:
+//   label|M|N|K|batch|BN|static id|epilogue groups|transposed|group_m|m tiles|n tiles|k blocks|stores|ctas
+extern "C" __attribute__((visibility("default"))) int b2x_plan_routes(const char* mlir, size_t mlir_size, int num_replicas, char* out, size_t out_cap,
+                                                                       size_t* out_size) {
+  std::string text;
+  int code = 0;
+  try {
+    auto m = b2x::parse_module(std::string(mlir, mlir_size));
+    b2x::PlanOptions o = options_from_environment(num_replicas);
+    b2x::Plan plan = b2x::build_plan(*m, o, 0);
+    for (auto& s : plan.steps) {
+      if (s.kind != b2x::StepKind::GEMM || !s.g_tensor_core) continue;
+      B2xGemmArgs ga{};
+      ga.elem = (uint8_t)s.ga.dtype;
+      ga.batch = s.gB; ga.M = s.gM; ga.N = s.gN; ga.K = s.gK;
+      ga.a_batch_stride = s.ga.batch_stride; ga.a_row_stride = s.ga.row_stride; ga.a_k_stride = s.ga.k_stride;
+      ga.b_batch_stride = s.gb.batch_stride; ga.b_row_stride = s.gb.row_stride; ga.b_k_stride = s.gb.k_stride;
+      if (s.g_split_f32) {
+        ga.K = 3 * s.gK;
+        ga.a_k_stride = 1; ga.a_row_stride = ga.K; ga.a_batch_stride = s.gM * ga.K;
+        ga.b_k_stride = 1; ga.b_row_stride = ga.K; ga.b_batch_stride = s.gN * ga.K;
+      }
+      int32_t r[10] = {};
+      int rc = b2x_gemm_tc_route(&ga, &s.vm.prog, r);
+      text += s.label + "|" + std::to_string(s.gM) + "|" + std::to_string(s.gN) + "|" + std::to_string(ga.K) + "|" + std::to_string(s.gB);
+      for (int i = 0; i < 10; i++) text += "|" + std::to_string(rc ? -1 : r[i]);
+      text += "\n";
     }
   } catch (const b2x::CompileError& e) {
     code = e.code;

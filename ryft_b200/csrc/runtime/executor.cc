@@ -68,9 +68,11 @@ PJRT_Error* run_plan(PJRT_LoadedExecutable* le, int local_index, int replica, co
         ra.out_elem = (uint8_t)s.r_out_dtype; ra.init_elem = (uint8_t)s.r_init_dtype;
         ra.init_imm = s.r_init_imm;
         ra.init_ptr = s.r_init_is_imm ? nullptr : bind(s.r_init_buf);
-        ra.out = bind(s.r_out);
+        ra.out = s.r_out.valid() ? bind(s.r_out) : nullptr;
         ra.scratch = s.scratch.valid() ? bind(s.scratch) : nullptr;
         ra.vec = s.vm.vec;
+        B2xVmProgram post;
+        if (s.has_post) { bind_program(s.post, bind, &post); ra.host_post = &post; }
         int rc = b2x_launch_reduce(&prog, &ra, cs);
         if (rc) return kernel_error(rc, s);
         break;

@@ -200,6 +200,9 @@ struct PJRT_Client {
   std::thread poller;
   std::unique_ptr<b2x::NcclComms> nccl;
   std::atomic<int64_t> executions{0};
+  // Held while an execution that contains collectives enqueues on all of its devices: two such executions started from
+  // different host threads must reach every device's communicator in the same order, or neither collective completes.
+  std::mutex collective_enqueue_mu;
   void post(Pending p);
   ~PJRT_Client();
 };

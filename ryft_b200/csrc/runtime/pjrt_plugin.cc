@@ -172,6 +172,17 @@ static void await_definition(PJRT_Buffer* b) {
   d->cv.wait(lk, [&] { return d->done; });
 }
 
+// A kernel whose bounded wait ran out leaves a non-zero code in the device's status word (mapped host memory).  The
+// first completion on that device that finds it reports DEADLINE_EXCEEDED and clears the word, so that one expiry
+// fails the work that observed it and not every execution and copy that follows.
+static void report_expired_wait(PJRT_Device* dev, PJRT_Error_Code* code, std::string* msg) {
+  if (!dev->status_host) return;
+  const int32_t st = __atomic_exchange_n(&dev->status_host[0], 0, __ATOMIC_ACQ_REL);
+  if (st == 0 || *code != PJRT_Error_Code_OK) return;
+  *code = PJRT_Error_Code_DEADLINE_EXCEEDED;
+  *msg = "a kernel gave up waiting on an internal barrier (status " + std::to_string(st) + ")";
+}
+
 static void release_buffer_memory(PJRT_Buffer* b) {
   if (!b->ptr) return;
   PJRT_Device* d = b->device;
@@ -713,10 +724,7 @@ static PJRT_Error* copy_to_host(PJRT_Buffer* b, void* dst, size_t offset, size_t
   PJRT_Event* pe = new PJRT_Event();
   PJRT_Device* dev = d;
   b->client->post({ev, d->cuda_ordinal, pe, [dev](PJRT_Error_Code* code, std::string* msg) {
-                     if (*code == PJRT_Error_Code_OK && dev->status_host[0] != 0) {
-                       *code = PJRT_Error_Code_DEADLINE_EXCEEDED;
-                       *msg = "a kernel gave up waiting on an internal barrier (status " + std::to_string(dev->status_host[0]) + ")";
-                     }
+                     report_expired_wait(dev, code, msg);
                    }});
   *event = pe;
   return nullptr;
@@ -1141,6 +1149,8 @@ static PJRT_Error* LoadedExecutable_Execute(PJRT_LoadedExecutable_Execute_Args* 
     }
   }
   if (!first_err) {
+    std::unique_lock<std::mutex> coll_order;
+    if (plan0.num_collectives > 0) coll_order = std::unique_lock<std::mutex>(le->client->collective_enqueue_mu);
     auto run_one = [&](size_t k) {
       const int li = locals[k];
       PJRT_Device* dev = le->addressable[li];
@@ -1185,15 +1195,25 @@ static PJRT_Error* LoadedExecutable_Execute(PJRT_LoadedExecutable_Execute_Args* 
       else { cudaEventCreateWithFlags(&ob->ready, cudaEventDisableTiming); cudaEventRecord(ob->ready, done_stream); }
       if (a->output_lists && a->output_lists[k]) a->output_lists[k][o] = ob;
     }
-    // inputs are read by the enqueued kernels: their memory must not be reused before those finish
+    // Inputs are read by the enqueued kernels: their memory must not be reused before those finish.  Memory the plugin
+    // owns is freed in compute-stream order, which covers every reader on that stream; a view of foreign memory needs
+    // an event, and so does any argument of a plan with detached collectives, because those read on the communication
+    // stream, which the compute stream never waits for.
     if (!failed) {
+      const bool comm_readers = done_stream != dev->compute;
       for (size_t i = 0; i < n_args; i++) {
         PJRT_Buffer* b = a->argument_lists[k][i];
-        if (!b->owns) {
+        if (!b->owns || comm_readers) {
           cudaEvent_t keep;
           cudaEventCreateWithFlags(&keep, cudaEventDisableTiming);
-          cudaEventRecord(keep, dev->compute);
+          cudaEventRecord(keep, done_stream);
           std::lock_guard<std::mutex> bl(b->mu);
+          // a buffer that is an argument step after step would otherwise collect one event per execution
+          size_t kept = 0;
+          for (auto ev : b->pending_reads) {
+            if (cudaEventQuery(ev) == cudaSuccess) cudaEventDestroy(ev); else b->pending_reads[kept++] = ev;
+          }
+          b->pending_reads.resize(kept);
           b->pending_reads.push_back(keep);
         }
       }
@@ -1207,10 +1227,7 @@ static PJRT_Error* LoadedExecutable_Execute(PJRT_LoadedExecutable_Execute_Args* 
         cudaEventRecord(ce, done_stream);
         PJRT_Device* d = dev;
         le->client->post({ce, dev->cuda_ordinal, ev, [d](PJRT_Error_Code* code, std::string* msg) {
-                            if (*code == PJRT_Error_Code_OK && d->status_host[0] != 0) {
-                              *code = PJRT_Error_Code_DEADLINE_EXCEEDED;
-                              *msg = "a kernel gave up waiting on an internal barrier (status " + std::to_string(d->status_host[0]) + ")";
-                            }
+                            report_expired_wait(d, code, msg);
                           }});
       }
       a->device_complete_events[k] = ev;
@@ -1247,7 +1264,7 @@ static PJRT_Error* Ext_WaitStream(PJRT_Wait_Until_Buffer_Ready_On_Stream_Args* a
 static int step_kernel_launches(const Step& s) {
   switch (s.kind) {
     case StepKind::ELEMENTWISE: return 1;
-    case StepKind::REDUCE: return reduce_splits(s.rA, s.rR, s.rB) > 1 ? 2 : 1;
+    case StepKind::REDUCE: return reduce_launches(s.rA, s.rR, s.rB);
     case StepKind::GEMM: return s.g_split_f32 ? 2 : 1;
     case StepKind::ATTENTION: return 1;
     default: return 0;

@@ -53,6 +53,8 @@ struct Step {
   DType r_init_dtype = DType::F32;
   BufRef scratch;                  // REDUCE partials, GEMM f32-split operands
   int64_t scratch_bytes = 0;
+  bool has_post = false;           // REDUCE: consumer groups of the result run inside the reduce kernel on each finished value
+  VmBinding post;                  // their program: the result arrives as VM_SRC_ACC0, the program does the stores
 
   // GEMM: C[b][m][n] = sum_k A[b][m][k] * B[b][k][n]; the epilogue program consumes the accumulator
   int64_t gB = 1, gM = 0, gN = 0, gK = 0;
@@ -119,5 +121,7 @@ Plan build_plan(const Module& m, const PlanOptions& opt, int replica);
 // Number of partial results per output element the reduce kernel will use for an [A, R, B] reduction; the planner
 // sizes scratch with it and the launcher uses the same value.
 int reduce_splits(int64_t A, int64_t R, int64_t B);
+// Kernel launches of one reduce step of that shape (a split column reduction folds its partials with a second launch).
+int reduce_launches(int64_t A, int64_t R, int64_t B);
 
 }  // namespace b2x

@@ -21,6 +21,10 @@ namespace {
 
 [[noreturn]] void unimplemented(const std::string& m) { throw CompileError(kUnimplemented, m); }
 [[noreturn]] void internal(const std::string& m) { throw CompileError(kInternal, "planner: " + m); }
+// A fusion group that does not fit the accumulator machine (instructions, tensors, temporaries, index dims).  The
+// planner answers by cutting the group at an interior value; the message reaches the caller only when no cut exists.
+struct GroupTooLarge : CompileError { explicit GroupTooLarge(const std::string& m) : CompileError(kUnimplemented, m) {} };
+[[noreturn]] void too_large(const std::string& m) { throw GroupTooLarge(m); }
 
 struct Layout {
   BufRef buf;
@@ -231,7 +235,7 @@ class Planner {
   }
   BufRef materialise(const Value* v) {
     ValueState& s = st(v);
-    if (s.has_layout && s.layout.buf.valid() && s.preassigned) return s.layout.buf;
+    if (s.has_layout && s.layout.buf.valid() && (s.preassigned || s.alloc >= 0 || s.out_index >= 0)) return s.layout.buf;
     if (const Value* r = in_place_result(v)) {
       BufRef shared = materialise(r);
       st(r).preassigned = true;
@@ -252,6 +256,9 @@ class Planner {
   void match_attention();
   void emit_attention(const Op& op, const AttnMatch& m);
   void emit_group_for_root(const Value* v);
+  bool collect_consumer_roots(const Op& op, const Value* res, std::vector<const Value*>* fused_roots);
+  void force_root(const Value* v);
+  const Value* pick_cut(const Value* root);
   void emit_reduce(const Op& op);
   void emit_dot(const Op& op);
   void emit_view_or_copy(const Op& op);
@@ -336,7 +343,7 @@ void Planner::GroupBuilder::add_output(const Value* v, const BufRef& buf) {
 }
 
 int Planner::GroupBuilder::alloc_temp() {
-  if (free_temps.empty()) unimplemented("an elementwise fusion group needs more than " + std::to_string(B2X_VM_TEMPS) + " live temporaries");
+  if (free_temps.empty()) too_large("an elementwise fusion group needs more than " + std::to_string(B2X_VM_TEMPS) + " live temporaries");
   int t = free_temps.back();
   free_temps.pop_back();
   return t;
@@ -524,9 +531,9 @@ VmBinding Planner::GroupBuilder::finish(int final_node) {
   }
   if (mdims.empty()) { mdims.push_back(1); for (auto& s : mstr) s.push_back(0); }
   if ((int)mdims.size() > B2X_VM_MAX_DIMS)
-    unimplemented("an elementwise fusion group needs more than " + std::to_string(B2X_VM_MAX_DIMS) + " index dimensions after merging");
+    too_large("an elementwise fusion group needs more than " + std::to_string(B2X_VM_MAX_DIMS) + " index dimensions after merging");
   if ((int)tensors.size() > B2X_VM_MAX_TENSORS)
-    unimplemented("an elementwise fusion group touches more than " + std::to_string(B2X_VM_MAX_TENSORS) + " tensors");
+    too_large("an elementwise fusion group touches more than " + std::to_string(B2X_VM_MAX_TENSORS) + " tensors");
 
   // ---- use counts, precision marks ----
   for (auto& n : nodes) for (int i : n.in) nodes[i].uses++;
@@ -566,7 +573,7 @@ VmBinding Planner::GroupBuilder::finish(int final_node) {
     if ((elem == DType::BF16 && prev.rnd == VM_RN_BF16) || (elem == DType::F16 && prev.rnd == VM_RN_F16)) prev.rnd = VM_RN_NONE;
   }
   if ((int)code.size() > B2X_VM_MAX_INSTR)
-    unimplemented("an elementwise fusion group compiles to " + std::to_string(code.size()) + " instructions; the limit is " + std::to_string(B2X_VM_MAX_INSTR));
+    too_large("an elementwise fusion group compiles to " + std::to_string(code.size()) + " instructions; the limit is " + std::to_string(B2X_VM_MAX_INSTR));
 
   VmBinding vb;
   B2xVmProgram& pr = vb.prog;
@@ -807,26 +814,75 @@ void Planner::push_vm_step(VmBinding&& vm, const std::string& label) {
   plan_.steps.push_back(std::move(s));
 }
 
+// Makes an interior value of a group a root of its own, after classification: it is then computed by a group of its
+// own and its former group loads it from memory.
+void Planner::force_root(const Value* v) {
+  ValueState& s = st(v);
+  s.root = true;
+  const int g = n_groups_++;
+  group_root_.push_back(v);
+  root_group_[v] = g;
+  s.groups.clear();
+  s.groups.insert(g);
+}
+
+// Where to cut a group that is too large: the interior value (computed by the group, not cheap, so that it becomes a
+// leaf once it is a root) whose expression holds closest to half of the group's ops.  nullptr when there is none.
+const Value* Planner::pick_cut(const Value* root) {
+  std::map<const Value*, int64_t> ops;   // ops evaluated below a value, counted as a tree
+  std::function<int64_t(const Value*)> count = [&](const Value* v) -> int64_t {
+    if (v != root && load_as_leaf(v)) return 0;
+    if (!v->def) return 0;
+    auto it = ops.find(v);
+    if (it != ops.end()) return it->second;
+    int64_t n = 1;
+    for (auto u : v->def->operands) n += count(u);
+    n = std::min<int64_t>(n, 1 << 20);
+    ops[v] = n;
+    return n;
+  };
+  const int64_t total = count(root);
+  const Value* best = nullptr;
+  int64_t best_dist = 0;
+  for (auto& kv : ops) {
+    const Value* v = kv.first;
+    if (v == root || st(v).cheap || !st(v).fusible || kv.second < 2) continue;
+    const int64_t dist = std::llabs(2 * kv.second - total);
+    if (!best || dist < best_dist || (dist == best_dist && v->id < best->id)) { best = v; best_dist = dist; }
+  }
+  return best;
+}
+
 void Planner::emit_group_for_root(const Value* v) {
   int g = root_group_[v];
   if (emitted_groups_.count(g)) return;
   emitted_groups_.insert(g);
-  GroupBuilder gb;
-  gb.P = this;
-  gb.root_dims = v->type.dims;
-  gb.computing.insert(v);
   BufRef out = materialise(v);
-  gb.add_output(v, out);
-  VmBinding vb = gb.finish(-1);
-  push_vm_step(std::move(vb), std::string("fused:") + op_name(v->def->kind) + ":%" + v->name);
+  for (;;) {
+    GroupBuilder gb;
+    gb.P = this;
+    gb.root_dims = v->type.dims;
+    gb.computing.insert(v);
+    try {
+      gb.add_output(v, out);
+      VmBinding vb = gb.finish(-1);
+      push_vm_step(std::move(vb), std::string("fused:") + op_name(v->def->kind) + ":%" + v->name);
+      return;
+    } catch (const GroupTooLarge&) {
+      const Value* cut = pick_cut(v);
+      if (!cut) throw;
+      force_root(cut);
+      emit_group_for_root(cut);   // may cut again below
+    }
+  }
 }
 
 int reduce_splits_impl(int64_t A, int64_t R, int64_t B) {
-  // Enough independent pieces to fill the machine without starving each piece of work: 24 per SM, a whole number of
-  // rounds for 1, 2, 3, 4, 6 or 8 resident CTAs per SM.  Must agree with b2x_reduce_splits of the kernel library.
+  // Enough independent pieces to fill the machine in one wave of four resident CTAs per SM without starving each piece
+  // of work.  Must agree with b2x_reduce_splits of the kernel library.
   int64_t outputs = A * std::max<int64_t>(1, (B + 255) / 256);
-  if (outputs >= 296 || R < 4096) return 1;
-  int64_t s = std::min<int64_t>((3552 + outputs - 1) / outputs, R / 2048);
+  if (outputs <= 0 || outputs >= 296 || R < 4096) return 1;   // an empty result has nothing to split
+  int64_t s = std::min<int64_t>((592 + outputs - 1) / outputs, R / 2048);
   return (int)std::max<int64_t>(1, std::min<int64_t>(s, 4096));
 }
 
@@ -879,7 +935,19 @@ void Planner::emit_reduce(const Op& op) {
       gb.nodes.push_back(n);
       final_node = 0;
     }
-    s.vm = gb.finish(final_node);
+    try {
+      s.vm = gb.finish(final_node);
+    } catch (const GroupTooLarge&) {
+      // the producing chain does not fit into the prologue: compute the reduced tensor (or part of its chain) with
+      // groups of its own and read it back
+      if (!first || load_as_leaf(x) || st(x).cheap) throw;
+      const Value* cut = pick_cut(x);
+      if (!cut) { cut = x; }
+      force_root(cut);
+      emit_group_for_root(cut);
+      p--;
+      continue;
+    }
     // vectors run along R for row reductions and along B otherwise; they must not straddle a row
     {
       int64_t along = (B == 1) ? R : B;
@@ -887,7 +955,37 @@ void Planner::emit_reduce(const Op& op) {
     }
     if (last) {
       s.r_out_dtype = res->type.dtype;
-      s.r_out = materialise(res);
+      // Consumer groups of a small result run inside the reduce kernel, on each finished value (e.g. the scaling of a
+      // loss): no second launch, no round trip of the result through memory.
+      std::vector<const Value*> fused_roots;
+      bool res_needs_memory = true;
+      if (A * B <= 4096) res_needs_memory = collect_consumer_roots(op, res, &fused_roots);
+      while (!fused_roots.empty()) {
+        GroupBuilder pb;
+        pb.P = this;
+        pb.root_dims = res->type.dims;
+        pb.acc0_value = res;
+        try {
+          if (res_needs_memory) pb.add_output(res, materialise(res));
+          for (auto r : fused_roots) pb.computing.insert(r);
+          for (auto r : fused_roots) pb.add_output(r, materialise(r));
+          s.post = pb.finish(-1);
+          s.has_post = true;
+          break;
+        } catch (const GroupTooLarge&) {
+          fused_roots.clear();
+        }
+      }
+      if (s.has_post) {
+        for (auto r : fused_roots) emitted_groups_.insert(root_group_[r]);
+        s.label += "+epilogue(";
+        for (auto r : fused_roots) s.label += "%" + r->name + " ";
+        s.label += ")";
+        touch_vm(s.post);
+        if (res_needs_memory) s.r_out = layout_of(res).buf;
+      } else {
+        s.r_out = materialise(res);
+      }
       s.r_init_is_imm = init_imm;
       if (init_imm) s.r_init_imm = element_to_reg(init->def->const_data.data(), init->type.dtype);
       else { s.r_init_buf = layout_of(init).buf; s.r_init_dtype = init->type.dtype; }
@@ -983,6 +1081,34 @@ bool collapse(const std::vector<int64_t>& dims, const std::vector<int64_t>& stri
   return true;
 }
 
+// The elementwise consumer groups of a kernel result `res` that can run inside the producing kernel (as a GEMM epilogue
+// or on the finished values of a reduce): groups rooted at a value of the same shape whose other inputs all exist when
+// the kernel runs and that reach `res` with unchanged coordinates.  Returns whether `res` itself must still be stored.
+bool Planner::collect_consumer_roots(const Op& op, const Value* res, std::vector<const Value*>* fused_roots) {
+  bool res_needs_memory = false;
+  for (auto u : res->users) if (!is_fusible_kind(*u) && !(u->kind == OpKind::REDUCE && u->operands[0] == res)) res_needs_memory = true;
+  for (auto o : m_.outputs) if (o == res) res_needs_memory = true;
+  const int my_index = op_index_[&op];
+  for (int g : st(res).groups) {
+    const Value* r = group_root_[g];
+    bool ok = opt_.allow_epilogue_fusion && r != nullptr && r->type.dims == res->type.dims;
+    // every other input of the group must already exist when the kernel runs, and `res` must be reached with
+    // unchanged coordinates (not underneath a broadcast)
+    std::function<bool(const Value*, bool)> ready = [&](const Value* v, bool under_bcast) -> bool {
+      if (v == res) return !under_bcast;
+      if (v != r && load_as_leaf(v)) return (v->def == nullptr || op_index_[v->def] < my_index) && st(v).has_layout;
+      if (!v->def) return true;
+      bool ub = under_bcast || v->def->kind == OpKind::BROADCAST_IN_DIM;
+      for (auto o : v->def->operands) if (!ready(o, ub)) return false;
+      return true;
+    };
+    if (ok) ok = ready(r, false);
+    if (ok) fused_roots->push_back(r); else res_needs_memory = true;
+  }
+  std::sort(fused_roots->begin(), fused_roots->end(), [](const Value* a, const Value* b) { return a->id < b->id; });
+  return res_needs_memory;
+}
+
 void Planner::emit_dot(const Op& op) {
   const Value* lv = op.operands[0];
   const Value* rv = op.operands[1];
@@ -1067,45 +1193,31 @@ void Planner::emit_dot(const Op& op) {
   }
 
   // ---- epilogue: fold in the elementwise consumer groups of the accumulator where possible ----
-  bool res_needs_memory = false;
   std::vector<const Value*> fused_roots;
-  {
-    for (auto u : res->users) if (!is_fusible_kind(*u) && !(u->kind == OpKind::REDUCE && u->operands[0] == res)) res_needs_memory = true;
-    for (auto o : m_.outputs) if (o == res) res_needs_memory = true;
-    const int my_index = op_index_[&op];
-    for (int g : st(res).groups) {
-      const Value* r = group_root_[g];
-      bool ok = opt_.allow_epilogue_fusion && r != nullptr && r->type.dims == res->type.dims;
-      // every other input of the group must already exist when the GEMM runs, and `res` must be reached with
-      // unchanged coordinates (not underneath a broadcast)
-      std::function<bool(const Value*, bool)> ready = [&](const Value* v, bool under_bcast) -> bool {
-        if (v == res) return !under_bcast;
-        if (v != r && load_as_leaf(v)) return (v->def == nullptr || op_index_[v->def] < my_index) && st(v).has_layout;
-        if (!v->def) return true;
-        bool ub = under_bcast || v->def->kind == OpKind::BROADCAST_IN_DIM;
-        for (auto o : v->def->operands) if (!ready(o, ub)) return false;
-        return true;
-      };
-      if (ok) ok = ready(r, false);
-      if (ok) fused_roots.push_back(r); else res_needs_memory = true;
-    }
-    std::sort(fused_roots.begin(), fused_roots.end(), [](const Value* a, const Value* b) { return a->id < b->id; });
-  }
+  bool res_needs_memory = collect_consumer_roots(op, res, &fused_roots);
 
-  GroupBuilder gb;
-  gb.P = this;
-  gb.root_dims = res->type.dims;
-  gb.acc0_value = res;
-  if (res_needs_memory || fused_roots.empty()) {
-    BufRef out = materialise(res);
-    gb.add_output(res, out);
+  for (;;) {
+    GroupBuilder gb;
+    gb.P = this;
+    gb.root_dims = res->type.dims;
+    gb.acc0_value = res;
+    try {
+      if (res_needs_memory || fused_roots.empty()) {
+        BufRef out = materialise(res);
+        gb.add_output(res, out);
+      }
+      for (auto r : fused_roots) gb.computing.insert(r);
+      for (auto r : fused_roots) { BufRef out = materialise(r); gb.add_output(r, out); }
+      s.vm = gb.finish(-1);
+      break;
+    } catch (const GroupTooLarge&) {
+      // the consumer groups do not fit into one epilogue: store the plain result and let them run as kernels of their own
+      if (fused_roots.empty()) throw;
+      fused_roots.clear();
+      res_needs_memory = true;
+    }
   }
-  for (auto r : fused_roots) {
-    emitted_groups_.insert(root_group_[r]);
-    gb.computing.insert(r);
-  }
-  for (auto r : fused_roots) { BufRef out = materialise(r); gb.add_output(r, out); }
-  s.vm = gb.finish(-1);
+  for (auto r : fused_roots) emitted_groups_.insert(root_group_[r]);
   if (s.vm.vec != 8) s.g_tensor_core = false, s.g_split_f32 = false;
   // The accumulator arrives as F32 (or S32) registers; a bf16/f16 result type rounds when stored.
   s.bytes = (double)lv->type.byte_size() + (double)rv->type.byte_size();
@@ -1246,7 +1358,8 @@ static void step_bufs(const Step& s, std::vector<BufRef>* reads, std::vector<Buf
     case StepKind::ELEMENTWISE: vm_sets(s.vm); break;
     case StepKind::REDUCE:
       vm_sets(s.vm);
-      writes->push_back(s.r_out);
+      if (s.has_post) vm_sets(s.post);
+      if (s.r_out.valid()) writes->push_back(s.r_out);
       if (s.r_init_buf.valid()) reads->push_back(s.r_init_buf);
       if (s.scratch.valid()) writes->push_back(s.scratch);
       break;
@@ -1391,6 +1504,7 @@ void Planner::assign_arena() {
   auto fix = [&](BufRef& b) { if (b.kind == BufRef::TEMP) { b.offset = allocs_[b.index].offset; } };
   for (auto& s : plan_.steps) {
     for (auto& b : s.vm.bufs) fix(b);
+    for (auto& b : s.post.bufs) fix(b);
     fix(s.r_out); fix(s.r_init_buf); fix(s.scratch); fix(s.ga.buf); fix(s.gb.buf);
     fix(s.aq); fix(s.ak); fix(s.av); fix(s.ao); fix(s.c_src); fix(s.c_dst);
     for (auto& c : s.colls) { fix(c.src); fix(c.dst); }
@@ -1509,6 +1623,10 @@ std::string vm_str(const VmBinding& vm) {
 }  // namespace
 
 int reduce_splits(int64_t A, int64_t R, int64_t B) { return reduce_splits_impl(A, R, B); }
+int reduce_launches(int64_t A, int64_t R, int64_t B) {
+  if (A <= 0 || B <= 0) return 0;
+  return (reduce_splits_impl(A, R, B) > 1 && R > 0 && B != 1) ? 2 : 1;
+}
 
 std::string Plan::dump() const {
   std::ostringstream o;
@@ -1523,6 +1641,7 @@ std::string Plan::dump() const {
       case StepKind::REDUCE:
         o << "reduce " << s.label << " [A=" << s.rA << ",R=" << s.rR << ",B=" << s.rB << "] monoid=" << (int)s.monoid << " -> " << buf_str(s.r_out)
           << ":" << dtype_name(s.r_out_dtype) << "\n" << vm_str(s.vm);
+        if (s.has_post) o << "    on each result:\n" << vm_str(s.post);
         break;
       case StepKind::GEMM:
         o << "gemm " << s.label << " B=" << s.gB << " M=" << s.gM << " N=" << s.gN << " K=" << s.gK << (s.g_tensor_core ? " tcgen05" : " simt")

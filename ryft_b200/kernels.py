@@ -36,7 +36,7 @@ class VmProgram(C.Structure):
 class ReduceArgs(C.Structure):
     _fields_ = [("A", C.c_int64), ("R", C.c_int64), ("B", C.c_int64), ("monoid", C.c_uint8), ("cls", C.c_uint8), ("out_elem", C.c_uint8),
                 ("init_elem", C.c_uint8), ("init_imm", C.c_uint32), ("init_ptr", C.c_void_p), ("out", C.c_void_p), ("scratch", C.c_void_p),
-                ("vec", C.c_int)]
+                ("vec", C.c_int), ("host_post", C.c_void_p)]
 
 
 def load() -> C.CDLL:

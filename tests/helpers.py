@@ -69,3 +69,31 @@ def check_program(client, text: str, inputs: Sequence[np.ndarray], what: str = "
     for i, (g, w) in enumerate(zip(got, want)):
         assert_close(g, w, f"{what} output {i}", **tol)
     return got
+
+
+# ---- the literal metrics of the build's tolerances, recorded per configuration -----------------------------------------------
+_REPORT: dict = {}
+
+
+def record_metric(name: str, **metrics) -> None:
+    """Remembers the literal error metrics of a configuration (max-abs error / RMS of the expected output for 16-bit
+    floats, relative Frobenius error for f32) next to the bound that the test asserts; printed with `-s`, and written
+    as JSON to the file named by B2X_PARITY_REPORT when that variable is set."""
+    import json
+    import os
+    _REPORT[name] = {k: (float(v) if isinstance(v, (int, float, np.floating)) else v) for k, v in metrics.items()}
+    print(f"PARITY {name}: " + ", ".join(f"{k}={v:.3e}" if isinstance(v, float) else f"{k}={v}" for k, v in _REPORT[name].items()))
+    path = os.environ.get("B2X_PARITY_REPORT")
+    if path:
+        with open(path, "w") as f:
+            json.dump(_REPORT, f, indent=1, sort_keys=True)
+
+
+def literal_metrics(actual: np.ndarray, expected: np.ndarray) -> dict:
+    """Both literal metrics of the build's tolerances plus the relaxed 16-bit one that assert_close applies."""
+    a64, e64 = actual.astype(np.float64), expected.astype(np.float64)
+    rms = float(np.sqrt(np.mean(e64 ** 2))) if e64.size else 0.0
+    scale = np.maximum(np.abs(e64), rms)
+    relaxed = float((np.abs(a64 - e64) / np.where(scale > 0, scale, 1.0)).max()) if e64.size else 0.0
+    return {"max_abs_over_rms": ev.max_abs_over_rms(a64, e64), "rel_frobenius": ev.rel_frobenius(a64, e64), "max_err_over_max_rms_elem": relaxed,
+            "mismatch_fraction": float(np.mean(a64 != e64)) if e64.size else 0.0}

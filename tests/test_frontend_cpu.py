@@ -116,7 +116,8 @@ def test_causal_mask_is_folded_into_the_gemm_epilogue():
 def test_c4_plan_shape():
     dump = ryft_b200.plan_dump(configs.c4_program())
     assert dump.count("gemm ") == 5 and dump.count("tcgen05") == 5
-    assert "7 steps" in dump                       # 5 GEMMs + loss reduce + scalar scale
+    assert "6 steps" in dump                       # 5 GEMMs + the loss reduce, which scales its own result
+    assert "reduce reduce:%19+epilogue(%21 )" in dump and "load acc0; mul #" in dump
     # the forward GEMM stores H and gelu(H) in bf16 from one accumulator
     first = dump.split("[1]")[0]
     assert first.count("store") == 2 and ":bf16" in first and ":f32" not in first.split("vm:")[1].split("code:")[0]
@@ -130,14 +131,14 @@ def test_c5_collectives_are_split_hoisted_and_run_in_place():
     assert first_ar < last_gemm, "the first gradient all-reduce must start before the last GEMM is issued"
     # the divide by the replica count (a power of two) moved in front of the collective and into the GEMM epilogue:
     # no scaling pass remains, the collectives run in place on the output buffers and nothing in the plan waits for them
-    assert "elementwise fused:stablehlo.multiply:%60" not in dump and dump.count("elementwise ") == 1
+    assert "elementwise fused:stablehlo.multiply:%60" not in dump and dump.count("elementwise ") == 0   # (the loss scale runs inside the reduce)
     assert "out1 -> out1" in dump and "out0 -> out0" in dump and dump.count("detached") == 2
     assert "load acc0; mul #0x3e000000; store T0;" in dump       # accumulator * 1/8 straight into the output
 
 
 def test_scale_by_a_non_power_of_two_is_not_moved():
     dump = ryft_b200.plan_dump(configs.c4_program(256, 128, 384, replicas=3), num_replicas=3)
-    assert dump.count("elementwise ") == 3 and "(wait #" in dump   # loss scale + two gradient scaling passes behind the all-reduce
+    assert dump.count("elementwise ") == 2 and "(wait #" in dump   # two gradient scaling passes behind the all-reduce
 
 
 @pytest.mark.parametrize("body,needle", [
@@ -182,3 +183,57 @@ def test_builder_matches_reference_program_text():
     # crates/ryft-pjrt/src/programs.rs:2492-2498
     assert text == ("module {\n  func.func @main(%arg0: tensor<2x1xi32>, %arg1: tensor<2x1xi32>) -> tensor<2x1xi32> {\n"
                     "    %0 = stablehlo.add %arg0, %arg1 : tensor<2x1xi32>\n    return %0 : tensor<2x1xi32>\n  }\n}\n")
+
+
+def test_oversize_fusion_groups_are_cut_instead_of_rejected():
+    """A fusion group that exceeds the kernels' program limits (56 instructions, 8 tensors, 6 temporaries) is cut at an
+    interior value, which becomes a kernel of its own."""
+    b = Builder()
+    y = x = b.arg([1024, 1024], "f32")
+    for _ in range(60):
+        y = b.tanh(y)
+    dump = ryft_b200.plan_dump(b.build(y))
+    assert dump.count("elementwise fused:") == 2 and dump.count(" tanh;") == 60
+    b = Builder()
+    xs = [b.arg([1024, 1024], "f32") for _ in range(10)]
+    y = xs[0]
+    for v in xs[1:]:
+        y = b.add(y, v)
+    dump = ryft_b200.plan_dump(b.build(y))
+    assert dump.count("elementwise fused:") == 2 and dump.count(" add T") == 9
+    # the same chain as the prologue of a reduce, and as the epilogue of a GEMM
+    b = Builder()
+    y = x = b.arg([1024, 1024], "f32")
+    for _ in range(60):
+        y = b.tanh(y)
+    dump = ryft_b200.plan_dump(b.build(b.reduce(y, b.constant(0.0, [], "f32"), "add", [1])))
+    assert "reduce reduce:" in dump and dump.count(" tanh;") == 60
+    b = Builder()
+    lhs = b.arg([256, 128], "bf16"); rhs = b.arg([128, 256], "bf16")
+    y = b.dot_general(lhs, rhs, ([], []), ([1], [0]), out_dtype="f32")
+    for _ in range(60):
+        y = b.tanh(y)
+    dump = ryft_b200.plan_dump(b.build(y))
+    assert "gemm dot_general" in dump and dump.count(" tanh;") == 60
+
+
+def test_empty_reductions_plan_without_dividing_by_zero():
+    b = Builder()
+    x = b.arg([0, 8192], "f32")
+    dump = ryft_b200.plan_dump(b.build(b.reduce(x, b.constant(0.0, [], "f32"), "add", [1])))
+    assert "A=0,R=8192" in dump
+    import ctypes as C
+    lib = C.CDLL(str(ryft_b200.KERNELS_PATH))
+    lib.b2x_reduce_splits.argtypes = [C.c_int64] * 3
+    assert lib.b2x_reduce_splits(0, 8192, 1) == 1 and lib.b2x_reduce_splits(0, 1 << 20, 0) == 1
+
+
+def test_benchmark_programs_take_specialised_gemm_variants():
+    """The kernel variant each GEMM of the benchmark programs runs, as the launcher decides it (host only)."""
+    r4 = {r["label"].split("+")[0]: r for r in ryft_b200.plan_routes(configs.c4_program())}
+    assert len(r4) == 5 and all(r["bn"] == 256 and r["static_id"] and r["ctas"] == 148 for r in r4.values())
+    assert r4["dot_general:%0"]["transposed"] == 1 and r4["dot_general:%16"]["transposed"] == 0 and r4["dot_general:%16"]["stores"] == 2
+    (r2,) = ryft_b200.plan_routes(configs.c2_program())
+    assert (r2["bn"], r2["epi_groups"], r2["k_blocks"], r2["stores"]) == (256, 1, 2, 1) and r2["static_id"]
+    (r1,) = ryft_b200.plan_routes(configs.c1_program())
+    assert r1["K"] == 3 * 768 and r1["static_id"]

@@ -181,6 +181,39 @@ def test_poison_execution_fails_that_launch_only(client):
     assert ok[0].outputs[0].to_numpy().ravel().tolist() == [2, 2]
 
 
+def test_expired_device_wait_is_reported_once_as_deadline_exceeded(client):
+    """A wait inside a kernel that nothing satisfies must end by itself: with one mbarrier arrival withheld (a host-side
+    switch of the launcher; every other block of the kernel runs normally) the roles of that block give up after about
+    a second, the kernel returns, and the execution's completion event carries DEADLINE_EXCEEDED.  The device's status
+    word is cleared by that report: the next execution on the same device succeeds and is correct."""
+    import os
+    import time
+    from ryft_b200.stablehlo import Builder
+    b = Builder()
+    x = b.arg([256, 128], "bf16"); y = b.arg([128, 256], "bf16")
+    text = b.build(b.dot_general(x, y, ([], []), ([1], [0]), out_dtype="f32"))
+    exe = client.compile(pjrt.Program.mlir(text))
+    dev = exe.addressable_devices()[0]
+    import ml_dtypes
+    xs = np.ones((256, 128), np.float32).astype(ml_dtypes.bfloat16)
+    ys = np.ones((128, 256), np.float32).astype(ml_dtypes.bfloat16)
+    bufs = [client.buffer(xs, device=dev), client.buffer(ys, device=dev)]
+    os.environ["B2X_DEBUG_WITHHOLD_ARRIVE"] = "1"
+    try:
+        t0 = time.perf_counter()
+        outs = exe.execute([pjrt.ExecutionDeviceInputs(bufs)])
+    finally:
+        del os.environ["B2X_DEBUG_WITHHOLD_ARRIVE"]
+    with pytest.raises(pjrt.PjrtError) as e:
+        outs[0].done.await_()
+    waited = time.perf_counter() - t0
+    assert e.value.code_name == "DEADLINE_EXCEEDED" and "gave up waiting" in e.value.message
+    assert waited < 20.0, f"the kernel took {waited:.1f} s to give up"
+    ok = exe.execute([pjrt.ExecutionDeviceInputs(bufs)])
+    ok[0].done.await_()
+    assert np.array_equal(ok[0].outputs[0].to_numpy(), np.full((256, 256), 128.0, np.float32))
+
+
 def test_error_buffer_propagates(client):
     exe = client.compile(pjrt.Program.mlir(ADD_PROGRAM))
     a = client.buffer(np.ones((2, 1), np.int32))
