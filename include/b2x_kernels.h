@@ -106,6 +106,42 @@ typedef struct {
 } B2xAttentionArgs;
 B2X_API int b2x_launch_attention(const B2xAttentionArgs* host_args, int32_t* status, b2x_stream_t stream);
 
+/* Ops over 64-bit element types (i64, ui64, f64; linear_algebra.rs:671-701 and communication.rs:821-841 write the
+ * reference's worked examples with i64 tensors).  The fused-elementwise programs above keep values in 32-bit registers,
+ * so an op that reads or writes a 64-bit tensor runs as one launch of its own: every operand is addressed through
+ * per-dimension element strides (0 = broadcast), one thread per result element, arithmetic in int64 / uint64 / double.
+ * The store converts to `out_elem` with StableHLO's convert rules, so B2X_WIDE_COPY also serves convert,
+ * broadcast_in_dim and transpose. */
+#define B2X_WIDE_MAX_DIMS 6
+enum B2xWideOpKind {
+  B2X_WIDE_COPY = 0, B2X_WIDE_FILL, B2X_WIDE_IOTA, B2X_WIDE_COMPARE, B2X_WIDE_SELECT, B2X_WIDE_CLAMP,
+  B2X_WIDE_ADD, B2X_WIDE_SUB, B2X_WIDE_MUL, B2X_WIDE_DIV, B2X_WIDE_REM, B2X_WIDE_POW, B2X_WIDE_MAX, B2X_WIDE_MIN, B2X_WIDE_AND, B2X_WIDE_OR, B2X_WIDE_XOR,
+  B2X_WIDE_NEG, B2X_WIDE_ABS, B2X_WIDE_SIGN, B2X_WIDE_NOT, B2X_WIDE_TANH, B2X_WIDE_EXP, B2X_WIDE_LOG, B2X_WIDE_SQRT, B2X_WIDE_RSQRT, B2X_WIDE_LOGISTIC,
+  B2X_WIDE_FLOOR, B2X_WIDE_CEIL, B2X_WIDE_EXPM1, B2X_WIDE_LOG1P, B2X_WIDE_SIN, B2X_WIDE_COS
+};
+typedef struct {
+  int32_t op;                 /* B2xWideOpKind */
+  int32_t n_in;               /* operands: 0..3 */
+  int32_t n_dims;             /* result dims (row-major result) */
+  int32_t aux;                /* IOTA: the dimension; COMPARE: B2xCmp direction */
+  int32_t aux2;               /* COMPARE: 0 by operand type, 1 unsigned, 2 signed */
+  uint8_t out_elem;           /* B2xElem of the result */
+  uint8_t in_elem[3];
+  int64_t n_elements;
+  int64_t dim[B2X_WIDE_MAX_DIMS];
+  int64_t in_stride[3][B2X_WIDE_MAX_DIMS];   /* elements */
+  const void* in[3];
+  void* out;
+  uint64_t imm;               /* FILL: the value's bit pattern in the class of out_elem (int64 / uint64 / double) */
+} B2xWideOp;
+B2X_API int b2x_launch_wide_elementwise(const B2xWideOp* host_op, b2x_stream_t stream);
+/* stablehlo.reduce of the middle extent of a dense [A, R, B] tensor of a 64-bit type (functional.rs:188-219). */
+B2X_API int b2x_launch_wide_reduce(const void* in, uint8_t elem, int64_t A, int64_t R, int64_t B, int monoid, const void* init_ptr, uint64_t init_imm,
+                                   void* out, b2x_stream_t stream);
+/* stablehlo.dot_general over 64-bit operands as a strided batched GEMM (linear_algebra.rs:561-592); `out` is the dense
+ * row-major [batch, M, N] result of element type `out_elem`. */
+B2X_API int b2x_launch_wide_gemm(const B2xGemmArgs* host_args, uint8_t out_elem, void* out, b2x_stream_t stream);
+
 /* Number of kernels launched through this library since load (all entry points); used by bench reporting. */
 B2X_API int64_t b2x_kernel_launch_count(void);
 

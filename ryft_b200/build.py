@@ -23,7 +23,7 @@ INCLUDE = ROOT.parent / "include"
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 CXXFLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall,-Wno-unused-function"]
 
-KERNEL_SOURCES = ["kernels/elementwise.cu", "kernels/reduce.cu", "kernels/gemm_simt.cu", "kernels/gemm_tc.cu", "kernels/gemm_tc_static.cu", "kernels/attention.cu"]
+KERNEL_SOURCES = ["kernels/elementwise.cu", "kernels/reduce.cu", "kernels/gemm_simt.cu", "kernels/gemm_tc.cu", "kernels/gemm_tc_static.cu", "kernels/attention.cu", "kernels/wide.cu"]
 HOST_SOURCES = ["frontend/parser.cc", "frontend/verify.cc", "frontend/canonicalize.cc", "runtime/planner.cc", "runtime/proto.cc", "runtime/nccl_dyn.cc",
                 "runtime/executor.cc", "runtime/pjrt_plugin.cc", "runtime/debug_api.cc"]
 

@@ -9,18 +9,23 @@
 // longest causal prefix first.  The key blocks of a tile (128 keys each) are dealt alternately to two independent
 // softmax streams: stream s owns blocks j = s, s + 2, ..., its own score buffer, probability buffer, K/V stage and
 // output accumulator, and keeps its own running (max, sum).  While one stream exponentiates, the tensor pipe works
-// for the other; the two partial results are merged once, at the end.  352 threads:
+// for the other; the two partial results are merged once, at the end.  96 + 256 * TPR threads:
 //   warp 0      TMA producer: Q once, then K_j and V_j into stage j & 1 as soon as that stage's previous K (after its
 //               Q K^T retired) or V (after its P V retired) is free; each CTA loads its own tiles
-//   warps 1,10  MMA issuers, one per stream: S_s = Q K_j^T into TMEM score buffer s, O_s += P_s V_j into accumulator s
-//   warps 2-5   softmax stream 0, warps 6-9 stream 1; one query row per thread: the 128 scores of the row are read from
-//               TMEM once and stay in registers (row max, exp2, row sum), P goes as bf16 into 128-byte-swizzled
-//               shared memory for the second MMA; the accumulator is rescaled only when the running max grew by more
-//               than 2^8 (exact: the same stale max is used for the row sum)
+//   warps 1,2   MMA issuers, one per stream: S_s = Q K_j^T into TMEM score buffer s, O_s += P_s V_j into accumulator s
+//   warps 3..   softmax, 4 * TPR warps per stream.  TPR = 2 (the default): two threads share a query row, each owns 64
+//               of the block's 128 keys, so that four softmax warps per scheduler hide each other's latencies (with one
+//               thread per row there are two, and the exponential phase runs at a third of the special-function
+//               pipe's rate).  A thread reads all 128 scores of its row from TMEM for the row maximum (both threads of
+//               a row thus hold the same maximum without talking to each other) and keeps its own 64 in registers:
+//               exp2, partial row sum, P as bf16 into 128-byte-swizzled shared memory for the second MMA.  The
+//               accumulator is rescaled only when the running max grew by more than 2^8 (exact: the same stale max is
+//               used for the row sum); the partial sums of a row meet in the final merge.
 // Causal tiles above the diagonal are skipped; the diagonal block and ragged key tails are masked in registers.
 // Bound: tensor pipe / MUFU (exp2), about equal for D = 128; algorithmic FLOPs = 4 * BH * D * (unmasked scores).
 // Every wait is bounded; on expiry the CTA unwinds, frees TMEM and reports through `status`.
 #include <atomic>
+#include <cstdlib>
 #include "../../../include/b2x_kernels.h"
 #include "common.cuh"
 #include "sm100.cuh"
@@ -41,11 +46,13 @@ struct AttnParams {
 constexpr int AT_M = 128;   // query rows per CTA
 constexpr int AT_N = 128;   // keys per block
 
-template <int D>
+// PT: the probabilities go to the second MMA through TMEM (as its A operand) instead of shared memory; the P buffers
+// then shrink to the 2 KB per stream that the final merge needs.
+template <int D, bool PT>
 struct AttnSmem {
   static constexpr int Q_BYTES = AT_M * D * 2;
   static constexpr int KV_BYTES = AT_N * D * 2;
-  static constexpr int P_BYTES = AT_M * AT_N * 2;
+  static constexpr int P_BYTES = PT ? 2048 : AT_M * AT_N * 2;
   static constexpr int Q_OFF = 0;
   static constexpr int K_OFF = Q_OFF + Q_BYTES;            // 2 stages (one per stream)
   static constexpr int V_OFF = K_OFF + 2 * KV_BYTES;       // 2 stages
@@ -85,12 +92,12 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
   return r;
 }
-template <int D>
-__global__ void __launch_bounds__(352, 1)
+template <int D, int TPR, bool PT>
+__global__ void __launch_bounds__(96 + 256 * TPR, 1)
 k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
             const __grid_constant__ AttnParams p, int32_t* status) {
   using namespace sm100;
-  using SM = AttnSmem<D>;
+  using SM = AttnSmem<D, PT>;
   constexpr int DC = D / 64;                 // 64-wide (128-byte) chunks of the head dimension
   constexpr uint32_t TMEM_COLS = 512;        // S0 [0,128), S1 [128,256), O0 [256, 256 + D), O1 [256 + D, 256 + 2 D)
   constexpr uint32_t CHUNK_BYTES = 128 * 128;  // one [128 rows x 128 bytes] swizzled sub-tile
@@ -106,9 +113,9 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                  bar_pf = b0 + 104, bar_pv = b0 + 120, bar_merge = b0 + 136, bar_drain = b0 + 144;   // drain[2]
   uint32_t* tmem_slot = (uint32_t*)(bars + 20);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-  // per stream and row (max * scale_log2, sum) for the final merge; stream s keeps them at the start of its own
-  // probability buffer, which is idle once its last P V product has retired
-  auto merge_slot = [&](int s, int row) -> float2* { return (float2*)(smem + SM::P_OFF + s * SM::P_BYTES) + row; };
+  // per stream, row half and row (max * scale_log2, partial sum) for the final merge; stream s keeps them at the start of
+  // its own probability buffer, which is idle once its last P V product has retired
+  auto merge_slot = [&](int s, int half, int row) -> float2* { return (float2*)(smem + SM::P_OFF + s * SM::P_BYTES) + half * AT_M + row; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // consecutive CTAs are the query tiles of one (batch, head), longest causal prefix first: they run together and find
@@ -124,9 +131,9 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     mbar_init(bar_q, 1);
     for (int s = 0; s < 2; s++) {
       mbar_init(bar_kf + 8 * s, 1); mbar_init(bar_ke + 8 * s, 1); mbar_init(bar_vf + 8 * s, 1); mbar_init(bar_ve + 8 * s, 1);
-      mbar_init(bar_sf + 8 * s, 1); mbar_init(bar_se + 8 * s, 4); mbar_init(bar_pf + 8 * s, 4); mbar_init(bar_pv + 8 * s, 1);
+      mbar_init(bar_sf + 8 * s, 1); mbar_init(bar_se + 8 * s, 4 * TPR); mbar_init(bar_pf + 8 * s, 4 * TPR); mbar_init(bar_pv + 8 * s, 1);
     }
-    mbar_init(bar_merge, 8); mbar_init(bar_drain, 1); mbar_init(bar_drain + 8, 1);
+    mbar_init(bar_merge, 8 * TPR); mbar_init(bar_drain, 1); mbar_init(bar_drain + 8, 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
@@ -180,12 +187,12 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
           }
       }
     }
-  } else if (warp == 1 || warp == 10) {
+  } else if (warp == 1 || warp == 2) {
     // ---------------------------------------------- MMA issuers -----------------------------------------------------
     // One issuing thread per stream, so that a stream whose probabilities are late never holds up the other stream's
     // next score block.  The two threads touch disjoint TMEM columns and shared-memory buffers (Q is only read).
     if (lane == 0) {
-      const int s = warp == 1 ? 0 : 1;
+      const int s = warp - 1;
       const int n_mine = nblk > s ? (nblk - s + 1) / 2 : 0;
       bool ok = mbar_wait(bar_q, 0, abort_flag, status, 12);
       auto issue_qk = [&](int it) -> bool {
@@ -203,25 +210,42 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       };
       if (ok && n_mine > 0) ok = issue_qk(0);
       for (int it = 0; it < n_mine && ok; it++) {
-        // the stream has copied this block's scores into registers: its score buffer can take its next block
-        if (it + 1 < n_mine) {
-          if (!mbar_wait(bar_se + 8 * s, (uint32_t)(it & 1), abort_flag, status, 14)) { ok = false; break; }
-          if (!issue_qk(it + 1)) { ok = false; break; }
+        if constexpr (!PT) {
+          // the stream has copied this block's scores into registers: its score buffer can take its next block
+          if (it + 1 < n_mine) {
+            if (!mbar_wait(bar_se + 8 * s, (uint32_t)(it & 1), abort_flag, status, 14)) { ok = false; break; }
+            if (!issue_qk(it + 1)) { ok = false; break; }
+          }
         }
         if (!mbar_wait(bar_vf + 8 * s, (uint32_t)(it & 1), abort_flag, status, 15)) { ok = false; break; }
         if (!mbar_wait(bar_pf + 8 * s, (uint32_t)(it & 1), abort_flag, status, 16)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t pa = sbase + SM::P_OFF + s * SM::P_BYTES, va = sbase + SM::V_OFF + s * SM::KV_BYTES;
+        const uint32_t va = sbase + SM::V_OFF + s * SM::KV_BYTES;
         const uint32_t o_tmem = tmem_base + 256u + (uint32_t)(s * D);
+        if constexpr (PT) {
+          // A = P from TMEM: row = lane, 16 keys of a k-step = 8 columns (two bf16 per column) at the start of the stream's
+          // score buffer; B = V (MN-major: head-dim chunks of 64 are CHUNK_BYTES apart, 8 key rows per 1 KiB)
+          const uint32_t p_tmem = tmem_base + (uint32_t)(s * 128);
 #pragma unroll
-        for (int k = 0; k < AT_N / 16; k++) {
-          // A = P (K-major: keys contiguous); B = V (MN-major: head-dim chunks of 64 are CHUNK_BYTES apart, 8 key rows per 1 KiB)
-          const uint32_t aoff = (uint32_t)(k >> 2) * CHUNK_BYTES + (uint32_t)(k & 3) * 32;
-          umma_ss<false>(o_tmem, make_smem_desc(pa + aoff, 16, 1024), make_smem_desc(va + (uint32_t)k * 2048, CHUNK_BYTES, 1024), p.idesc_pv,
-                         (it > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < AT_N / 16; k++)
+            umma_ts_f16(o_tmem, p_tmem + (uint32_t)(k * 8), make_smem_desc(va + (uint32_t)k * 2048, CHUNK_BYTES, 1024), p.idesc_pv, (it > 0 || k > 0) ? 1u : 0u);
+        } else {
+          const uint32_t pa = sbase + SM::P_OFF + s * SM::P_BYTES;
+#pragma unroll
+          for (int k = 0; k < AT_N / 16; k++) {
+            // A = P (K-major: keys contiguous); B = V (MN-major: head-dim chunks of 64 are CHUNK_BYTES apart, 8 key rows per 1 KiB)
+            const uint32_t aoff = (uint32_t)(k >> 2) * CHUNK_BYTES + (uint32_t)(k & 3) * 32;
+            umma_ss<false>(o_tmem, make_smem_desc(pa + aoff, 16, 1024), make_smem_desc(va + (uint32_t)k * 2048, CHUNK_BYTES, 1024), p.idesc_pv,
+                           (it > 0 || k > 0) ? 1u : 0u);
+          }
         }
         tc_commit(bar_ve + 8 * s);    // V stage free
         tc_commit(bar_pv + 8 * s);    // the stream's accumulator and probability buffer may be touched again
+        if constexpr (PT) {
+          // the probabilities sit in the score buffer: the next score block may overwrite it only after the product above
+          // has read them, which the tensor pipe guarantees by executing this thread's MMAs in issue order
+          if (it + 1 < n_mine && !issue_qk(it + 1)) { ok = false; break; }
+        }
       }
       // everything this thread issued must retire before TMEM is released
       tc_commit(bar_drain + 8 * s);
@@ -229,8 +253,12 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     }
   } else {
     // ---------------------------------------------- softmax ---------------------------------------------------------
-    const int s = (warp - 2) >> 2;                // stream
-    const int quad = warp & 3;
+    constexpr int WPS = 4 * TPR;                  // softmax warps per stream
+    constexpr int KW = AT_N / TPR;                // keys of a block that this thread exponentiates
+    constexpr int KC = KW / 32;                   // ... in chunks of 32
+    const int s = (warp - 3) / WPS;               // stream
+    const int half = ((warp - 3) % WPS) >> 2;     // which part of the row's keys
+    const int quad = warp & 3;                    // TMEM lanes [32 * quad, 32 * quad + 32): fixed by the warp's number
     const int row = quad * 32 + lane;             // row of the tile == TMEM lane
     const int64_t qrow = (int64_t)q0 + row;
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
@@ -244,28 +272,50 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       const int j = 2 * it + s;
       if (!mbar_wait(bar_sf + 8 * s, (uint32_t)(it & 1), abort_flag, status, 17)) { ok = false; break; }
       tc_fence_after();
-      uint32_t r[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; c++) tmem_ld_32x32(s_addr + (uint32_t)(c * 32), r[c]);
-      tc_wait_ld();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_se + 8 * s);
       // columns of this block that this row may attend to: [0, lim]
       int64_t lim = p.Sk - 1 - (int64_t)j * AT_N;
       if (p.causal) { const int64_t c = qrow - (int64_t)j * AT_N; lim = c < lim ? c : lim; }
       const bool need_mask = __any_sync(0xffffffffu, lim < AT_N - 1);
+      uint32_t r[KC][32];
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if constexpr (TPR == 2) {
+        // the other part of the row: only its maximum is needed (one chunk at a time: its 32 registers are free again
+        // before this thread's own scores are loaded)
+#pragma unroll 1
+        for (int c = 0; c < KC; c++) {
+          const int col0 = (half ^ 1) * KW + c * 32;
+          uint32_t t[32];
+          tmem_ld_32x32(s_addr + (uint32_t)col0, t);
+          tc_wait_ld();
+          if (need_mask) {
+#pragma unroll
+            for (int i = 0; i < 32; i++) if (col0 + i > lim) t[i] = 0xff800000u;
+          }
+#pragma unroll
+          for (int i = 0; i < 16; i++) mx4[i & 3] = max3(mx4[i & 3], __uint_as_float(t[2 * i]), __uint_as_float(t[2 * i + 1]));
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < KC; c++) tmem_ld_32x32(s_addr + (uint32_t)(half * KW + c * 32), r[c]);
+      tc_wait_ld();
+      if constexpr (!PT) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_se + 8 * s);
+      } else if constexpr (TPR == 2) {
+        // both threads of a row have read the scores before either overwrites part of them with probabilities
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + s * 4 + quad) : "memory");
+      }
       if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < 4; c++)
+        for (int c = 0; c < KC; c++)
 #pragma unroll
-          for (int i = 0; i < 32; i++) if (c * 32 + i > lim) r[c][i] = 0xff800000u;
+          for (int i = 0; i < 32; i++) if (half * KW + c * 32 + i > lim) r[c][i] = 0xff800000u;
       }
       float mx;
       {
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 0; c < 4; c++)
+        for (int c = 0; c < KC; c++)
 #pragma unroll
           for (int i = 0; i < 16; i++) mx4[i & 3] = max3(mx4[i & 3], __uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1]));
         mx = max3(mx4[0], mx4[1], max3(mx4[2], mx4[3], -INFINITY));
@@ -282,18 +332,16 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         if (!mbar_wait(bar_pv + 8 * s, (uint32_t)((it - 1) & 1), abort_flag, status, 18)) { ok = false; break; }
         tc_fence_after();
         if (__any_sync(0xffffffffu, rescale)) {
+          // each thread of a row rescales its share of the accumulator's columns (both took the same decision)
 #pragma unroll 1
-          for (int c = 0; c < D / 32; c++) {
-            uint32_t o[32];
-            tmem_ld_32x32(o_addr + (uint32_t)(c * 32), o);
+          for (int c = half * (D / 16 / TPR); c < (half + 1) * (D / 16 / TPR); c++) {
+            // 16 columns at a time: the block's scores stay in registers meanwhile
+            uint32_t o[16];
+            tmem_ld_32x16(o_addr + (uint32_t)(c * 16), o);
             tc_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            uint32_t lo[16], hi[16];
-#pragma unroll
-            for (int i = 0; i < 16; i++) { lo[i] = o[i]; hi[i] = o[16 + i]; }
-            tmem_st_32x16(o_addr + (uint32_t)(c * 32), lo);
-            tmem_st_32x16(o_addr + (uint32_t)(c * 32 + 16), hi);
+            for (int i = 0; i < 16; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x16(o_addr + (uint32_t)(c * 16), o);
           }
           tc_wait_st();
         }
@@ -305,7 +353,8 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       const uint64_t sc2 = pack2(sc_bits, sc_bits), mn2 = pack2(mn_bits, mn_bits);
       uint64_t ps2[2] = {0ull, 0ull};
 #pragma unroll
-      for (int c = 0; c < 4; c++) {
+      for (int c = 0; c < KC; c++) {
+        uint32_t pw[16];                                  // 32 keys as bf16 pairs
         // 32 keys = 64 bytes = four 16-byte pieces of this row; piece index within the 128-byte line is XOR-swizzled
 #pragma unroll
         for (int q = 0; q < 4; q++) {
@@ -321,33 +370,46 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             __nv_bfloat162 t = __floats2bfloat162_rn(e0, e1);
             w[h] = *reinterpret_cast<uint32_t*>(&t);
           }
-          const int piece = c * 4 + q;                 // 0..15 over the 128 keys
-          const int sub = piece >> 3, in = piece & 7;
-          sts_v4(prow_s + (uint32_t)(sub * CHUNK_BYTES + ((in ^ (row & 7)) << 4)), w[0], w[1], w[2], w[3]);
+          if constexpr (PT) {
+#pragma unroll
+            for (int h = 0; h < 4; h++) pw[q * 4 + h] = w[h];
+          } else {
+            const int piece = (half * KW) / 8 + c * 4 + q;   // 0..15 over the 128 keys
+            const int sub = piece >> 3, in = piece & 7;
+            sts_v4(prow_s + (uint32_t)(sub * CHUNK_BYTES + ((in ^ (row & 7)) << 4)), w[0], w[1], w[2], w[3]);
+          }
         }
+        // key k of the block lives in column k / 2 of the stream's score buffer (low half of the word: the even key)
+        if constexpr (PT) tmem_st_32x16(s_addr + (uint32_t)((half * KW) / 2 + c * 16), pw);
       }
       {
         uint32_t a0, a1, b0, b1;
         unpack2(ps2[0], a0, a1); unpack2(ps2[1], b0, b1);
         l += (__uint_as_float(a0) + __uint_as_float(a1)) + (__uint_as_float(b0) + __uint_as_float(b1));
       }
-      // P visible to the tensor-core (async) proxy
-      tc_fence_before();
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      if constexpr (PT) {
+        tc_wait_st();
+        tc_fence_before();
+      } else {
+        // P visible to the tensor-core (async) proxy
+        tc_fence_before();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pf + 8 * s);
     }
     // ---- merge the two streams and write O / l as bf16 ----
     if (ok && n_mine > 0) ok = mbar_wait(bar_pv + 8 * s, (uint32_t)((n_mine - 1) & 1), abort_flag, status, 19);
     if (poisoned) l = __int_as_float(0x7fc00000);
-    *merge_slot(s, row) = make_float2((n_mine > 0 && m_used != -INFINITY) ? m_used * p.scale_log2 : -INFINITY, n_mine > 0 ? l : 0.f);
+    *merge_slot(s, half, row) = make_float2((n_mine > 0 && m_used != -INFINITY) ? m_used * p.scale_log2 : -INFINITY, n_mine > 0 ? l : 0.f);
     tc_fence_before();
     __syncwarp();
     if (lane == 0) mbar_arrive(bar_merge);
     if (ok) ok = mbar_wait(bar_merge, 0, abort_flag, status, 20);
     if (ok) {
       tc_fence_after();
-      const float2 mine = *merge_slot(s, row), other = *merge_slot(s ^ 1, row);
+      float2 mine = *merge_slot(s, 0, row), other = *merge_slot(s ^ 1, 0, row);
+      if constexpr (TPR == 2) { mine.y += merge_slot(s, 1, row)->y; other.y += merge_slot(s ^ 1, 1, row)->y; }
       const float mm = fmaxf(mine.x, other.x);
       const float a_mine = (mine.x == -INFINITY) ? 0.f : fast_exp2(mine.x - mm);
       const float a_other = (other.x == -INFINITY) ? 0.f : fast_exp2(other.x - mm);
@@ -357,16 +419,20 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       const bool have_mine = n_mine > 0, have_other = (nblk > (s ^ 1));
       const uint32_t o_mine = o_addr, o_other = tmem_base + lane_addr + 256u + (uint32_t)((s ^ 1) * D);
       __nv_bfloat16* orow = p.out + ((int64_t)bh * p.Sq + qrow) * D;
-      // stream s writes head-dim columns [s * D/2, (s + 1) * D/2)
+      // the 2 * TPR threads of a row share the head dimension: thread (s, half) writes columns [g * W, (g + 1) * W) with
+      // g = s * TPR + half and W = D / (2 * TPR)
+      constexpr int W = D / (2 * TPR);
+      const int g = s * TPR + half;
+      // 16 columns at a time: the merge is a cold path and must not set the kernel's register count
 #pragma unroll 1
-      for (int c = s * (D / 64); c < (s + 1) * (D / 64); c++) {
-        uint32_t x[32], y[32];
-        if (have_mine) tmem_ld_32x32(o_mine + (uint32_t)(c * 32), x);
-        if (have_other) tmem_ld_32x32(o_other + (uint32_t)(c * 32), y);
+      for (int c = g * (W / 16); c < (g + 1) * (W / 16); c++) {
+        uint32_t x[16], y[16];
+        if (have_mine) tmem_ld_32x16(o_mine + (uint32_t)(c * 16), x);
+        if (have_other) tmem_ld_32x16(o_other + (uint32_t)(c * 16), y);
         tc_wait_ld();
-        float f[32];
+        float f[16];
 #pragma unroll
-        for (int i = 0; i < 32; i++) {
+        for (int i = 0; i < 16; i++) {
           float v = 0.f;
           if (have_mine) v = __uint_as_float(x[i]) * w_mine;
           if (have_other) v = fmaf(__uint_as_float(y[i]), w_other, v);
@@ -374,14 +440,14 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         }
         if (qrow < p.Sq) {
 #pragma unroll
-          for (int q = 0; q < 4; q++) {
+          for (int q = 0; q < 2; q++) {
             uint32_t w[4];
 #pragma unroll
             for (int h = 0; h < 4; h++) {
               __nv_bfloat162 t = __floats2bfloat162_rn(f[q * 8 + 2 * h], f[q * 8 + 2 * h + 1]);
               w[h] = *reinterpret_cast<uint32_t*>(&t);
             }
-            *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4*>(orow + c * 16 + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
       }
@@ -393,9 +459,9 @@ k_attention(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
 }
 
-template <int D>
+template <int D, int TPR, bool PT>
 static int launch_attention(const B2xAttentionArgs* a, int32_t* status, cudaStream_t stream) {
-  using SM = AttnSmem<D>;
+  using SM = AttnSmem<D, PT>;
   CUtensorMap tmQ, tmK, tmV;
   const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   if (!encode_3d(&tmQ, dt, 2, a->q, D, (uint64_t)a->Sq, (uint64_t)a->BH, D, (uint64_t)a->Sq * D, 64, AT_M)) return (int)cudaErrorInvalidValue;
@@ -409,7 +475,7 @@ static int launch_attention(const B2xAttentionArgs* a, int32_t* status, cudaStre
   p.out = (__nv_bfloat16*)a->o;
   p.idesc_qk = sm100::make_idesc(1u, false, false, AT_M, AT_N);
   p.idesc_pv = sm100::make_idesc(1u, false, true, AT_M, D);
-  auto kern = k_attention<D>;
+  auto kern = k_attention<D, TPR, PT>;
   {
     int dev = 0;
     cudaGetDevice(&dev);
@@ -423,7 +489,7 @@ static int launch_attention(const B2xAttentionArgs* a, int32_t* status, cudaStre
   const int64_t grid = (int64_t)p.n_q_tiles * a->BH;
   if (grid <= 0) return 0;
   if (grid > 0x7fffffff) return (int)cudaErrorInvalidValue;
-  kern<<<(unsigned)grid, 352, SM::TOTAL, stream>>>(tmQ, tmK, tmV, p, status);
+  kern<<<(unsigned)grid, 96 + 256 * TPR, SM::TOTAL, stream>>>(tmQ, tmK, tmV, p, status);
   count_launch();
   return (int)cudaGetLastError();
 }
@@ -435,7 +501,20 @@ extern "C" int b2x_launch_attention(const B2xAttentionArgs* a, int32_t* status, 
   cudaStream_t stream = (cudaStream_t)stream_;
   if (a->BH <= 0 || a->Sq <= 0 || a->Sk <= 0) return (int)cudaErrorInvalidValue;
   if (((uintptr_t)a->q & 15) || ((uintptr_t)a->k & 15) || ((uintptr_t)a->v & 15) || ((uintptr_t)a->o & 15)) return (int)cudaErrorInvalidValue;
-  if (a->D == 128) return launch_attention<128>(a, status, stream);
-  if (a->D == 64) return launch_attention<64>(a, status, stream);
+  // Variants kept for comparison, both measured slower on the 4096 x 128 causal case (0.85 ms and 0.72 ms against 0.68 ms):
+  // B2X_ATTENTION_P=tmem (probabilities through TMEM as the second MMA's A operand: frees the P buffers, but a stream's next
+  // score block must then wait for its P V product), B2X_ATTENTION_THREADS_PER_ROW=2 (two threads share a query row)
+  const char* tpr = getenv("B2X_ATTENTION_THREADS_PER_ROW");
+  const char* pv = getenv("B2X_ATTENTION_P");
+  const bool two = tpr && tpr[0] == '2';
+  const bool via_smem = !(pv && pv[0] == 't');
+  if (a->D == 128) {
+    if (via_smem) return two ? launch_attention<128, 2, false>(a, status, stream) : launch_attention<128, 1, false>(a, status, stream);
+    return two ? launch_attention<128, 2, true>(a, status, stream) : launch_attention<128, 1, true>(a, status, stream);
+  }
+  if (a->D == 64) {
+    if (via_smem) return two ? launch_attention<64, 2, false>(a, status, stream) : launch_attention<64, 1, false>(a, status, stream);
+    return two ? launch_attention<64, 2, true>(a, status, stream) : launch_attention<64, 1, true>(a, status, stream);
+  }
   return (int)cudaErrorInvalidValue;
 }

@@ -108,6 +108,10 @@ __global__ void __launch_bounds__(256, ID != 0 ? 4 : 1) k_reduce_rows(const __gr
   const uint32_t ident = red_identity(K.monoid, K.cls);
   // the program's dims are [A, R] (or one merged dim): the coordinates of a vector are (a, r) without a division
   const bool rows2 = P.n_dims == 2 && P.dim[1] == K.R;
+  // rows of K.R elements addressed through the row-wise driver (usable when R fits its 32-bit column index)
+  const bool row_driver = ID != 0 && V == 8 && K.R > 0 && K.R < (1ll << 28);
+  VmRowPlan rplan;
+  if (row_driver) rplan = vm_row_plan(P, (uint32_t)K.R); else rplan.fast = false;
   for (int64_t piece0 = (int64_t)blockIdx.x * PIECES_PER_CTA; piece0 < n_pieces; piece0 += (int64_t)gridDim.x * PIECES_PER_CTA) {
     const int64_t piece = piece0 + threadIdx.x / T;
     uint32_t total = ident;
@@ -120,21 +124,53 @@ __global__ void __launch_bounds__(256, ID != 0 ? 4 : 1) k_reduce_rows(const __gr
       const int64_t STEP = BLOCK * K.S;
       const int64_t r1 = K.R;
       int64_t r = s * BLOCK + (int64_t)lane_in_piece * V;
-      if constexpr (ID != 0) {
-        // specialised programs are short: four vectors per trip, so that all four vectors' loads are in flight together
-        // (the kernel is bound by memory latency, not by issue slots)
-        uint32_t tot[4] = {ident, ident, ident, ident};
-        for (; r + 3 * STEP < r1; r += 4 * STEP) {
-          uint32_t acc[4][V];
+      if constexpr (ID != 0 && V == 8) {
+        // Specialised programs are short, so the address arithmetic decides the instruction count: the row's operand
+        // addresses are set up once (vm_row_begin) and a vector then costs one 32-bit multiply-add per tensor.  Four
+        // vectors per trip keep all their loads in flight together.
+        VmRow vrow;
+        vrow.vec = false;
+        if (row_driver && rplan.affine) vm_row_begin(P, rplan, (uint64_t)a, (uint32_t)K.R, vrow);
+        if (vrow.vec && vm_row_all_contiguous(P, vrow)) {
+          // every operand is contiguous along the row: branch-free fetches, all four vectors' loads in flight at once
+          uint32_t tot[4] = {ident, ident, ident, ident};
+          for (; r + 3 * STEP < r1; r += 4 * STEP) {
+            uint32_t acc[4][V];
 #pragma unroll
-          for (int u = 0; u < 4; u++) vm_run_at<V, ID>(P, (uint64_t)(a * K.R + r + u * STEP), rows2, a, r + u * STEP, zero, acc[u]);
+            for (int u = 0; u < 4; u++) vm_run_row_contig<V, ID>(P, vrow, (uint32_t)(r + u * STEP), zero, acc[u]);
 #pragma unroll
-          for (int j = 0; j < V; j++) {
+            for (int j = 0; j < V; j++) {
 #pragma unroll
-            for (int u = 0; u < 4; u++) tot[u] = red_combine_t<MC>(tot[u], acc[u][j], K.monoid, K.cls);
+              for (int u = 0; u < 4; u++) tot[u] = red_combine_t<MC>(tot[u], acc[u][j], K.monoid, K.cls);
+            }
+          }
+          total = red_combine_t<MC>(red_combine_t<MC>(tot[0], tot[1], K.monoid, K.cls), red_combine_t<MC>(tot[2], tot[3], K.monoid, K.cls), K.monoid, K.cls);
+          for (; r < r1; r += STEP) {
+            uint32_t acc[V];
+            vm_run_row_contig<V, ID>(P, vrow, (uint32_t)r, zero, acc);
+#pragma unroll
+            for (int j = 0; j < V; j++) total = red_combine_t<MC>(total, acc[j], K.monoid, K.cls);
+          }
+        } else if (vrow.vec) {
+          uint32_t tot[4] = {ident, ident, ident, ident};
+          for (; r + 3 * STEP < r1; r += 4 * STEP) {
+            uint32_t acc[4][V];
+#pragma unroll
+            for (int u = 0; u < 4; u++) vm_run_row_vec<V, ID>(P, vrow, (uint32_t)(r + u * STEP), zero, acc[u]);
+#pragma unroll
+            for (int j = 0; j < V; j++) {
+#pragma unroll
+              for (int u = 0; u < 4; u++) tot[u] = red_combine_t<MC>(tot[u], acc[u][j], K.monoid, K.cls);
+            }
+          }
+          total = red_combine_t<MC>(red_combine_t<MC>(tot[0], tot[1], K.monoid, K.cls), red_combine_t<MC>(tot[2], tot[3], K.monoid, K.cls), K.monoid, K.cls);
+          for (; r < r1; r += STEP) {
+            uint32_t acc[V];
+            vm_run_row_vec<V, ID>(P, vrow, (uint32_t)r, zero, acc);
+#pragma unroll
+            for (int j = 0; j < V; j++) total = red_combine_t<MC>(total, acc[j], K.monoid, K.cls);
           }
         }
-        total = red_combine_t<MC>(red_combine_t<MC>(tot[0], tot[1], K.monoid, K.cls), red_combine_t<MC>(tot[2], tot[3], K.monoid, K.cls), K.monoid, K.cls);
       }
       for (; r < r1; r += STEP) {
         uint32_t acc[V];

@@ -301,6 +301,41 @@ __device__ __forceinline__ float vm_tanh_fast(float x) {
   return y;
 }
 
+// Fast tanh of a whole vector (used where the planner allows the hardware approximation: a 16-bit float value that is
+// only returned).  tanh.approx goes through the 16-lane special-function pipe, which a GEMM epilogue that applies tanh
+// to every element saturates long before memory does.  When every element of the vector has |x| <= 1 (pre-activations
+// usually do) an odd polynomial on the FMA pipes, two elements per instruction, replaces it: x * P(x^2) with P of degree
+// 4 fitted to tanh(x) / x on [0, 1], relative error below 2^-16 (tanh.approx: 2^-11).  Anything else, NaN included,
+// takes tanh.approx.
+template <int V>
+__device__ __forceinline__ void vm_tanh_fast_vec(uint32_t (&a)[V]) {
+  if constexpr (V % 2 == 0) {
+    float m = 0.f;
+#pragma unroll
+    for (int j = 0; j < V; j++) asm("max.NaN.f32 %0, %0, %1;" : "+f"(m) : "f"(fabsf(u2f(a[j]))));   // a NaN element makes m NaN
+    if (m <= 1.0f) {
+      auto splat = [](float v) { uint64_t r; asm("mov.b64 %0, {%1, %1};" : "=l"(r) : "r"(__float_as_uint(v))); return r; };
+      const uint64_t c4 = splat(0.009248304937f), c3 = splat(-0.04529244860f), c2 = splat(0.1307216824f), c1 = splat(-0.3330772912f),
+                     one = splat(1.0f);
+#pragma unroll
+      for (int j = 0; j < V; j += 2) {
+        uint64_t x, t, p;
+        asm("mov.b64 %0, {%1, %2};" : "=l"(x) : "r"(a[j]), "r"(a[j + 1]));
+        asm("mul.rn.f32x2 %0, %1, %1;" : "=l"(t) : "l"(x));
+        asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(p) : "l"(t), "l"(c4), "l"(c3));
+        asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(p) : "l"(p), "l"(t), "l"(c2));
+        asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(p) : "l"(p), "l"(t), "l"(c1));
+        asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(p) : "l"(p), "l"(t), "l"(one));
+        asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(p) : "l"(x), "l"(p));
+        asm("mov.b64 {%0, %1}, %2;" : "=r"(a[j]), "=r"(a[j + 1]) : "l"(p));
+      }
+      return;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < V; j++) a[j] = f2u(vm_tanh_fast(u2f(a[j])));
+}
+
 // tanh to within about 2 ulp without divergent branches: odd polynomial for |x| < 0.3, 1 - 2 / (1 + e^{2|x|}) above
 // (ex2.approx and rcp.approx are each within 2^-22 relative, the result is >= 0.29 there so the absolute error of the
 // quotient stays below one ulp of the result).
@@ -439,7 +474,7 @@ __device__ __forceinline__ int64_t vm_offset(const B2xVmTensor& T, const int64_t
 // constants (specialised programs) the switches below fold away and only the selected op's code remains.
 // `off[t]` is tensor t's element offset for this vector without the part contributed by `col` along the innermost dim
 // (callers that have no separate column pass col = 0 and fold everything into off).
-template <int V, bool RF = false, bool STG = false>
+template <int V, bool RF = false, bool STG = false, bool AC = false>
 __device__ __forceinline__ void vm_exec(const B2xVmProgram& P, const int64_t (&coord)[B2X_VM_MAX_DIMS], const int nd,
                                         const int64_t (&off)[B2X_VM_MAX_TENSORS], const VmRowAddr& RA, const int64_t col, const uint8_t op,
                                         const uint8_t src_kind, const uint8_t src_idx, const uint8_t aux, const uint8_t tc, const uint8_t rnd,
@@ -455,7 +490,9 @@ __device__ __forceinline__ void vm_exec(const B2xVmProgram& P, const int64_t (&c
           const char* rp = nullptr; int32_t cs = 0;
 #pragma unroll
           for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) if (t == src_idx) { rp = RA.rp[t]; cs = RA.cs[t]; }
-          vm_fetch_row<V>(rp + (int64_t)((int32_t)col * cs), elem, cs != 0, S.b);
+          // AC: the caller has checked that every tensor the program reads is contiguous along the row, so the fetch has
+          // no branch and the loads of several vectors can be in flight together
+          vm_fetch_row<V>(rp + (int64_t)((int32_t)col * cs), elem, AC ? true : cs != 0, S.b);
         } else {
           const B2xVmTensor& T = P.tensors[src_idx];
           int64_t o = 0;
@@ -553,7 +590,12 @@ __device__ __forceinline__ void vm_exec(const B2xVmProgram& P, const int64_t (&c
       if (tc == VM_F32) B2X_VM_UN_F(fabsf(x))
       else if (tc == VM_S32) { _Pragma("unroll") for (int j = 0; j < V; j++) { int x = (int)S.acc[j]; S.acc[j] = (uint32_t)(x < 0 ? -x : x); } }
       break;
-    case VM_TANH: if (aux) B2X_VM_UN_F(vm_tanh_fast(x)) else B2X_VM_UN_F(vm_tanh(x)) break;
+    // GEMM epilogues (RF / STG) are bound by instruction issue, not by the special-function pipe: there the one-instruction
+    // tanh.approx wins; the standalone elementwise kernel has issue slots to spare and takes the polynomial
+    case VM_TANH:
+      if (aux) { if constexpr (RF || STG) B2X_VM_UN_F(vm_tanh_fast(x)) else vm_tanh_fast_vec<V>(S.acc); }
+      else B2X_VM_UN_F(vm_tanh(x))
+      break;
     case VM_EXP: if (aux) B2X_VM_UN_F(__expf(x)) else B2X_VM_UN_F(expf(x)) break;
     case VM_SQRT: B2X_VM_UN_F(sqrtf(x)) break;
     case VM_LOG: if (aux) B2X_VM_UN_F(__logf(x)) else B2X_VM_UN_RARE(VM_LOG) break;
@@ -632,19 +674,19 @@ __host__ __device__ constexpr int vm_static_stores() {
   return k;
 }
 
-template <int V, int ID, bool RF, bool STG, int PC>
+template <int V, int ID, bool RF, bool STG, int PC, bool AC = false>
 __device__ __forceinline__ void vm_unroll(const B2xVmProgram& P, const int64_t (&coord)[B2X_VM_MAX_DIMS], const int nd,
                                           const int64_t (&off)[B2X_VM_MAX_TENSORS], const VmRowAddr& RA, const int64_t col,
                                           const uint32_t (&acc0)[V], VmState<V>& S) {
   if constexpr (PC < VmStatic<ID>::n) {
     constexpr VmSig G = VmStatic<ID>::at(PC);
     constexpr uint8_t elem = (G.src_kind == VM_SRC_TENSOR) ? VmStatic<ID>::elem(G.src_idx) : (uint8_t)0;
-    vm_exec<V, RF, STG>(P, coord, nd, off, RA, col, G.op, G.src_kind, G.src_idx, G.aux, G.tc, G.rnd, P.code[PC].imm, elem, acc0, S);
-    vm_unroll<V, ID, RF, STG, PC + 1>(P, coord, nd, off, RA, col, acc0, S);
+    vm_exec<V, RF, STG, AC>(P, coord, nd, off, RA, col, G.op, G.src_kind, G.src_idx, G.aux, G.tc, G.rnd, P.code[PC].imm, elem, acc0, S);
+    vm_unroll<V, ID, RF, STG, PC + 1, AC>(P, coord, nd, off, RA, col, acc0, S);
   }
 }
 
-template <int V, int ID, bool RF = false, bool STG = false>
+template <int V, int ID, bool RF = false, bool STG = false, bool AC = false>
 __device__ __forceinline__ void vm_run_core(const B2xVmProgram& P, const int64_t (&coord)[B2X_VM_MAX_DIMS], const int64_t (&off)[B2X_VM_MAX_TENSORS],
                                             const VmRowAddr& RA, const int64_t col, const uint32_t (&acc0)[V], uint32_t (&acc)[V]) {
   const int nd = P.n_dims;
@@ -659,7 +701,7 @@ __device__ __forceinline__ void vm_run_core(const B2xVmProgram& P, const int64_t
       vm_exec<V, RF>(P, coord, nd, off, RA, col, I.op, I.src_kind, I.src_idx, I.aux, I.tc, I.rnd, I.imm, elem, acc0, S);
     }
   } else {
-    vm_unroll<V, ID, RF, STG, 0>(P, coord, nd, off, RA, col, acc0, S);
+    vm_unroll<V, ID, RF, STG, 0, AC>(P, coord, nd, off, RA, col, acc0, S);
   }
 #pragma unroll
   for (int j = 0; j < V; j++) acc[j] = S.acc[j];
@@ -827,6 +869,20 @@ __device__ __forceinline__ void vm_run_row(const B2xVmProgram& P, const VmRow& R
 template <int V, int ID = 0>
 __device__ __forceinline__ void vm_run_row_vec(const B2xVmProgram& P, const VmRow& R, uint32_t col, const uint32_t (&acc0)[V], uint32_t (&acc)[V]) {
   vm_run_core<V, ID, true>(P, R.coord, R.off, R.addr, (int64_t)col, acc0, acc);
+}
+
+// Same again for rows on which every tensor the program reads is contiguous (no operand broadcast along the row): the
+// fetches are straight-line loads.
+template <int V, int ID>
+__device__ __forceinline__ void vm_run_row_contig(const B2xVmProgram& P, const VmRow& R, uint32_t col, const uint32_t (&acc0)[V], uint32_t (&acc)[V]) {
+  vm_run_core<V, ID, true, false, true>(P, R.coord, R.off, R.addr, (int64_t)col, acc0, acc);
+}
+// Whether vm_run_row_contig applies to a row prepared by vm_row_begin.
+__device__ __forceinline__ bool vm_row_all_contiguous(const B2xVmProgram& P, const VmRow& R) {
+  bool ok = R.vec;
+#pragma unroll
+  for (int t = 0; t < B2X_VM_MAX_TENSORS; t++) if (t < P.n_tensors) ok = ok && R.addr.cs[t] != 0;
+  return ok;
 }
 
 // Addressing of a block of consecutive result rows whose tensor offsets are affine in the row number (the usual case:

@@ -60,7 +60,30 @@ PJRT_Error* run_plan(PJRT_LoadedExecutable* le, int local_index, int replica, co
         if (rc) return kernel_error(rc, s);
         break;
       }
+      case StepKind::WIDE: {
+        B2xWideOp w{};
+        w.op = s.w_op; w.n_in = s.w_n_in; w.n_dims = (int)s.w_dims.size(); w.aux = s.w_aux; w.aux2 = s.w_aux2;
+        w.out_elem = (uint8_t)s.w_out_dtype;
+        w.n_elements = 1;
+        for (size_t d = 0; d < s.w_dims.size(); d++) { w.dim[d] = s.w_dims[d]; w.n_elements *= s.w_dims[d]; }
+        for (int k = 0; k < s.w_n_in; k++) {
+          w.in_elem[k] = (uint8_t)s.w_in_dtype[k];
+          w.in[k] = bind(s.w_in[k]);
+          for (size_t d = 0; d < s.w_in_strides[k].size() && d < (size_t)B2X_WIDE_MAX_DIMS; d++) w.in_stride[k][d] = s.w_in_strides[k][d];
+        }
+        w.out = bind(s.w_out);
+        w.imm = s.w_imm;
+        int rc = b2x_launch_wide_elementwise(&w, cs);
+        if (rc) return kernel_error(rc, s);
+        break;
+      }
       case StepKind::REDUCE: {
+        if (s.wide) {
+          int rc = b2x_launch_wide_reduce(bind(s.w_in[0]), (uint8_t)s.w_in_dtype[0], s.rA, s.rR, s.rB, (int)s.monoid,
+                                          s.r_init_is_imm ? nullptr : bind(s.r_init_buf), s.w_imm, bind(s.r_out), cs);
+          if (rc) return kernel_error(rc, s);
+          break;
+        }
         bind_program(s.vm, bind, &prog);
         B2xReduceArgs ra{};
         ra.A = s.rA; ra.R = s.rR; ra.B = s.rB;
@@ -86,7 +109,9 @@ PJRT_Error* run_plan(PJRT_LoadedExecutable* le, int local_index, int replica, co
         ga.a_batch_stride = s.ga.batch_stride; ga.a_row_stride = s.ga.row_stride; ga.a_k_stride = s.ga.k_stride;
         ga.b_batch_stride = s.gb.batch_stride; ga.b_row_stride = s.gb.row_stride; ga.b_k_stride = s.gb.k_stride;
         int rc;
-        if (s.g_tensor_core) {
+        if (s.wide) {
+          rc = b2x_launch_wide_gemm(&ga, (uint8_t)s.w_out_dtype, bind(s.w_out), cs);
+        } else if (s.g_tensor_core) {
           if (s.g_split_f32) {
             // A' = [hi | hi | lo], B' = [hi | lo | hi]: K-major rows of 3K floats in scratch
             float* a_split = (float*)bind(s.scratch);

@@ -87,6 +87,11 @@ struct PJRT_Device {
   std::mutex poison_mu;
   std::map<int, std::pair<PJRT_Error_Code, std::string>> poisoned;  // launch_id -> error
   std::mutex launch_mu;  // serialises enqueues of whole executions on this device
+  // Pinned staging blocks for small device-to-host reads: a copy into pageable host memory makes cudaMemcpyAsync wait
+  // for the stream, so the caller would sit out the whole step it is reading a scalar from.
+  std::mutex staging_mu;
+  std::vector<void*> staging_free;   // blocks of kStagingBlock bytes
+  static constexpr size_t kStagingBlock = 64 << 10;
 };
 
 // Definition of a buffer that is filled after it was created (asynchronous host-to-device transfers): consumers that

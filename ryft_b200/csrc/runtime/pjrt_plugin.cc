@@ -119,6 +119,8 @@ PJRT_Client::~PJRT_Client() {
     if (d->d2h) cudaStreamDestroy(d->d2h);
     if (d->comm) cudaStreamDestroy(d->comm);
     if (d->status_host) cudaFreeHost(d->status_host);
+    for (void* p : d->staging_free) cudaFreeHost(p);
+    d->staging_free.clear();
   }
 }
 
@@ -710,7 +712,18 @@ static PJRT_Error* copy_to_host(PJRT_Buffer* b, void* dst, size_t offset, size_t
   PJRT_Device* d = b->device;
   B2X_CUDA(cudaSetDevice(d->cuda_ordinal));
   if (b->ready) B2X_CUDA(cudaStreamWaitEvent(d->d2h, b->ready, 0));
-  if (size) B2X_CUDA(cudaMemcpyAsync(dst, (const char*)b->ptr + offset, size, cudaMemcpyDeviceToHost, d->d2h));
+  // Small reads (a loss, a metric) go through a pinned staging block and reach `dst` on the poller thread when the copy
+  // has finished: the call returns at once even though `dst` is ordinary pageable memory, so a training loop can
+  // enqueue its next step before the current one is done.  Larger reads are dominated by the transfer itself.
+  void* staging = nullptr;
+  if (size && size <= PJRT_Device::kStagingBlock) {
+    std::lock_guard<std::mutex> sl(d->staging_mu);
+    if (!d->staging_free.empty()) { staging = d->staging_free.back(); d->staging_free.pop_back(); }
+  }
+  if (size && size <= PJRT_Device::kStagingBlock && !staging) {
+    if (cudaHostAlloc(&staging, PJRT_Device::kStagingBlock, cudaHostAllocDefault) != cudaSuccess) { cudaGetLastError(); staging = nullptr; }
+  }
+  if (size) B2X_CUDA(cudaMemcpyAsync(staging ? staging : dst, (const char*)b->ptr + offset, size, cudaMemcpyDeviceToHost, d->d2h));
   cudaEvent_t ev, keep;
   B2X_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
   B2X_CUDA(cudaEventRecord(ev, d->d2h));
@@ -723,7 +736,12 @@ static PJRT_Error* copy_to_host(PJRT_Buffer* b, void* dst, size_t offset, size_t
   b->pending_reads.push_back(keep);
   PJRT_Event* pe = new PJRT_Event();
   PJRT_Device* dev = d;
-  b->client->post({ev, d->cuda_ordinal, pe, [dev](PJRT_Error_Code* code, std::string* msg) {
+  b->client->post({ev, d->cuda_ordinal, pe, [dev, staging, dst, size](PJRT_Error_Code* code, std::string* msg) {
+                     if (staging) {
+                       if (*code == PJRT_Error_Code_OK) memcpy(dst, staging, size);
+                       std::lock_guard<std::mutex> sl(dev->staging_mu);
+                       dev->staging_free.push_back(staging);
+                     }
                      report_expired_wait(dev, code, msg);
                    }});
   *event = pe;
@@ -1264,7 +1282,8 @@ static PJRT_Error* Ext_WaitStream(PJRT_Wait_Until_Buffer_Ready_On_Stream_Args* a
 static int step_kernel_launches(const Step& s) {
   switch (s.kind) {
     case StepKind::ELEMENTWISE: return 1;
-    case StepKind::REDUCE: return reduce_launches(s.rA, s.rR, s.rB);
+    case StepKind::WIDE: return 1;
+    case StepKind::REDUCE: return s.wide ? 1 : reduce_launches(s.rA, s.rR, s.rB);
     case StepKind::GEMM: return s.g_split_f32 ? 2 : 1;
     case StepKind::ATTENTION: return 1;
     default: return 0;
@@ -1281,7 +1300,7 @@ static PJRT_Error* Ext_StepTiming(B2X_StepTiming_Args* a) {
     for (auto& s : plan.steps) {
       const char* kind = s.kind == StepKind::GEMM ? (s.g_tensor_core ? "gemm_tc " : "gemm_simt ") : s.kind == StepKind::REDUCE ? "reduce " :
                          s.kind == StepKind::ELEMENTWISE ? "elementwise " : s.kind == StepKind::ATTENTION ? "attention " :
-                         s.kind == StepKind::COPY ? "copy " : "collective ";
+                         s.kind == StepKind::COPY ? "copy " : s.kind == StepKind::WIDE ? "wide " : "collective ";
       le->step_labels.push_back(std::string(kind) + s.label);
       le->step_flops.push_back(s.flops);
       le->step_bytes.push_back(s.bytes);

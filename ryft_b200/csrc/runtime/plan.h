@@ -21,7 +21,7 @@ struct BufRef {
   bool valid() const { return kind != NONE; }
 };
 
-enum class StepKind : uint8_t { ELEMENTWISE, REDUCE, GEMM, ATTENTION, ALL_REDUCE, ALL_GATHER, COPY };
+enum class StepKind : uint8_t { ELEMENTWISE, REDUCE, GEMM, ATTENTION, ALL_REDUCE, ALL_GATHER, COPY, WIDE };
 
 struct VmBinding {
   B2xVmProgram prog{};             // tensor pointers are null in the plan; bound at launch
@@ -81,6 +81,20 @@ struct Step {
   // COPY
   BufRef c_src, c_dst;
   int64_t c_bytes = 0;
+
+  // 64-bit element types (i64, ui64, f64) do not fit the 32-bit registers of the fused-elementwise programs: an op that
+  // reads or writes such a tensor is a step of its own.  WIDE: one elementwise op (or copy / fill / iota) with strided
+  // operands; REDUCE and GEMM steps with `wide` set use the 64-bit kernels and the REDUCE / GEMM fields above.
+  bool wide = false;
+  int w_op = 0;                    // B2xWideOpKind
+  int w_aux = 0, w_aux2 = 0;
+  int w_n_in = 0;
+  DType w_in_dtype[3] = {DType::S64, DType::S64, DType::S64};
+  DType w_out_dtype = DType::S64;
+  std::vector<int64_t> w_dims;
+  std::vector<int64_t> w_in_strides[3];
+  BufRef w_in[3], w_out;
+  uint64_t w_imm = 0;
 
   // bookkeeping for cost analysis
   double flops = 0, bytes = 0;

@@ -8,6 +8,8 @@
 // arena whose offsets are assigned from value lifetimes.
 #include "plan.h"
 
+#include "../../../include/b2x_kernels.h"
+
 #include <algorithm>
 #include <cmath>
 #include <cstring>
@@ -88,7 +90,15 @@ uint32_t element_to_reg(const uint8_t* p, DType t) {
   }
 }
 
+bool is_wide_type(DType t) { return dtype_size(t) == 8; }
+// An op that reads or writes a 64-bit tensor: it runs as a step of its own on the 64-bit kernels.
+bool touches_wide(const Op& op) {
+  for (auto v : op.operands) if (is_wide_type(v->type.dtype)) return true;
+  for (auto v : op.results) if (is_wide_type(v->type.dtype)) return true;
+  return false;
+}
 bool is_fusible_kind(const Op& op) {
+  if (touches_wide(op)) return false;
   if (op.kind == OpKind::BROADCAST_IN_DIM) return true;
   if (op.kind == OpKind::CONSTANT) return op.splat;
   if (op.kind == OpKind::RETURN) return false;
@@ -262,6 +272,9 @@ class Planner {
   void emit_reduce(const Op& op);
   void emit_dot(const Op& op);
   void emit_view_or_copy(const Op& op);
+  void emit_wide(const Op& op);
+  void emit_wide_copy(const Layout& src, DType src_dt, const std::vector<int64_t>& dims, const BufRef& dst, DType dst_dt, const std::string& label);
+  void emit_wide_reduce(const Op& op);
   void emit_collective(const Op& op);
   void emit_outputs();
   BufRef emit_strided_copy(const Layout& src, DType dt, const std::vector<int64_t>& dims, const std::string& label);
@@ -389,6 +402,17 @@ void Planner::GroupBuilder::gen(int ni) {
   const Op& op = *n.op;
   auto bin = [&](uint8_t fwd, uint8_t rev, uint8_t aux, uint8_t tc, uint8_t rnd) {
     int x = n.in[0], y = n.in[1];
+    if (x == y && nodes[x].k == GNode::TENSOR && nodes[x].temp < 0 && !free_temps.empty()) {
+      // both operands are the same tensor element (x * x): fetch it once
+      gen(x);
+      int t = alloc_temp();
+      B2xVmInstr S{}; S.op = VM_SAVE; S.aux = (uint8_t)t; code.push_back(S);
+      B2xVmInstr I{}; I.op = fwd; I.aux = aux; I.tc = tc; I.rnd = rnd; I.src_kind = VM_SRC_TEMP; I.src_idx = (uint8_t)t;
+      code.push_back(I);
+      free_temps.push_back(t);
+      consume(y);
+      return;
+    }
     if (simple(y)) { gen(x); emit(fwd, nullptr, y, aux, tc, rnd); }
     else if (simple(x)) { gen(y); emit(rev, nullptr, x, aux, tc, rnd); }
     else {
@@ -887,6 +911,7 @@ int reduce_splits_impl(int64_t A, int64_t R, int64_t B) {
 }
 
 void Planner::emit_reduce(const Op& op) {
+  if (is_wide_type(op.operands[0]->type.dtype)) { emit_wide_reduce(op); return; }
   const Value* x = op.operands[0];
   const Value* init = op.operands[1];
   const Value* res = op.results[0];
@@ -1026,7 +1051,7 @@ BufRef Planner::emit_strided_copy(const Layout& src, DType dt, const std::vector
   for (auto d : dims) n *= d;
   BufRef dst = new_temp(n * dtype_size(dt));
   if (dtype_size(dt) == 8) {
-    if (!is_row_major(dims, src.strides)) unimplemented("layout-changing copies of 64-bit element types are not supported");
+    if (!is_row_major(dims, src.strides)) { emit_wide_copy(src, dt, dims, dst, dt, label); return dst; }
     Step s; s.kind = StepKind::COPY; s.label = label; s.c_src = src.buf; s.c_dst = dst; s.c_bytes = n * 8;
     touch(src.buf); touch(dst);
     plan_.steps.push_back(s);
@@ -1045,6 +1070,172 @@ BufRef Planner::emit_strided_copy(const Layout& src, DType dt, const std::vector
   VmBinding vb = gb.finish(-1);
   push_vm_step(std::move(vb), label);
   return dst;
+}
+
+// ---- 64-bit element types ----------------------------------------------------------------------------------------------
+// Copies (and converts) a strided view into a dense row-major tensor with the 64-bit elementwise kernel.
+void Planner::emit_wide_copy(const Layout& src, DType src_dt, const std::vector<int64_t>& dims, const BufRef& dst, DType dst_dt, const std::string& label) {
+  if ((int)dims.size() > B2X_WIDE_MAX_DIMS) unimplemented("64-bit tensors of rank above " + std::to_string(B2X_WIDE_MAX_DIMS));
+  Step s;
+  s.kind = StepKind::WIDE;
+  s.label = label;
+  s.w_op = B2X_WIDE_COPY;
+  s.w_n_in = 1;
+  s.w_in_dtype[0] = src_dt; s.w_out_dtype = dst_dt;
+  s.w_dims = dims;
+  s.w_in_strides[0] = src.strides;
+  s.w_in[0] = src.buf; s.w_out = dst;
+  int64_t n = 1;
+  for (auto d : dims) n *= d;
+  s.bytes = (double)n * (dtype_size(src_dt) + dtype_size(dst_dt));
+  touch(src.buf); touch(dst);
+  plan_.steps.push_back(std::move(s));
+}
+
+// One elementwise-class op over 64-bit tensors (or converting to / from one).
+void Planner::emit_wide(const Op& op) {
+  const Value* res = op.results[0];
+  if (res->type.rank() > B2X_WIDE_MAX_DIMS) unimplemented("64-bit tensors of rank above " + std::to_string(B2X_WIDE_MAX_DIMS));
+  Step s;
+  s.kind = StepKind::WIDE;
+  s.label = std::string(op_name(op.kind)) + ":%" + res->name;
+  s.w_dims = res->type.dims;
+  s.w_out_dtype = res->type.dtype;
+  auto operand = [&](int k, const Value* v, const std::vector<int>& map) {
+    // map[i] = result dim that operand dim i walks (-1: the operand dim has extent 1)
+    Layout& L = layout_of(v);
+    std::vector<int64_t> st(res->type.rank(), 0);
+    for (int i = 0; i < v->type.rank(); i++) if (map[i] >= 0 && v->type.dims[i] > 1) st[map[i]] += L.strides[i];
+    s.w_in[k] = L.buf; s.w_in_dtype[k] = v->type.dtype; s.w_in_strides[k] = st;
+    touch(L.buf);
+  };
+  auto same_shape = [&](const Value* v) {
+    std::vector<int> ident(v->type.rank());
+    for (int i = 0; i < v->type.rank(); i++) ident[i] = i;
+    if (v->type.rank() == 0) ident.clear();
+    return ident;
+  };
+  static const std::map<OpKind, int> simple = {
+      {OpKind::ADD, B2X_WIDE_ADD}, {OpKind::SUBTRACT, B2X_WIDE_SUB}, {OpKind::MULTIPLY, B2X_WIDE_MUL}, {OpKind::DIVIDE, B2X_WIDE_DIV},
+      {OpKind::REMAINDER, B2X_WIDE_REM}, {OpKind::POWER, B2X_WIDE_POW}, {OpKind::MAXIMUM, B2X_WIDE_MAX}, {OpKind::MINIMUM, B2X_WIDE_MIN},
+      {OpKind::AND, B2X_WIDE_AND}, {OpKind::OR, B2X_WIDE_OR}, {OpKind::XOR, B2X_WIDE_XOR}, {OpKind::NEGATE, B2X_WIDE_NEG}, {OpKind::ABS, B2X_WIDE_ABS},
+      {OpKind::SIGN, B2X_WIDE_SIGN}, {OpKind::NOT, B2X_WIDE_NOT}, {OpKind::TANH, B2X_WIDE_TANH}, {OpKind::EXP, B2X_WIDE_EXP}, {OpKind::LOG, B2X_WIDE_LOG},
+      {OpKind::SQRT, B2X_WIDE_SQRT}, {OpKind::RSQRT, B2X_WIDE_RSQRT}, {OpKind::LOGISTIC, B2X_WIDE_LOGISTIC}, {OpKind::FLOOR, B2X_WIDE_FLOOR},
+      {OpKind::CEIL, B2X_WIDE_CEIL}, {OpKind::EXPM1, B2X_WIDE_EXPM1}, {OpKind::LOG1P, B2X_WIDE_LOG1P}, {OpKind::SINE, B2X_WIDE_SIN},
+      {OpKind::COSINE, B2X_WIDE_COS}, {OpKind::CONVERT, B2X_WIDE_COPY}, {OpKind::SELECT, B2X_WIDE_SELECT}, {OpKind::CLAMP, B2X_WIDE_CLAMP},
+      {OpKind::COMPARE, B2X_WIDE_COMPARE}};
+  switch (op.kind) {
+    case OpKind::CONSTANT: {   // splat (dense constants live in the constant pool)
+      s.w_op = B2X_WIDE_FILL;
+      // bit pattern of the value in the class of the result type (int64 / uint64 / double)
+      const uint8_t* p = op.const_data.data();
+      switch (res->type.dtype) {
+        case DType::S64: case DType::U64: case DType::F64: memcpy(&s.w_imm, p, 8); break;
+        default: internal("wide fill of a narrow type");
+      }
+      break;
+    }
+    case OpKind::IOTA:
+      s.w_op = B2X_WIDE_IOTA;
+      s.w_aux = (int)op.iota_dim;
+      break;
+    case OpKind::BROADCAST_IN_DIM: {
+      s.w_op = B2X_WIDE_COPY;
+      s.w_n_in = 1;
+      const Value* u = op.operands[0];
+      std::vector<int> map(u->type.rank());
+      for (int i = 0; i < u->type.rank(); i++) map[i] = u->type.dims[i] == 1 ? -1 : (int)op.dims[i];
+      operand(0, u, map);
+      break;
+    }
+    default: {
+      auto it = simple.find(op.kind);
+      if (it == simple.end()) unimplemented(std::string(op_name(op.kind)) + " over 64-bit element types");
+      s.w_op = it->second;
+      s.w_n_in = (int)op.operands.size();
+      if (s.w_n_in > 3) internal("wide op with more than three operands");
+      for (int k = 0; k < s.w_n_in; k++) {
+        const Value* v = op.operands[k];
+        // a scalar predicate of select and scalar bounds of clamp apply to every element
+        std::vector<int> map = (v->type.rank() == 0 && res->type.rank() != 0) ? std::vector<int>() : same_shape(v);
+        operand(k, v, map);
+      }
+      if (op.kind == OpKind::COMPARE) {
+        s.w_aux = (int)op.cmp_dir;
+        s.w_aux2 = op.cmp_type == CmpType::UNSIGNED ? 1 : (op.cmp_type == CmpType::SIGNED ? 2 : 0);
+      }
+      break;
+    }
+  }
+  s.w_out = materialise(res);
+  s.bytes = (double)res->type.byte_size();
+  for (int k = 0; k < s.w_n_in; k++) s.bytes += (double)op.operands[k]->type.byte_size();
+  touch(s.w_out);
+  plan_.steps.push_back(std::move(s));
+}
+
+// stablehlo.reduce over a 64-bit tensor: one pass per maximal run of adjacent reduced dims, innermost first.
+void Planner::emit_wide_reduce(const Op& op) {
+  const Value* x = op.operands[0];
+  const Value* init = op.operands[1];
+  const Value* res = op.results[0];
+  const DType dt = x->type.dtype;
+  Layout L = layout_of(x);
+  BufRef cur = L.buf;
+  if (!is_row_major(x->type.dims, L.strides)) cur = emit_strided_copy(L, dt, x->type.dims, "copy:reduce_operand");
+  std::vector<int64_t> rd = op.dims;
+  std::sort(rd.begin(), rd.end());
+  std::vector<std::pair<int, int>> runs;
+  std::vector<int64_t> shape = x->type.dims;
+  if (rd.empty()) runs.push_back({(int)shape.size(), (int)shape.size() - 1});
+  else {
+    size_t i = 0;
+    while (i < rd.size()) { size_t j = i; while (j + 1 < rd.size() && rd[j + 1] == rd[j] + 1) j++; runs.push_back({(int)rd[i], (int)rd[j]}); i = j + 1; }
+    std::reverse(runs.begin(), runs.end());
+  }
+  const bool init_imm = init->def && init->def->kind == OpKind::CONSTANT && init->def->splat;
+  for (size_t p = 0; p < runs.size(); p++) {
+    const bool last = p + 1 == runs.size();
+    const int lo = runs[p].first, hi = runs[p].second;
+    int64_t A = 1, R = 1, B = 1;
+    for (int d = 0; d < (int)shape.size(); d++) { if (d < lo) A *= shape[d]; else if (d <= hi) R *= shape[d]; else B *= shape[d]; }
+    Step s;
+    s.kind = StepKind::REDUCE;
+    s.wide = true;
+    s.label = std::string("reduce:%") + res->name + (runs.size() > 1 ? ":pass" + std::to_string(p) : "");
+    s.rA = A; s.rR = R; s.rB = B;
+    s.monoid = op.monoid;
+    s.w_in[0] = cur; s.w_in_dtype[0] = dt;
+    s.r_out_dtype = dt;
+    if (last) {
+      s.r_out = materialise(res);
+      s.r_init_is_imm = init_imm;
+      if (init_imm) memcpy(&s.w_imm, init->def->const_data.data(), 8);
+      else { s.r_init_buf = layout_of(init).buf; s.r_init_dtype = dt; }
+    } else {
+      s.r_out = new_temp(A * B * 8);
+      s.r_init_is_imm = true;
+      // identity of the monoid in the class of dt
+      const bool f = dt == DType::F64, sg = dt == DType::S64;
+      double one = 1.0, ninf = -INFINITY, pinf = INFINITY;
+      uint64_t id = 0;
+      switch (op.monoid) {
+        case Monoid::ADD: case Monoid::OR: case Monoid::XOR: id = 0; break;
+        case Monoid::MUL: if (f) memcpy(&id, &one, 8); else id = 1; break;
+        case Monoid::MAX: if (f) memcpy(&id, &ninf, 8); else id = sg ? 0x8000000000000000ull : 0ull; break;
+        case Monoid::MIN: if (f) memcpy(&id, &pinf, 8); else id = sg ? 0x7fffffffffffffffull : ~0ull; break;
+        case Monoid::AND: id = ~0ull; break;
+      }
+      s.w_imm = id;
+    }
+    s.bytes = (double)A * R * B * 8;
+    touch(cur); touch(s.r_out); touch(s.r_init_buf);
+    cur = s.r_out;
+    plan_.steps.push_back(std::move(s));
+    std::vector<int64_t> ns;
+    for (int d = 0; d < (int)shape.size(); d++) if (d < lo || d > hi) ns.push_back(shape[d]);
+    shape = ns;
+  }
 }
 
 void Planner::emit_view_or_copy(const Op& op) {
@@ -1115,10 +1306,12 @@ void Planner::emit_dot(const Op& op) {
   const Value* res = op.results[0];
   DType in_dt = lv->type.dtype;
   if (rv->type.dtype != in_dt) unimplemented("dot_general with operands of different element types");
-  bool float_in = (in_dt == DType::F32 || in_dt == DType::BF16 || in_dt == DType::F16);
-  bool int_in = (in_dt == DType::S32 || in_dt == DType::S8 || in_dt == DType::S16 || in_dt == DType::U8 || in_dt == DType::U16 || in_dt == DType::U32);
+  const bool wide = is_wide_type(in_dt) || is_wide_type(res->type.dtype);
+  bool float_in = (in_dt == DType::F32 || in_dt == DType::BF16 || in_dt == DType::F16 || in_dt == DType::F64);
+  bool int_in = (in_dt == DType::S32 || in_dt == DType::S8 || in_dt == DType::S16 || in_dt == DType::U8 || in_dt == DType::U16 || in_dt == DType::U32 ||
+                 in_dt == DType::S64 || in_dt == DType::U64);
   if (!float_in && !int_in) unimplemented(std::string("dot_general over ") + dtype_name(in_dt));
-  class_of(res->type.dtype);
+  if (!wide) class_of(res->type.dtype);
 
   auto free_dims = [](int rank, const std::vector<int64_t>& a, const std::vector<int64_t>& b) {
     std::vector<int64_t> f;
@@ -1173,6 +1366,16 @@ void Planner::emit_dot(const Op& op) {
   s.gB = Bl; s.gM = M; s.gN = N; s.gK = Kl;
   s.g_acc_dtype = float_in ? DType::F32 : DType::S32;
   s.flops = 2.0 * (double)s.gB * (double)M * (double)N * (double)Kl;
+  if (wide) {
+    // 64-bit operands or result: the plain strided kernel, result stored densely, consumers read it from memory
+    s.wide = true;
+    s.w_out_dtype = res->type.dtype;
+    s.w_out = materialise(res);
+    s.bytes = (double)lv->type.byte_size() + (double)rv->type.byte_size() + (double)res->type.byte_size();
+    touch(s.ga.buf); touch(s.gb.buf); touch(s.w_out);
+    plan_.steps.push_back(std::move(s));
+    return;
+  }
 
   // ---- tensor-core eligibility ----
   auto tc_operand_ok = [&](const GemmOperand& g, int64_t rows) {
@@ -1286,7 +1489,7 @@ void Planner::emit_collective(const Op& op) {
   }
   plan_.steps.push_back(std::move(s));
   for (auto& pc : pending_copies) {
-    if (dtype_size(pc.dt) == 8) unimplemented("all_gather of 64-bit elements along an inner dimension");
+    if (dtype_size(pc.dt) == 8) { emit_wide_copy(pc.src, pc.dt, pc.dims, pc.dst, pc.dt, "copy:all_gather_interleave"); continue; }
     GroupBuilder gb;
     gb.P = this;
     gb.root_dims = pc.dims;
@@ -1313,8 +1516,9 @@ void Planner::emit_outputs() {
     BufRef dst;
     dst.kind = BufRef::OUT;
     dst.index = (int)i;
-    if (is_row_major(v->type.dims, L.strides) || dtype_size(v->type.dtype) == 8) {
-      if (!is_row_major(v->type.dims, L.strides)) unimplemented("returning a transposed view of a 64-bit tensor");
+    if (!is_row_major(v->type.dims, L.strides) && dtype_size(v->type.dtype) == 8) {
+      emit_wide_copy(L, v->type.dtype, v->type.dims, dst, v->type.dtype, "copy:output" + std::to_string(i));
+    } else if (is_row_major(v->type.dims, L.strides)) {
       Step c;
       c.kind = StepKind::COPY;
       c.label = "copy:output" + std::to_string(i);
@@ -1356,7 +1560,17 @@ static void step_bufs(const Step& s, std::vector<BufRef>* reads, std::vector<Buf
   };
   switch (s.kind) {
     case StepKind::ELEMENTWISE: vm_sets(s.vm); break;
+    case StepKind::WIDE:
+      for (int k = 0; k < s.w_n_in; k++) reads->push_back(s.w_in[k]);
+      writes->push_back(s.w_out);
+      break;
     case StepKind::REDUCE:
+      if (s.wide) {
+        reads->push_back(s.w_in[0]);
+        writes->push_back(s.r_out);
+        if (s.r_init_buf.valid()) reads->push_back(s.r_init_buf);
+        break;
+      }
       vm_sets(s.vm);
       if (s.has_post) vm_sets(s.post);
       if (s.r_out.valid()) writes->push_back(s.r_out);
@@ -1365,6 +1579,7 @@ static void step_bufs(const Step& s, std::vector<BufRef>* reads, std::vector<Buf
       break;
     case StepKind::GEMM:
       reads->push_back(s.ga.buf); reads->push_back(s.gb.buf);
+      if (s.wide) { writes->push_back(s.w_out); break; }
       vm_sets(s.vm);
       if (s.scratch.valid()) writes->push_back(s.scratch);
       break;
@@ -1507,6 +1722,8 @@ void Planner::assign_arena() {
     for (auto& b : s.post.bufs) fix(b);
     fix(s.r_out); fix(s.r_init_buf); fix(s.scratch); fix(s.ga.buf); fix(s.gb.buf);
     fix(s.aq); fix(s.ak); fix(s.av); fix(s.ao); fix(s.c_src); fix(s.c_dst);
+    for (int k = 0; k < 3; k++) fix(s.w_in[k]);
+    fix(s.w_out);
     for (auto& c : s.colls) { fix(c.src); fix(c.dst); }
   }
 }
@@ -1551,6 +1768,11 @@ Plan Planner::run() {
         if (is_fusible_kind(op)) {
           const Value* r = op.results[0];
           if (st(r).root && !st(r).dead) emit_group_for_root(r);
+          break;
+        }
+        if (touches_wide(op) && (op_is_elementwise(op.kind) || op.kind == OpKind::CONSTANT || op.kind == OpKind::IOTA ||
+                                 op.kind == OpKind::BROADCAST_IN_DIM)) {
+          emit_wide(op);
           break;
         }
         switch (op.kind) {
@@ -1639,12 +1861,17 @@ std::string Plan::dump() const {
     switch (s.kind) {
       case StepKind::ELEMENTWISE: o << "elementwise " << s.label << "\n" << vm_str(s.vm); break;
       case StepKind::REDUCE:
+        if (s.wide) {
+          o << "reduce " << s.label << " [A=" << s.rA << ",R=" << s.rR << ",B=" << s.rB << "] monoid=" << (int)s.monoid << " 64-bit " << buf_str(s.w_in[0]) << " -> "
+            << buf_str(s.r_out) << ":" << dtype_name(s.r_out_dtype) << "\n";
+          break;
+        }
         o << "reduce " << s.label << " [A=" << s.rA << ",R=" << s.rR << ",B=" << s.rB << "] monoid=" << (int)s.monoid << " -> " << buf_str(s.r_out)
           << ":" << dtype_name(s.r_out_dtype) << "\n" << vm_str(s.vm);
         if (s.has_post) o << "    on each result:\n" << vm_str(s.post);
         break;
       case StepKind::GEMM:
-        o << "gemm " << s.label << " B=" << s.gB << " M=" << s.gM << " N=" << s.gN << " K=" << s.gK << (s.g_tensor_core ? " tcgen05" : " simt")
+        o << "gemm " << s.label << " B=" << s.gB << " M=" << s.gM << " N=" << s.gN << " K=" << s.gK << (s.wide ? " 64-bit" : (s.g_tensor_core ? " tcgen05" : " simt"))
           << (s.g_split_f32 ? " 3xtf32" : "") << " A=" << buf_str(s.ga.buf) << "(" << s.ga.batch_stride << "," << s.ga.row_stride << ","
           << s.ga.k_stride << ") B=" << buf_str(s.gb.buf) << "(" << s.gb.batch_stride << "," << s.gb.row_stride << "," << s.gb.k_stride << ")\n"
           << vm_str(s.vm);
@@ -1656,6 +1883,13 @@ std::string Plan::dump() const {
       case StepKind::ALL_REDUCE: case StepKind::ALL_GATHER:
         o << (s.kind == StepKind::ALL_REDUCE ? "all_reduce" : "all_gather") << " #" << s.coll_id << " " << buf_str(s.colls[0].src) << " -> " << buf_str(s.colls[0].dst)
           << " count=" << s.colls[0].count << " groups=" << s.replica_groups.size() << (s.coll_detached ? " detached" : "") << "\n";
+        break;
+      case StepKind::WIDE:
+        o << "wide " << s.label << " op=" << s.w_op << " dims=[";
+        for (size_t d = 0; d < s.w_dims.size(); d++) o << (d ? "," : "") << s.w_dims[d];
+        o << "]";
+        for (int k = 0; k < s.w_n_in; k++) o << " " << buf_str(s.w_in[k]) << ":" << dtype_name(s.w_in_dtype[k]);
+        o << " -> " << buf_str(s.w_out) << ":" << dtype_name(s.w_out_dtype) << "\n";
         break;
       case StepKind::COPY: o << "copy " << s.label << " " << buf_str(s.c_src) << " -> " << buf_str(s.c_dst) << " " << s.c_bytes << " B\n"; break;
     }

@@ -573,3 +573,58 @@ def test_reduce_with_zero_outputs_and_long_rows(client):
     text = b.build(b.reduce(x, b.constant(0.0, [], "f32"), "add", [1]))
     (got,) = check_program(client, text, [np.zeros((0, 8192), np.float32)], "empty rows")
     assert got.shape == (0,)
+
+
+# ---- 64-bit element types ----------------------------------------------------------------------------------------------------
+
+def test_dot_general_batched_identity_example_i64(client):
+    """The reference's worked example of dot_general as it is written there, with i64 tensors
+    (crates/ryft-mlir/src/dialects/stable_hlo/operations/linear_algebra.rs:671-701)."""
+    b = Builder()
+    x = b.arg([2, 2, 2], "i64"); y = b.arg([2, 2, 2], "i64")
+    text = b.build(b.dot_general(x, y, ([0], [0]), ([2], [1])))
+    lhs = np.array([[[1, 2], [3, 4]], [[5, 6], [7, 8]]], np.int64)
+    rhs = np.array([[[1, 0], [0, 1]], [[1, 0], [0, 1]]], np.int64)
+    (got,) = check_program(client, text, [lhs, rhs], "i64 dot_general example")
+    assert got.dtype == np.int64 and np.array_equal(got, lhs)
+
+
+@pytest.mark.parametrize("dtype,np_dt", [("i64", np.int64), ("ui64", np.uint64)])
+def test_64_bit_integer_arithmetic_is_bit_exact(client, dtype, np_dt):
+    shape = (37, 5)
+    b = Builder()
+    x = b.arg(shape, dtype); y = b.arg(shape, dtype); z = b.arg([5], dtype)
+    zb = b.broadcast_in_dim(z, [1], list(shape))
+    one = b.splat(1, y)
+    outs = [b.add(x, y), b.subtract(x, y), b.multiply(x, y), b.maximum(x, zb), b.minimum(x, y),
+            b.divide(x, b.maximum(b.abs(y) if dtype == "i64" else y, one)), b.compare("GE", x, zb, "SIGNED" if dtype == "i64" else "UNSIGNED"),
+            b.select(b.compare("LT", x, y, "SIGNED" if dtype == "i64" else "UNSIGNED"), x, y), b.iota(1, list(shape), dtype),
+            b.convert(x, "i32"), b.convert(x, "f32"), b.transpose(x, [1, 0]),
+            b.reduce(x, b.constant(0, [], dtype), "add", [0, 1]), b.reduce(x, b.constant(0, [], dtype), "add", [0]),
+            b.reduce(x, b.constant(0, [], dtype), "maximum", [1])]
+    big = np.random.default_rng(40).integers(0, 2 ** 40, size=shape).astype(np_dt)      # values beyond 32 bits
+    if dtype == "i64":
+        big = big - (2 ** 39)
+    check_program(client, b.build(*outs), [big, rnd(shape, np.int32, 41).astype(np_dt) if dtype == "i64" else rnd(shape, np.uint32, 41).astype(np_dt),
+                                           rnd((5,), np.int32, 42).astype(np_dt) if dtype == "i64" else rnd((5,), np.uint32, 42).astype(np_dt)], dtype)
+
+
+def test_f64_arithmetic_reduce_and_dot(client):
+    """Double-precision programs: elementwise chain, conversions to and from narrower floats, reductions, dot_general.
+    Results are compared as f64 at 1e-12 relative Frobenius error (only summation order may differ)."""
+    b = Builder()
+    x = b.arg([48, 24], "f64"); y = b.arg([24, 40], "f64"); h = b.arg([48, 24], "bf16")
+    d = b.dot_general(x, y, ([], []), ([1], [0]))
+    e = b.add(b.multiply(x, x), b.convert(h, "f64"))
+    t = b.tanh(b.divide(e, b.splat(3.0, e)))
+    outs = [d, t, b.convert(t, "f32"), b.convert(e, "bf16"), b.reduce(e, b.constant(0.0, [], "f64"), "add", [0, 1]),
+            b.reduce(d, b.constant(float("-inf"), [], "f64"), "maximum", [1]), b.exponential(b.negate(b.abs(x))), b.sqrt(b.abs(x))]
+    r = np.random.default_rng(43)
+    ins = [r.standard_normal((48, 24)), r.standard_normal((24, 40)), r.standard_normal((48, 24)).astype(np.float32).astype(BF16)]
+    got = run_gpu(client, b.build(*outs), ins)
+    want = run_oracle(b.build(*outs), ins)
+    for i, (g, w) in enumerate(zip(got, want)):
+        if w.dtype == np.float64:
+            assert g.dtype == np.float64 and np.linalg.norm(g - w) <= 1e-12 * max(np.linalg.norm(w), 1e-300), i
+        else:
+            assert_close(g, w, f"f64 program output {i}")
