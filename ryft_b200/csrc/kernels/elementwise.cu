@@ -38,7 +38,7 @@ extern "C" int b2x_launch_elementwise(const B2xVmProgram* prog, int64_t n_elemen
   dim3 grid((unsigned)blocks), block(256);
   if (vec == 8) {
     // a program whose structure was known at build time runs as straight-line code, anything else is interpreted
-    switch (vm_static_lookup(vm_signature_hash(*prog))) {
+    switch (vm_static_enabled() ? vm_static_lookup(vm_signature_hash(*prog)) : 0) {
 #define X(I) case I: k_elementwise<8, I><<<grid, block, 0, stream>>>(*prog, n_vec); break;
       B2X_VM_STATIC_ELEMENTWISE(X)
 #undef X

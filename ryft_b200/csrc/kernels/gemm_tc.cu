@@ -167,7 +167,7 @@ static int tc_route(const B2xGemmArgs* a, const B2xVmProgram* epilogue, TcRoute*
     p.group_m = (int)gm;
   }
   p.idesc = sm100::make_idesc(r->tf32 ? 2u : (a->elem == EL_BF16 ? 1u : 0u), r->a_mn, r->b_mn, TC_BM, (uint32_t)BN);
-  const int id = vm_static_lookup(vm_signature_hash(*epilogue));
+  const int id = vm_static_enabled() ? vm_static_lookup(vm_signature_hash(*epilogue)) : 0;
   r->static_id = (id && (r->tf32 ? tc_static_has_tf32(id, BN) : tc_static_has(id, BN))) ? id : 0;
   return 0;
 }

@@ -52,6 +52,26 @@ def programs():
             b = Builder()
             x = b.arg([256, 128], dt_in); y = b.arg([128, n], dt_in)
             out.append((b.build(b.dot_general(x, y, ([], []), ([1], [0]), out_dtype=dt_out)), 1))
+    # the usual dense-layer epilogues: bias, then nothing / logistic / relu / tanh-GELU, stored as bf16 (tanh is config 2's),
+    # and bias alone stored as f32; at the two tile widths that large GEMMs take
+    import math
+    for n in (128, 2048):
+        for act in ("none", "logistic", "relu", "gelu"):
+            b = Builder()
+            x = b.arg([256, 128], "bf16"); w = b.arg([128, n], "bf16"); bias = b.arg([n], "f32")
+            y = b.add(b.dot_general(x, w, ([], []), ([1], [0]), out_dtype="f32"), b.broadcast_in_dim(bias, [1], [256, n]))
+            if act == "logistic":
+                y = b.logistic(y)
+            elif act == "relu":
+                y = b.maximum(y, b.splat(0.0, y))
+            elif act == "gelu":
+                c0 = math.sqrt(2.0 / math.pi)
+                inner = b.multiply(b.splat(c0, y), b.add(y, b.multiply(b.splat(0.044715, y), b.multiply(b.multiply(y, y), y))))
+                y = b.multiply(b.multiply(b.splat(0.5, y), y), b.add(b.splat(1.0, y), b.tanh(inner)))
+            out.append((b.build(b.convert(y, "bf16")), 1))
+        b = Builder()
+        x = b.arg([256, 128], "bf16"); w = b.arg([128, n], "bf16"); bias = b.arg([n], "f32")
+        out.append((b.build(b.add(b.dot_general(x, w, ([], []), ([1], [0]), out_dtype="f32"), b.broadcast_in_dim(bias, [1], [256, n]))), 1))
     # common standalone shapes: copy/transposed copy, scale, add, axpy-like, row/full reductions of f32 and bf16
     for dt in ("f32", "bf16"):
         b = Builder()

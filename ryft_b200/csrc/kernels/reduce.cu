@@ -93,6 +93,37 @@ __device__ __forceinline__ void red_write(const ReduceKArgs& K, const B2xVmProgr
   red_finish(K, Q, K.out, index, v);
 }
 
+// Tail of a split row reduction: this CTA's partials are in memory; it takes a ticket, and whoever draws the last one
+// folds all partials (in index order, so the result does not depend on which CTA that is) and finishes the outputs.
+__device__ __forceinline__ void red_fold_by_last_cta(const ReduceKArgs& K, const B2xVmProgram& Q, uint32_t* smem, int* s_last, uint32_t ident) {
+  if (!(K.S > 1 && K.ticket != nullptr)) return;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) *s_last = (atomicAdd(K.ticket, 1) == (int)gridDim.x - 1) ? 1 : 0;
+  __syncthreads();
+  if (!*s_last) return;
+  __threadfence();
+  const uint32_t* parts = (const uint32_t*)K.out;
+  for (int64_t a = 0; a < K.A; a++) {
+    uint32_t v = ident;
+    for (int64_t i = threadIdx.x; i < K.S; i += 256) v = red_combine(v, __ldcg(parts + a * K.S + i), K.monoid, K.cls);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = red_combine(v, __shfl_xor_sync(0xffffffffu, v, off), K.monoid, K.cls);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      uint32_t t = smem[0];
+#pragma unroll
+      for (int w = 1; w < 8; w++) t = red_combine(t, smem[w], K.monoid, K.cls);
+      ReduceKArgs F = K;
+      F.S = 1;
+      red_finish(F, Q, K.final_out, a, t);
+    }
+  }
+  if (threadIdx.x == 0) { *K.ticket = 0; __threadfence(); }
+}
+
 // Row reduction.  T = threads cooperating on one (row, split) piece: 32 or 256.
 template <int V, int T, int ID, int MC>
 __global__ void __launch_bounds__(256, ID != 0 ? 4 : 1) k_reduce_rows(const __grid_constant__ B2xVmProgram P, const __grid_constant__ ReduceKArgs K,
@@ -195,35 +226,92 @@ __global__ void __launch_bounds__(256, ID != 0 ? 4 : 1) k_reduce_rows(const __gr
       }
     }
   }
-  if (K.S > 1 && K.ticket != nullptr) {
-    // this CTA's partials are in memory: take a ticket; whoever draws the last one folds all partials
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) s_last = (atomicAdd(K.ticket, 1) == (int)gridDim.x - 1) ? 1 : 0;
-    __syncthreads();
-    if (s_last) {
-      __threadfence();
-      const uint32_t* parts = (const uint32_t*)K.out;
-      for (int64_t a = 0; a < K.A; a++) {
-        uint32_t v = ident;
-        for (int64_t i = threadIdx.x; i < K.S; i += 256) v = red_combine(v, __ldcg(parts + a * K.S + i), K.monoid, K.cls);
+  red_fold_by_last_cta(K, Q, smem, &s_last, ident);
+}
+
+// The plainest reductions - sum, sum of squares and maximum of one dense f32 or bf16 tensor, CTA-per-piece - without the
+// fused-elementwise machinery: the loop is eight loads and sixteen arithmetic instructions per trip, which is what lets
+// a 134 MB reduction run at the memory system's speed rather than at the instruction scheduler's.  Same pieces, same
+// tickets and the same fold as k_reduce_rows; ES = bytes per element (4: f32, 2: bf16), SQ = square each element first,
+// MC = 1 sum / 2 maximum (NaN-propagating).
+template <int ES, bool SQ, int MC>
+__global__ void __launch_bounds__(256) k_reduce_rows_direct(const char* __restrict__ base, const __grid_constant__ ReduceKArgs K,
+                                                            const __grid_constant__ B2xVmProgram Q) {
+  __shared__ uint32_t smem[8];
+  __shared__ int s_last;
+  const int64_t n_pieces = K.A * K.S;
+  const uint32_t ident = red_identity(K.monoid, K.cls);
+  auto fold8 = [&](float& t, const uint4& lo, const uint4& hi) {
+    float x[8];
+    if constexpr (ES == 4) {
+      x[0] = u2f(lo.x); x[1] = u2f(lo.y); x[2] = u2f(lo.z); x[3] = u2f(lo.w); x[4] = u2f(hi.x); x[5] = u2f(hi.y); x[6] = u2f(hi.z); x[7] = u2f(hi.w);
+    } else {
+      x[0] = u2f(lo.x << 16); x[1] = u2f(lo.x & 0xffff0000u); x[2] = u2f(lo.y << 16); x[3] = u2f(lo.y & 0xffff0000u);
+      x[4] = u2f(lo.z << 16); x[5] = u2f(lo.z & 0xffff0000u); x[6] = u2f(lo.w << 16); x[7] = u2f(lo.w & 0xffff0000u);
+    }
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) v = red_combine(v, __shfl_xor_sync(0xffffffffu, v, off), K.monoid, K.cls);
-        __syncthreads();
-        if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = v;
-        __syncthreads();
-        if (threadIdx.x == 0) {
-          uint32_t t = smem[0];
+    for (int j = 0; j < 8; j++) {
+      const float v = SQ ? x[j] * x[j] : x[j];      // the product is rounded before it is added, as the program says
+      if constexpr (MC == 1) t = __fadd_rn(t, v); else t = vm_fmax(t, v);
+    }
+  };
+  for (int64_t piece = blockIdx.x; piece < n_pieces; piece += gridDim.x) {
+    const int64_t a = piece / K.S, s = piece % K.S;
+    constexpr int64_t BLOCK = 256 * 8;
+    const int64_t STEP = BLOCK * K.S;
+    const char* row = base + a * K.R * ES;
+    int64_t r = s * BLOCK + (int64_t)threadIdx.x * 8;
+    float tot[4] = {u2f(ident), u2f(ident), u2f(ident), u2f(ident)};
+    for (; r + 3 * STEP < K.R; r += 4 * STEP) {
+      uint4 lo[4], hi[4];
 #pragma unroll
-          for (int w = 1; w < 8; w++) t = red_combine(t, smem[w], K.monoid, K.cls);
-          ReduceKArgs F = K;
-          F.S = 1;
-          red_finish(F, Q, K.final_out, a, t);
-        }
+      for (int u = 0; u < 4; u++) {
+        const uint4* p = (const uint4*)(row + (r + u * STEP) * ES);
+        lo[u] = __ldg(p);
+        if constexpr (ES == 4) hi[u] = __ldg(p + 1); else hi[u] = make_uint4(0, 0, 0, 0);
       }
-      if (threadIdx.x == 0) { *K.ticket = 0; __threadfence(); }
+#pragma unroll
+      for (int u = 0; u < 4; u++) fold8(tot[u], lo[u], hi[u]);
+    }
+    for (; r < K.R; r += STEP) {
+      const uint4* p = (const uint4*)(row + r * ES);
+      uint4 lo = __ldg(p), hi = make_uint4(0, 0, 0, 0);
+      if constexpr (ES == 4) hi = __ldg(p + 1);
+      fold8(tot[0], lo, hi);
+    }
+    uint32_t total = red_combine_t<MC>(red_combine_t<MC>(f2u(tot[0]), f2u(tot[1]), K.monoid, K.cls), red_combine_t<MC>(f2u(tot[2]), f2u(tot[3]), K.monoid, K.cls),
+                                       K.monoid, K.cls);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) total = red_combine_t<MC>(total, __shfl_xor_sync(0xffffffffu, total, off), K.monoid, K.cls);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = total;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      uint32_t t = smem[0];
+#pragma unroll
+      for (int w = 1; w < 8; w++) t = red_combine_t<MC>(t, smem[w], K.monoid, K.cls);
+      red_write(K, Q, piece, t);
     }
   }
+  red_fold_by_last_cta(K, Q, smem, &s_last, ident);
+}
+
+// Which direct kernel, if any, computes this prologue: 0 none, 1 the tensor itself, 2 its square.  The program must be
+// `load T0` or `load T0; save t; mul t` in f32 arithmetic over one dense, 16-byte aligned f32 or bf16 tensor.
+static int direct_kind(const B2xVmProgram& P, const ReduceKArgs& K, int vec) {
+  if (vec != 8 || P.n_tensors != 1 || K.cls != VM_F32 || K.B != 1) return 0;
+  const B2xVmTensor& T = P.tensors[0];
+  if (T.elem != EL_F32 && T.elem != EL_BF16) return 0;
+  const int es = T.elem == EL_F32 ? 4 : 2;
+  const bool dense = (P.n_dims == 1 && T.stride[0] == 1 && P.dim[0] == K.A * K.R) ||
+                     (P.n_dims == 2 && P.dim[1] == K.R && T.stride[1] == 1 && T.stride[0] == K.R);
+  if (!dense || ((uintptr_t)T.ptr & 15) || (K.A > 1 && (K.R * es) % 16 != 0) || K.R % 8 != 0) return 0;
+  auto plain = [](const B2xVmInstr& I) { return I.tc == VM_F32 && I.rnd == VM_RN_NONE; };
+  const B2xVmInstr* c = P.code;
+  if (!(c[0].op == VM_LOAD && c[0].src_kind == VM_SRC_TENSOR && c[0].src_idx == 0 && plain(c[0]))) return 0;
+  if (P.n_instr == 1) return 1;
+  if (P.n_instr == 3 && c[1].op == VM_SAVE && c[2].op == VM_MUL && c[2].src_kind == VM_SRC_TEMP && c[2].src_idx == c[1].aux && plain(c[2])) return 2;
+  return 0;
 }
 
 // Column reduction.  blockDim = (BX, RY) with BX * RY = 256; thread (bx, ry) owns V adjacent columns.
@@ -279,6 +367,20 @@ static int launch_one(const B2xVmProgram& P, ReduceKArgs K, const B2xVmProgram& 
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     dim3 grid((unsigned)blocks), block(256);
+    {
+      const int mc0 = red_combine_class(K.monoid, K.cls);
+      const int dk = (!warp_rows && (mc0 == 1 || mc0 == 2) && vm_static_enabled()) ? direct_kind(P, K, vec) : 0;
+      if (dk) {
+        const char* base = (const char*)P.tensors[0].ptr;
+        const bool f32 = P.tensors[0].elem == EL_F32;
+#define B2X_DIRECT(ES_, SQ_, MC_) k_reduce_rows_direct<ES_, SQ_, MC_><<<grid, block, 0, stream>>>(base, K, Q)
+        if (f32) { if (dk == 2) { if (mc0 == 1) B2X_DIRECT(4, true, 1); else B2X_DIRECT(4, true, 2); } else { if (mc0 == 1) B2X_DIRECT(4, false, 1); else B2X_DIRECT(4, false, 2); } }
+        else { if (dk == 2) { if (mc0 == 1) B2X_DIRECT(2, true, 1); else B2X_DIRECT(2, true, 2); } else { if (mc0 == 1) B2X_DIRECT(2, false, 1); else B2X_DIRECT(2, false, 2); } }
+#undef B2X_DIRECT
+        count_launch();
+        return (int)cudaGetLastError();
+      }
+    }
 #define B2X_ROWS_MC(VV, II, MM)                                                           \
     if (warp_rows) k_reduce_rows<VV, 32, II, MM><<<grid, block, 0, stream>>>(P, K, Q);    \
     else k_reduce_rows<VV, 256, II, MM><<<grid, block, 0, stream>>>(P, K, Q);
@@ -289,7 +391,7 @@ static int launch_one(const B2xVmProgram& P, ReduceKArgs K, const B2xVmProgram& 
     else { B2X_ROWS_MC(VV, II, 0) }
     const int mc = red_combine_class(K.monoid, K.cls);
     if (vec == 8) {
-      switch (vm_static_lookup(vm_signature_hash(P))) {
+      switch (vm_static_enabled() ? vm_static_lookup(vm_signature_hash(P)) : 0) {
 #define X(I) case I: B2X_ROWS(8, I) break;
         B2X_VM_STATIC_REDUCE(X)
 #undef X
