@@ -130,16 +130,20 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   constexpr int BK = 128 / ES;            // elements per 128-byte line: 64 (16-bit) or 32 (tf32)
   constexpr int UMMA_K = 32 / ES;         // 16 or 8
   constexpr int CHUNK = 128 / ES;         // MN-elements per 128-byte line in MN-major layout
-  constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
+  // Accumulators in TMEM: two 256-column ones, or four of 128 / 64 columns.  With four, each of the two epilogue groups
+  // owns a pair (tiles alternate between the groups, accumulators rotate over all four), so on a short-K problem a group
+  // finds its next tile's accumulator already filled instead of waiting for the MMA that its own epilogue just released.
+  constexpr int NACC = BN <= 128 ? 4 : 2;
+  constexpr uint32_t TMEM_COLS = (NACC * BN <= 32) ? 32 : (NACC * BN <= 64 ? 64 : (NACC * BN <= 128 ? 128 : (NACC * BN <= 256 ? 256 : 512)));
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t smem_base = smem_u32(smem);
   uint64_t* bars = (uint64_t*)(smem + SM::BAR_OFFSET);
-  // barrier slots: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], drain, sched_full[4], sched_empty[4]
+  // barrier slots: full[STAGES], empty[STAGES], tmem_full[NACC], tmem_empty[NACC], drain, sched_full[4], sched_empty[4]
   const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * STAGES, bar_tfull = bar_empty + 8 * STAGES,
-                 bar_tempty = bar_tfull + 16, bar_drain = bar_tempty + 16, bar_sfull = bar_drain + 8, bar_sempty = bar_sfull + 32;
-  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 5 + 8);
+                 bar_tempty = bar_tfull + 8 * NACC, bar_drain = bar_tempty + 8 * NACC, bar_sfull = bar_drain + 8, bar_sempty = bar_sfull + 32;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 2 * NACC + 1 + 8);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   // Tiles are handed out dynamically: the producer draws the next tile index from a global counter and publishes it
   // to the other roles through this ring, so a CTA that starts late (its SM was busy with another kernel, e.g. a
@@ -152,7 +156,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-    for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, TC_EPI_WARPS / p.epi_groups); }
+    for (int a = 0; a < NACC; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, TC_EPI_WARPS / p.epi_groups); }
     mbar_init(bar_drain, 1);
     for (int r = 0; r < RING; r++) { mbar_init(bar_sfull + 8 * r, 1); mbar_init(bar_sempty + 8 * r, TC_EPI_WARPS / p.epi_groups + 1); }
     *abort_flag = 0;
@@ -238,8 +242,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         const int32_t t = tile_ring[slot * 4];
         mbar_arrive(bar_sempty + 8 * slot);
         if (t < 0) break;
-        const int acc = (int)(local & 1);
-        const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+        const int acc = (int)(local % NACC);
+        const uint32_t acc_phase = (uint32_t)((local / NACC) & 1);
         if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, status, 2)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
@@ -283,8 +287,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_sempty + 8 * slot);
       if (t < 0) break;
-      const int acc = (int)(local & 1);
-      const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+      const int acc = (int)(local % NACC);
+      const uint32_t acc_phase = (uint32_t)((local / NACC) & 1);
       if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, status, 4)) { ok = false; break; }
       tc_fence_after();
       const int64_t row = (int64_t)m0 + quad * 32 + lane;

@@ -91,6 +91,10 @@ def main():
             key = row["hash"]
             ent = seen.setdefault(key, {"row": row, "roles": set()})
             ent["roles"].add((row["role"], row["bn"]))
+            # a GEMM epilogue is built for both wide tile widths: which one a problem takes depends on its K as well
+            if row["role"] == "gemm_tc" and row["bn"] >= 128:
+                ent["roles"].add((row["role"], 128))
+                ent["roles"].add((row["role"], 256))
     entries = sorted(seen.values(), key=lambda e: (e["row"]["n"], e["row"]["hash"]))
     lines = ["// Specialised fused-elementwise programs.  GENERATED by gen_vm_static.py from the launch plans of the benchmark",
              "// programs; regenerate after changing the planner's code generation.", "#pragma once", "namespace b2x {"]

@@ -854,7 +854,13 @@ static PJRT_Error* build_core(PJRT_Client* client, const std::string& code, cons
   } else {
     if (n > (int)client->devices.size())
       return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "replica_count = " + std::to_string(n) + " but the client has only " + std::to_string(client->devices.size()) + " devices");
-    for (int r = 0; r < n; r++) core->device_assignment.push_back(client->devices[r]->desc.id);
+    // default assignment: replica r on device r; a single-replica program of a process that cannot address device 0
+    // (one process per GPU) runs on that process's own first device
+    for (int r = 0; r < n; r++) {
+      PJRT_Device* d = client->devices[r];
+      if (n == 1 && !d->addressable && !client->addressable_devices.empty()) d = client->addressable_devices[0];
+      core->device_assignment.push_back(d->desc.id);
+    }
   }
   for (int id : core->device_assignment)
     if (id < 0 || id >= (int)client->devices.size()) return make_error(PJRT_Error_Code_INVALID_ARGUMENT, "device assignment names device " + std::to_string(id) + " which does not exist");

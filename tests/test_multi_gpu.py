@@ -125,3 +125,20 @@ def test_two_replica_gradient_step_matches_the_committed_fixture(client):
     for r in range(2):
         for k, (g, w) in enumerate(zip(got[r], outs[r])):
             assert_close(g, w, f"c5 fixture replica {r} output {k}")
+
+
+@needs2
+def test_reference_collective_examples_with_i64_as_written(client):
+    """The reference's worked examples of all_reduce and all_gather with the element type they are written in
+    (i64, crates/ryft-mlir/src/dialects/stable_hlo/operations/communication.rs:821-841 and :722-739)."""
+    b = Builder()
+    x = b.arg([4], "i64"); y = b.arg([4], "i64"); g = b.arg([2, 2], "i64")
+    r0, r1 = b.all_reduce([x, y], [[0, 1]])
+    text = b.build(r0, r1, b.all_gather(g, 1, [[0, 1]]))
+    reps = [[np.array([1, 2, 3, 4], np.int64), np.array([9, 10, 11, 12], np.int64), np.array([[1, 2], [3, 4]], np.int64)],
+            [np.array([5, 6, 7, 8], np.int64), np.array([13, 14, 15, 16], np.int64), np.array([[5, 6], [7, 8]], np.int64)]]
+    _, outs = run_replicated(client, text, reps)
+    for r in range(2):
+        assert outs[r][0].dtype == np.int64
+        assert outs[r][0].tolist() == [6, 8, 10, 12] and outs[r][1].tolist() == [22, 24, 26, 28]
+        assert outs[r][2].tolist() == [[1, 2, 5, 6], [3, 4, 7, 8]]
