@@ -146,10 +146,6 @@ static int tc_route(const B2xGemmArgs* a, const B2xVmProgram* epilogue, TcRoute*
     const int64_t m_tiles = (a->M + TC_BM - 1) / TC_BM;
     while (BN > 64 && m_tiles * ((a->N + BN - 1) / BN) * a->batch < kNumSms / 2) BN /= 2;
   }
-  // A short-K problem (a tile's main loop is a few k-blocks) is bound by its epilogue: 128-column tiles give the kernel
-  // four accumulators, a pair for each of the two epilogue groups, so that neither group waits for an MMA.
-  const int k_blocks = (int)((a->K + BK - 1) / BK);
-  if (k_blocks <= 8 && BN == 256) BN = 128;
   r->BN = BN;
   TcParams& p = r->p;
   p.batch = a->batch; p.M = a->M; p.N = a->N; p.K = a->K;
@@ -160,7 +156,7 @@ static int tc_route(const B2xGemmArgs* a, const B2xVmProgram* epilogue, TcRoute*
   if (p.num_tiles >= (1ll << 31)) return (int)cudaErrorInvalidValue;
   p.k_blocks = (int)((a->K + BK - 1) / BK);
   p.transposed = a->K <= 8192 ? 1 : 0;
-  p.epi_groups = (p.k_blocks <= 8 && BN > 128) ? 1 : 2;
+  p.epi_groups = p.k_blocks <= 8 ? 1 : 2;
   {
     // A slab of a group ~ 32 MiB (a quarter of the 126 MB L2)
     const int64_t slab_per_m_tile = (int64_t)TC_BM * a->K * es;

@@ -130,10 +130,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   constexpr int BK = 128 / ES;            // elements per 128-byte line: 64 (16-bit) or 32 (tf32)
   constexpr int UMMA_K = 32 / ES;         // 16 or 8
   constexpr int CHUNK = 128 / ES;         // MN-elements per 128-byte line in MN-major layout
-  // Accumulators in TMEM: two 256-column ones, or four of 128 / 64 columns.  With four, each of the two epilogue groups
-  // owns a pair (tiles alternate between the groups, accumulators rotate over all four), so on a short-K problem a group
-  // finds its next tile's accumulator already filled instead of waiting for the MMA that its own epilogue just released.
-  constexpr int NACC = BN <= 128 ? 4 : 2;
+  // Accumulators in TMEM.  Four 128-column accumulators (a pair for each of two epilogue groups, 128-wide tiles on
+  // short-K problems) were measured on config 2: 107 us against 92 us with two 256-column ones and one group, so two it is.
+  constexpr int NACC = 2;
   constexpr uint32_t TMEM_COLS = (NACC * BN <= 32) ? 32 : (NACC * BN <= 64 ? 64 : (NACC * BN <= 128 ? 128 : (NACC * BN <= 256 ? 256 : 512)));
 
   extern __shared__ uint8_t smem_raw[];
