@@ -843,6 +843,12 @@ typedef struct {
   const double* flops;        /* out: algorithmic FLOPs of one launch of the step */
   const double* bytes;        /* out: algorithmic bytes of one launch of the step */
   const int* kernel_launches; /* out: kernels this library launches per step (0 for NCCL collectives and copies) */
+  /* Read only when struct_size covers them.  replay > 0: enqueue the plan `replay` more times back to back with the
+   * arguments and outputs of the device's last recorded execution (recording must be enabled when that execution is
+   * launched, and the caller keeps its buffers alive), one pair of CUDA events around all of them: the device time of
+   * the kernels without the host work of an execution between launches.  Refused for plans with collectives. */
+  int replay;                 /* in */
+  float replay_ms;            /* out: device milliseconds of all `replay` repetitions together */
 } B2X_StepTiming_Args;
 typedef struct B2X_StepTiming_Extension {
   PJRT_Extension_Base base;

@@ -47,7 +47,7 @@ PJRT_Error* run_plan(PJRT_LoadedExecutable* le, int local_index, int replica, co
   B2xVmProgram prog;
   std::vector<int> outstanding;
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>>* timed = nullptr;
-  if (pd.timing) { pd.timed.emplace_back(); timed = &pd.timed.back(); }
+  if (pd.timing) { pd.timed.emplace_back(); timed = &pd.timed.back(); pd.last_args = args; pd.last_outs = outs; }
   for (const Step& s : plan.steps) {
     for (int w : s.wait_colls) B2X_CUDA(cudaStreamWaitEvent(cs, pd.coll_done[w], 0));
     const bool on_comm = s.kind == StepKind::ALL_REDUCE || s.kind == StepKind::ALL_GATHER;

@@ -174,6 +174,7 @@ struct PJRT_LoadedExecutable {
     bool timing = false;
     std::vector<std::vector<std::pair<cudaEvent_t, cudaEvent_t>>> timed;  // [execution][step]
     std::vector<float> step_ms;
+    std::vector<void*> last_args, last_outs;   // of the last execution launched while timing was on (for replay)
   };
   std::vector<std::string> step_labels;
   std::vector<const char*> step_label_ptrs;

@@ -1339,6 +1339,30 @@ static PJRT_Error* Ext_StepTiming(B2X_StepTiming_Args* a) {
     pd.timed.clear();
   }
   a->step_ms = pd.step_ms.data();
+  if (a->struct_size >= offsetof(B2X_StepTiming_Args, replay_ms) + sizeof(float) && a->replay > 0) {
+    a->replay_ms = 0.f;
+    B2X_CHECK_ARG(plan.num_collectives == 0, "replay is for plans without collectives");
+    B2X_CHECK_ARG(!pd.last_outs.empty() || !pd.last_args.empty(), "replay needs an execution launched while step timing was enabled");
+    PJRT_Device* dev = le->addressable[a->device_index];
+    std::lock_guard<std::mutex> dl(dev->launch_mu);
+    B2X_CUDA(cudaSetDevice(dev->cuda_ordinal));
+    const bool was = pd.timing;
+    pd.timing = false;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    B2X_CUDA(cudaEventCreate(&e0));
+    B2X_CUDA(cudaEventCreate(&e1));
+    PJRT_Error* err = nullptr;
+    cudaEventRecord(e0, dev->compute);
+    for (int i = 0; i < a->replay && !err; i++) err = run_plan(le, (int)a->device_index, le->logical_ids[a->device_index].replica, pd.last_args, pd.last_outs);
+    cudaEventRecord(e1, dev->compute);
+    cudaError_t e = cudaEventSynchronize(e1);
+    if (e == cudaSuccess && !err) e = cudaEventElapsedTime(&a->replay_ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    pd.timing = was;
+    if (err) return err;
+    if (e != cudaSuccess) return cuda_error(e, "timing the replayed plan");
+  }
   return nullptr;
 }
 

@@ -96,7 +96,7 @@ class _WaitStreamArgs(C.Structure):
 class _StepTimingArgs(C.Structure):
     _fields_ = [("struct_size", _sz), ("executable", _vp), ("device_index", _sz), ("enable", _i), ("collect", _i), ("num_steps", _sz),
                 ("num_executions", _sz), ("step_ms", C.POINTER(C.c_float)), ("labels", C.POINTER(C.c_char_p)), ("flops", C.POINTER(C.c_double)),
-                ("bytes", C.POINTER(C.c_double)), ("kernel_launches", C.POINTER(_i))]
+                ("bytes", C.POINTER(C.c_double)), ("kernel_launches", C.POINTER(_i)), ("replay", _i), ("replay_ms", C.c_float)]
 
 
 class _NamedValueUnion(C.Union):
@@ -817,20 +817,30 @@ class LoadedExecutable:
         """Step-timing extension of this plugin: per plan step, the label, algorithmic flops and bytes per launch,
         kernels launched per step and (when `collect`) the device milliseconds summed over the executions recorded
         since timing was enabled."""
-        ext = self.api.extension(EXTENSION_TYPE_STEP_TIMING)
-        if not ext:
-            raise PjrtError(12, "the plugin has no step-timing extension")
-        fn = C.c_void_p.from_address(ext + 24).value
-        a = _StepTimingArgs(); a.struct_size = C.sizeof(a); a.executable = self.handle; a.device_index = device_index
-        a.enable = enable; a.collect = 1 if collect else 0
-        err = _FN(fn)(C.addressof(a))
-        if err:
-            raise self.api._take_error(err)
+        a = self._step_timing_call(enable, collect, device_index, 0)
         out = []
         for i in range(a.num_steps):
             out.append({"label": a.labels[i].decode(), "flops": a.flops[i], "bytes": a.bytes[i], "kernel_launches": a.kernel_launches[i],
                         "ms": a.step_ms[i], "executions": int(a.num_executions)})
         return out
+
+    def replay(self, times: int, device_index: int = 0) -> float:
+        """Enqueues the plan `times` more times back to back with the arguments and outputs of the last execution that was
+        launched while step timing was enabled (the caller keeps those buffers alive) and returns the device milliseconds
+        of all repetitions together: the kernels' own time, without the host work of an execution between launches."""
+        return float(self._step_timing_call(-1, False, device_index, times).replay_ms)
+
+    def _step_timing_call(self, enable: int, collect: bool, device_index: int, replay: int) -> "_StepTimingArgs":
+        ext = self.api.extension(EXTENSION_TYPE_STEP_TIMING)
+        if not ext:
+            raise PjrtError(12, "the plugin has no step-timing extension")
+        fn = C.c_void_p.from_address(ext + 24).value
+        a = _StepTimingArgs(); a.struct_size = C.sizeof(a); a.executable = self.handle; a.device_index = device_index
+        a.enable = enable; a.collect = 1 if collect else 0; a.replay = replay
+        err = _FN(fn)(C.addressof(a))
+        if err:
+            raise self.api._take_error(err)
+        return a
 
     def delete(self) -> None:
         a = A["LoadedExecutable_Delete"](); a.executable = self.handle
