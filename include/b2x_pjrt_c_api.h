@@ -849,6 +849,7 @@ typedef struct {
    * the kernels without the host work of an execution between launches.  Refused for plans with collectives. */
   int replay;                 /* in */
   float replay_ms;            /* out: device milliseconds of all `replay` repetitions together */
+  float replay_host_ms;       /* out: host milliseconds spent enqueueing them (close to replay_ms = the host was the limit) */
 } B2X_StepTiming_Args;
 typedef struct B2X_StepTiming_Extension {
   PJRT_Extension_Base base;

@@ -1339,8 +1339,9 @@ static PJRT_Error* Ext_StepTiming(B2X_StepTiming_Args* a) {
     pd.timed.clear();
   }
   a->step_ms = pd.step_ms.data();
-  if (a->struct_size >= offsetof(B2X_StepTiming_Args, replay_ms) + sizeof(float) && a->replay > 0) {
+  if (a->struct_size >= offsetof(B2X_StepTiming_Args, replay_host_ms) + sizeof(float) && a->replay > 0) {
     a->replay_ms = 0.f;
+    a->replay_host_ms = 0.f;
     B2X_CHECK_ARG(plan.num_collectives == 0, "replay is for plans without collectives");
     B2X_CHECK_ARG(!pd.last_outs.empty() || !pd.last_args.empty(), "replay needs an execution launched while step timing was enabled");
     PJRT_Device* dev = le->addressable[a->device_index];
@@ -1353,7 +1354,9 @@ static PJRT_Error* Ext_StepTiming(B2X_StepTiming_Args* a) {
     B2X_CUDA(cudaEventCreate(&e1));
     PJRT_Error* err = nullptr;
     cudaEventRecord(e0, dev->compute);
+    const auto h0 = std::chrono::steady_clock::now();
     for (int i = 0; i < a->replay && !err; i++) err = run_plan(le, (int)a->device_index, le->logical_ids[a->device_index].replica, pd.last_args, pd.last_outs);
+    a->replay_host_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - h0).count();
     cudaEventRecord(e1, dev->compute);
     cudaError_t e = cudaEventSynchronize(e1);
     if (e == cudaSuccess && !err) e = cudaEventElapsedTime(&a->replay_ms, e0, e1);

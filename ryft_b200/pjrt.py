@@ -96,7 +96,7 @@ class _WaitStreamArgs(C.Structure):
 class _StepTimingArgs(C.Structure):
     _fields_ = [("struct_size", _sz), ("executable", _vp), ("device_index", _sz), ("enable", _i), ("collect", _i), ("num_steps", _sz),
                 ("num_executions", _sz), ("step_ms", C.POINTER(C.c_float)), ("labels", C.POINTER(C.c_char_p)), ("flops", C.POINTER(C.c_double)),
-                ("bytes", C.POINTER(C.c_double)), ("kernel_launches", C.POINTER(_i)), ("replay", _i), ("replay_ms", C.c_float)]
+                ("bytes", C.POINTER(C.c_double)), ("kernel_launches", C.POINTER(_i)), ("replay", _i), ("replay_ms", C.c_float), ("replay_host_ms", C.c_float)]
 
 
 class _NamedValueUnion(C.Union):
@@ -828,7 +828,9 @@ class LoadedExecutable:
         """Enqueues the plan `times` more times back to back with the arguments and outputs of the last execution that was
         launched while step timing was enabled (the caller keeps those buffers alive) and returns the device milliseconds
         of all repetitions together: the kernels' own time, without the host work of an execution between launches."""
-        return float(self._step_timing_call(-1, False, device_index, times).replay_ms)
+        a = self._step_timing_call(-1, False, device_index, times)
+        self.last_replay_host_ms = float(a.replay_host_ms)   # close to the device time: the host's enqueue rate was the limit
+        return float(a.replay_ms)
 
     def _step_timing_call(self, enable: int, collect: bool, device_index: int, replay: int) -> "_StepTimingArgs":
         ext = self.api.extension(EXTENSION_TYPE_STEP_TIMING)

@@ -254,6 +254,26 @@ module {
     assert np.array_equal(out, 2 * x)
 
 
+def test_step_timing_extension_records_steps_and_replays_the_last_execution(client):
+    """The plugin's private step-timing extension: per-step device times of recorded executions, and `replay`, which
+    enqueues the plan again with the last recorded execution's buffers (the results must come out the same)."""
+    exe = client.compile(pjrt.Program.mlir(ADD_PROGRAM), pjrt.CompilationOptions())
+    device = exe.addressable_devices()[0]
+    lhs = client.buffer(np.array([7, -1], np.int32).tobytes(), pjrt.BufferType.S32, [2, 1], device)
+    rhs = client.buffer(np.array([35, -41], np.int32).tobytes(), pjrt.BufferType.S32, [2, 1], device)
+    with pytest.raises(pjrt.PjrtError, match="replay needs an execution"):
+        exe.replay(2)
+    exe.step_timing(enable=1)
+    outs = exe.execute([pjrt.ExecutionDeviceInputs([lhs, rhs])])
+    outs[0].done.await_()
+    steps = exe.step_timing(enable=0, collect=True)
+    assert len(steps) == 1 and steps[0]["label"].startswith("elementwise") and steps[0]["executions"] == 1 and steps[0]["ms"] > 0
+    assert steps[0]["kernel_launches"] == 1
+    ms = exe.replay(5)
+    assert 0 < ms < 100
+    assert outs[0].outputs[0].copy_to_host().await_() == np.array([42, -42], np.int32).tobytes()
+
+
 def test_layouts_extension_on_executables_and_buffers(client):
     """crates/ryft-pjrt/src/extensions/layouts.rs:944-990: both inputs and the output of the i32 add program have
     layout "{1,0}"; a buffer reports the same layout as the client's default for its shape."""
