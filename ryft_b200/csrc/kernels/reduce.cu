@@ -64,6 +64,14 @@ struct ReduceKArgs {
   void* final_out;
   int32_t* ticket;     // CTAs that have written their partials; the last one resets it
   int32_t has_post;    // the final value goes to the consumer program Q instead of (or besides) `final_out`
+  // The consumer program digested on the host when it is `load acc0; <up to four of mul/add/sub/div by an immediate>;
+  // store T0` in f32 (the mean of a loss, a scaled norm): post_n >= 0, and the kernel applies it inline instead of
+  // starting the interpreter for one value (2.4 us on the one thread the whole launch waits for).
+  int32_t post_n;
+  uint8_t post_op[4];
+  uint32_t post_imm[4];
+  float* post_dst;
+  int64_t post_stride;
 };
 
 // Hands one finished output to the fused consumer program: element `index` of the result, value in ACC0.
@@ -83,7 +91,22 @@ __device__ __forceinline__ void red_finish(const ReduceKArgs& K, const B2xVmProg
   }
   v = red_combine(init, v, K.monoid, K.cls);
   uint32_t enc = vm_encode(v, (uint8_t)K.out_elem);
-  if (K.has_post) { red_post(Q, index, vm_decode(enc, (uint8_t)K.out_elem)); return; }
+  if (K.has_post) {
+    const uint32_t dv = vm_decode(enc, (uint8_t)K.out_elem);
+    if (K.post_n < 0) { red_post(Q, index, dv); return; }
+    float f = u2f(dv);
+    for (int i = 0; i < K.post_n; i++) {
+      const float y = u2f(K.post_imm[i]);
+      switch (K.post_op[i]) {
+        case VM_MUL: f = __fmul_rn(f, y); break;
+        case VM_ADD: f = __fadd_rn(f, y); break;
+        case VM_SUB: f = __fsub_rn(f, y); break;
+        default: f = __fdiv_rn(f, y); break;
+      }
+    }
+    K.post_dst[index * K.post_stride] = f;
+    return;
+  }
   const int es = vm_elem_size((uint8_t)K.out_elem);
   if (es == 4) ((uint32_t*)dst)[index] = enc; else if (es == 2) ((uint16_t*)dst)[index] = (uint16_t)enc; else ((uint8_t*)dst)[index] = (uint8_t)enc;
 }
@@ -124,9 +147,7 @@ __device__ __forceinline__ void red_fold_by_last_cta(const ReduceKArgs& K, const
       uint32_t t = smem[0];
 #pragma unroll
       for (int w = 1; w < 8; w++) t = red_combine(t, smem[w], K.monoid, K.cls);
-      ReduceKArgs F = K;
-      F.S = 1;
-      red_finish(F, Q, K.final_out, a, t);
+      red_finish(K, Q, K.final_out, a, t);
     }
   }
   if (threadIdx.x == 0) { *K.ticket = 0; __threadfence(); }
@@ -488,6 +509,24 @@ extern "C" int b2x_launch_reduce(const B2xVmProgram* prologue, const B2xReduceAr
   K.out_elem = a->out_elem; K.init_elem = a->init_elem;
   K.init_imm = a->init_imm; K.init_ptr = a->init_ptr;
   K.has_post = a->host_post != nullptr ? 1 : 0;
+  K.post_n = -1;
+  if (a->host_post && a->cls == VM_F32 && a->out_elem == EL_F32) {
+    const B2xVmProgram& q = *a->host_post;
+    const int n = q.n_instr;
+    bool simple = n >= 2 && n <= 6 && q.n_tensors == 1 && q.n_dims == 1 && q.tensors[0].elem == EL_F32 && q.code[0].op == VM_LOAD &&
+                  q.code[0].src_kind == VM_SRC_ACC0 && q.code[n - 1].op == VM_STORE && q.code[n - 1].src_kind == VM_SRC_TENSOR &&
+                  q.code[n - 1].src_idx == 0 && q.code[n - 1].rnd == VM_RN_NONE;
+    for (int i = 1; simple && i < n - 1; i++) {
+      const B2xVmInstr& I = q.code[i];
+      simple = (I.op == VM_MUL || I.op == VM_ADD || I.op == VM_SUB || I.op == VM_DIV) && I.src_kind == VM_SRC_IMM && I.tc == VM_F32 && I.rnd == VM_RN_NONE;
+    }
+    if (simple) {
+      K.post_n = n - 2;
+      for (int i = 1; i < n - 1; i++) { K.post_op[i - 1] = q.code[i].op; K.post_imm[i - 1] = q.code[i].imm; }
+      K.post_dst = (float*)q.tensors[0].ptr;
+      K.post_stride = q.tensors[0].stride[0];
+    }
+  }
   static const B2xVmProgram kNoPost{};
   const B2xVmProgram& Q = a->host_post ? *a->host_post : kNoPost;
   if (S <= 1 || a->R == 0) {
