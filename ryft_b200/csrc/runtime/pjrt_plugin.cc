@@ -1216,21 +1216,28 @@ static PJRT_Error* LoadedExecutable_Execute(PJRT_LoadedExecutable_Execute_Args* 
         ob->pjrt_type = to_pjrt_type(ob->type.dtype); ob->owns = false;
       }
       if (failed) { ob->err_code = L.err->code; ob->err_msg = L.err->message; }
-      else { cudaEventCreateWithFlags(&ob->ready, cudaEventDisableTiming); cudaEventRecord(ob->ready, done_stream); }
+      else {
+        // an output that no detached collective writes is final when the compute stream gets here (a loss can be read back
+        // while the gradients' all-reduce is still running behind the next step)
+        const bool on_comm = done_stream != dev->compute && (o >= plan0.out_in_detached.size() || plan0.out_in_detached[o]);
+        cudaEventCreateWithFlags(&ob->ready, cudaEventDisableTiming);
+        cudaEventRecord(ob->ready, on_comm ? done_stream : dev->compute);
+      }
       if (a->output_lists && a->output_lists[k]) a->output_lists[k][o] = ob;
     }
     // Inputs are read by the enqueued kernels: their memory must not be reused before those finish.  Memory the plugin
     // owns is freed in compute-stream order, which covers every reader on that stream; a view of foreign memory needs
-    // an event, and so does any argument of a plan with detached collectives, because those read on the communication
-    // stream, which the compute stream never waits for.
+    // an event, and so does an argument that a detached collective reads or writes, because that happens on the
+    // communication stream, which the compute stream never waits for.  (Only those: freeing a buffer with such an event
+    // makes the compute stream wait for the collective, which then no longer runs behind the next step.)
     if (!failed) {
-      const bool comm_readers = done_stream != dev->compute;
       for (size_t i = 0; i < n_args; i++) {
         PJRT_Buffer* b = a->argument_lists[k][i];
+        const bool comm_readers = done_stream != dev->compute && (i >= plan0.arg_in_detached.size() || plan0.arg_in_detached[i]);
         if (!b->owns || comm_readers) {
           cudaEvent_t keep;
           cudaEventCreateWithFlags(&keep, cudaEventDisableTiming);
-          cudaEventRecord(keep, done_stream);
+          cudaEventRecord(keep, comm_readers ? done_stream : dev->compute);
           std::lock_guard<std::mutex> bl(b->mu);
           // a buffer that is an argument step after step would otherwise collect one event per execution
           size_t kept = 0;

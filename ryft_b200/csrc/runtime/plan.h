@@ -110,6 +110,9 @@ struct Plan {
   int64_t arena_bytes = 0;
   int num_collectives = 0;
   bool has_detached_collectives = false;
+  // which arguments a detached collective reads or writes, and which outputs it writes: only those have a reader or
+  // writer on the communication stream after the compute stream has finished with the execution
+  std::vector<char> arg_in_detached, out_in_detached;
   std::vector<uint8_t> const_pool;
   double total_flops = 0, total_bytes = 0;
   int num_replicas = 1, num_partitions = 1;

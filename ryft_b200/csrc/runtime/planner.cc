@@ -1662,6 +1662,16 @@ void Planner::schedule_collectives() {
       if (!arena) { out[i].coll_detached = true; plan_.has_detached_collectives = true; }
     }
   }
+  plan_.arg_in_detached.assign(plan_.arg_types.size(), 0);
+  plan_.out_in_detached.assign(plan_.outputs.size(), 0);
+  for (auto& s : out) {
+    if (!s.coll_detached) continue;
+    for (auto& c : s.colls)
+      for (const BufRef* b : {&c.src, &c.dst}) {
+        if (b->kind == BufRef::ARG && (size_t)b->index < plan_.arg_in_detached.size()) plan_.arg_in_detached[b->index] = 1;
+        if (b->kind == BufRef::OUT && (size_t)b->index < plan_.out_in_detached.size()) plan_.out_in_detached[b->index] = 1;
+      }
+  }
   plan_.steps = std::move(out);
 }
 
