@@ -362,6 +362,7 @@ def run_own(args) -> dict:
             return client.buffer(pinned.data_ptr(), pjrt.BufferType.BF16, list(x.shape), device=dev, semantics=1)
 
         host = {"upload": 0.0, "execute": 0.0, "readback": 0.0, "wait": 0.0}
+        upload_each = []   # host milliseconds of every upload call of the timed loop (a slow one = the pool had to grow)
 
         def run_steps(n):
             # the input pipeline of a training loop: step i+1's tokens are uploaded while step i computes, and with
@@ -370,6 +371,7 @@ def run_own(args) -> dict:
             # enqueue calls cost (upload, execute, readback) and how long the host then sat waiting for the device.
             for k in host:
                 host[k] = 0.0
+            del upload_each[:]
             c = time.perf_counter
             xb = upload()
             pending = None
@@ -391,10 +393,12 @@ def run_own(args) -> dict:
                     pending = ev
                 t4 = c()
                 host["execute"] += t1 - t0; host["upload"] += t2 - t1; host["readback"] += t3 - t2; host["wait"] += t4 - t3
+                upload_each.append(round((t2 - t1) * 1e3, 3))
             if pending is not None:
                 pending.await_()
             loss_host[:] = hosts[(n - 1) & 1]
-        run_steps(2)
+        # enough untimed steps for the stream-ordered memory pool to hold every token buffer the pipelined loop keeps alive
+        run_steps(max(args.warmup, 4))
         # the upload alone, for reading the end-to-end figure: when it takes longer than a step, the host link bounds e2e
         t_up = time.perf_counter()
         upload().ready().await_()
@@ -407,7 +411,7 @@ def run_own(args) -> dict:
         e2e = {"value": flops_per_replica * n_rep * e2e_steps / wall / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": int(x.nbytes) * n_rep,
                "d2h_bytes_per_step": 4 * n_rep, "ms_per_step": wall / e2e_steps * 1e3, "loss": float(loss_host.view(np.float32)[0]),
                "h2d_alone_ms": h2d_ms, "h2d_alone_gb_per_s": x.nbytes / (h2d_ms * 1e-3) / 1e9,
-               "host_ms_per_step": {k: v / e2e_steps * 1e3 for k, v in host.items()},
+               "host_ms_per_step": {k: v / e2e_steps * 1e3 for k, v in host.items()}, "upload_call_ms_each": list(upload_each),
                "results_left_on_device": "dW1 and dW2 (512 MiB of f32 gradients) stay in HBM for the optimiser; only the loss is read back"}
 
     # ---- roofline of the dominant kernel (tcgen05 GEMM) from the per-step CUDA events of the timed region ----

@@ -49,6 +49,33 @@ def test_reference_all_reduce_example_two_replicas(client):
 
 
 @needs2
+def test_arguments_of_a_detached_all_reduce_outlive_their_handles(client):
+    """An all-reduce that nothing in the program waits for runs on the communication stream after the execute call has
+    returned.  Its operands are the caller's argument buffers: destroying them right away, and allocating new buffers of
+    the same size over them, must not disturb the collective (the plugin orders the free behind it)."""
+    b = Builder()
+    x = b.arg([16 * 1024 * 1024], "f32")
+    (r,) = b.all_reduce([x], [[0, 1]])
+    text = b.build(r)
+    exe = client.compile(pjrt.Program.mlir(text), pjrt.CompilationOptions(replica_count=2))
+    devs = exe.addressable_devices()
+    rng = np.random.default_rng(5)
+    data = [rng.standard_normal(16 * 1024 * 1024).astype(np.float32) for _ in range(2)]
+    want = data[0] + data[1]
+    for _ in range(3):
+        bufs = [client.buffer(data[i], device=devs[i]) for i in range(2)]
+        outs = exe.execute([pjrt.ExecutionDeviceInputs([bufs[0]]), pjrt.ExecutionDeviceInputs([bufs[1]])])
+        for x_ in bufs:
+            x_.delete()
+        del bufs
+        junk = [client.buffer(np.full(16 * 1024 * 1024, 7.0, np.float32), device=devs[i]) for i in range(2)]
+        for o in outs:
+            o.done.await_()
+            assert np.array_equal(o.outputs[0].to_numpy(), want)
+        del junk
+
+
+@needs2
 def test_reference_all_gather_example_two_replicas(client):
     # communication.rs:722-739 (i32): gather along dim 1
     b = Builder()
