@@ -162,9 +162,9 @@ NCU_TRAFFIC_BYTES_PER_LAUNCH = {
     "c5": 1.36e9,      # (1.35 + 1.60 + 1.49 + 1.10 + 1.27) GB / 5
     "c4": 1.36e9,
     "c2": 249.0e6,
-    "c3": 519.1e6,
+    "c3": 519.1e6,     # k_attention_pw: 403.1 MB read + 115.9 MB written
     "ew": 771.0e6,
-    "red": 139.1e6,
+    "red": 138.7e6,    # 134.3 MB read + 4.4 MB written
 }
 
 
