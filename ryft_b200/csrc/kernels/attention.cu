@@ -5,7 +5,11 @@
 // (builders: crates/ryft-mlir/src/dialects/stable_hlo/operations/linear_algebra.rs:756-797, functional.rs:188-219,
 // comparison.rs:136-164, control_flow.rs:263) and replaces it with this kernel; no score tensor touches HBM.
 //
-// One CTA per (batch*head, 128-row query tile); the tiles of one head are adjacent in the grid (K/V reuse in L2),
+// Two kernels live here.  k_attention_pw (further down; the default) is persistent: one CTA per SM, two workers per CTA,
+// each walking whole query tiles.  k_attention, described next, is the earlier one-tile-per-CTA form, kept as the
+// fallback and for comparison (B2X_ATTENTION_KERNEL=tile).
+//
+// k_attention: one CTA per (batch*head, 128-row query tile); the tiles of one head are adjacent in the grid (K/V reuse in L2),
 // longest causal prefix first.  The key blocks of a tile (128 keys each) are dealt alternately to two independent
 // softmax streams: stream s owns blocks j = s, s + 2, ..., its own score buffer, probability buffer, K/V stage and
 // output accumulator, and keeps its own running (max, sum).  While one stream exponentiates, the tensor pipe works
@@ -13,10 +17,9 @@
 //   warp 0      TMA producer: Q once, then K_j and V_j into stage j & 1 as soon as that stage's previous K (after its
 //               Q K^T retired) or V (after its P V retired) is free; each CTA loads its own tiles
 //   warps 1,2   MMA issuers, one per stream: S_s = Q K_j^T into TMEM score buffer s, O_s += P_s V_j into accumulator s
-//   warps 3..   softmax, 4 * TPR warps per stream.  TPR = 2 (the default): two threads share a query row, each owns 64
-//               of the block's 128 keys, so that four softmax warps per scheduler hide each other's latencies (with one
-//               thread per row there are two, and the exponential phase runs at a third of the special-function
-//               pipe's rate).  A thread reads all 128 scores of its row from TMEM for the row maximum (both threads of
+//   warps 3..   softmax, 4 * TPR warps per stream.  TPR = 1 (the default): one thread per query row.  TPR = 2: two threads
+//               share a query row, each owns 64 of the block's 128 keys (four softmax warps per scheduler instead of
+//               two; measured slower).  With TPR = 2 a thread reads all 128 scores of its row from TMEM for the row maximum (both threads of
 //               a row thus hold the same maximum without talking to each other) and keeps its own 64 in registers:
 //               exp2, partial row sum, P as bf16 into 128-byte-swizzled shared memory for the second MMA.  The
 //               accumulator is rescaled only when the running max grew by more than 2^8 (exact: the same stale max is
