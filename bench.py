@@ -355,7 +355,7 @@ def run_own(args) -> dict:
         pinned = torch.empty(x.size, dtype=torch.uint16).pin_memory()
         pinned.numpy()[:] = x.reshape(-1).view(np.uint16)
         loss_host = np.zeros(4, dtype=np.uint8)
-        e2e_steps = max(3, min(args.steps, 10))
+        e2e_steps = max(3, min(args.steps, 20))
 
         def upload():
             # asynchronous copy from pinned host memory on the plugin's transfer stream (ImmutableUntilTransferCompletes)
