@@ -153,6 +153,64 @@ __device__ __forceinline__ void red_fold_by_last_cta(const ReduceKArgs& K, const
   if (threadIdx.x == 0) { *K.ticket = 0; __threadfence(); }
 }
 
+// The same tail for the direct kernels (f32 sum or maximum, partials written by thread 0 only): the combine is fixed at
+// compile time, only the writer fences before it takes the ticket, and a plain f32 result without an init tensor or an
+// interpreted consumer is finished without the generic encode / decode path.
+template <int MC>
+__device__ __forceinline__ void red_fold_direct(const ReduceKArgs& K, const B2xVmProgram& Q, uint32_t* smem, int* s_last, uint32_t ident) {
+  if (!(K.S > 1 && K.ticket != nullptr)) return;
+  if (threadIdx.x == 0) {
+    __threadfence();                      // release: this CTA's partials before its ticket
+    const bool last = atomicAdd(K.ticket, 1) == (int)gridDim.x - 1;
+    if (last) __threadfence();            // acquire: every other CTA's partials after their tickets
+    *s_last = last ? 1 : 0;
+  }
+  __syncthreads();
+  if (!*s_last) return;
+  // the partials are read through L2 (ld.cg); the barrier above orders these reads behind thread 0's fence
+  const uint32_t* parts = (const uint32_t*)K.out;
+  for (int64_t a = 0; a < K.A; a++) {
+    uint32_t v = ident;
+    for (int64_t i0 = threadIdx.x; i0 < K.S; i0 += 1024) {
+      uint32_t x[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) x[u] = i0 + u * 256 < K.S ? __ldcg(parts + a * K.S + i0 + u * 256) : ident;
+#pragma unroll
+      for (int u = 0; u < 4; u++) v = red_combine_t<MC>(v, x[u], K.monoid, K.cls);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = red_combine_t<MC>(v, __shfl_xor_sync(0xffffffffu, v, off), K.monoid, K.cls);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      uint32_t t = smem[0];
+#pragma unroll
+      for (int w = 1; w < 8; w++) t = red_combine_t<MC>(t, smem[w], K.monoid, K.cls);
+      if (K.init_ptr == nullptr && K.out_elem == EL_F32 && K.init_elem == EL_F32 && (!K.has_post || K.post_n >= 0)) {
+        float f = u2f(red_combine_t<MC>(K.init_imm, t, K.monoid, K.cls));
+        if (K.has_post) {
+          for (int i = 0; i < K.post_n; i++) {
+            const float y = u2f(K.post_imm[i]);
+            switch (K.post_op[i]) {
+              case VM_MUL: f = __fmul_rn(f, y); break;
+              case VM_ADD: f = __fadd_rn(f, y); break;
+              case VM_SUB: f = __fsub_rn(f, y); break;
+              default: f = __fdiv_rn(f, y); break;
+            }
+          }
+          K.post_dst[a * K.post_stride] = f;
+        } else {
+          ((float*)K.final_out)[a] = f;
+        }
+      } else {
+        red_finish(K, Q, K.final_out, a, t);
+      }
+    }
+  }
+  if (threadIdx.x == 0) { *K.ticket = 0; __threadfence(); }
+}
+
 // Row reduction.  T = threads cooperating on one (row, split) piece: 32 or 256.
 template <int V, int T, int ID, int MC>
 __global__ void __launch_bounds__(256, ID != 0 ? 4 : 1) k_reduce_rows(const __grid_constant__ B2xVmProgram P, const __grid_constant__ ReduceKArgs K,
@@ -324,7 +382,7 @@ __global__ void __launch_bounds__(256) k_reduce_rows_direct(const char* __restri
       red_write(K, Q, piece, t);
     }
   }
-  red_fold_by_last_cta(K, Q, smem, &s_last, ident);
+  red_fold_direct<MC>(K, Q, smem, &s_last, ident);
 }
 
 // Which direct kernel, if any, computes this prologue: 0 none, 1 the tensor itself, 2 its square.  The program must be
