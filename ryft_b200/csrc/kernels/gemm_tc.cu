@@ -199,13 +199,24 @@ extern "C" int b2x_launch_gemm_tc(const B2xGemmArgs* a, const B2xVmProgram* epil
   CUtensorMapDataType dt = tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : (a->elem == EL_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
   CUtensorMap tmA, tmB;
   bool ok;
+  TcParams p = r.p;
+  // B2X_GEMM_LOADS=3d keeps one load per 128-byte-wide sub-tile of an MN-major operand (for comparison)
+  static const bool folded = [] { const char* e = getenv("B2X_GEMM_LOADS"); return !(e && e[0] == '3'); }();
+  p.a_mn_4d = p.b_mn_4d = 0;
   if (!a_mn) ok = encode_3d(&tmA, dt, es, a->a, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->batch, (uint64_t)a_ld, (uint64_t)a->a_batch_stride, BK, TC_BM);
-  else ok = encode_3d(&tmA, dt, es, a->a, (uint64_t)a->M, (uint64_t)a->K, (uint64_t)a->batch, (uint64_t)a_ld, (uint64_t)a->a_batch_stride, CHUNK, BK);
+  else {
+    ok = folded && encode_mn_major_4d(&tmA, dt, es, a->a, (uint64_t)a->M, (uint64_t)a->K, (uint64_t)a->batch, (uint64_t)a_ld, (uint64_t)a->a_batch_stride, CHUNK, BK, TC_BM);
+    if (ok) p.a_mn_4d = 1;
+    else ok = encode_3d(&tmA, dt, es, a->a, (uint64_t)a->M, (uint64_t)a->K, (uint64_t)a->batch, (uint64_t)a_ld, (uint64_t)a->a_batch_stride, CHUNK, BK);
+  }
   if (!ok) return (int)cudaErrorInvalidValue;
   if (!b_mn) ok = encode_3d(&tmB, dt, es, a->b, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->batch, (uint64_t)b_ld, (uint64_t)a->b_batch_stride, BK, BN);
-  else ok = encode_3d(&tmB, dt, es, a->b, (uint64_t)a->N, (uint64_t)a->K, (uint64_t)a->batch, (uint64_t)b_ld, (uint64_t)a->b_batch_stride, CHUNK, BK);
+  else {
+    ok = folded && encode_mn_major_4d(&tmB, dt, es, a->b, (uint64_t)a->N, (uint64_t)a->K, (uint64_t)a->batch, (uint64_t)b_ld, (uint64_t)a->b_batch_stride, CHUNK, BK, BN);
+    if (ok) p.b_mn_4d = 1;
+    else ok = encode_3d(&tmB, dt, es, a->b, (uint64_t)a->N, (uint64_t)a->K, (uint64_t)a->batch, (uint64_t)b_ld, (uint64_t)a->b_batch_stride, CHUNK, BK);
+  }
   if (!ok) return (int)cudaErrorInvalidValue;
-  const TcParams& p = r.p;
   if (tf32) {
     if (r.static_id) {
       rc = launch_tc_static_tf32(r.static_id, BN, tmA, tmB, p, *epilogue, status, stream);

@@ -31,6 +31,10 @@ namespace b2x {
 struct TcParams {
   int64_t batch, M, N, K;
   int32_t a_mn_major, b_mn_major;
+  // The MN-major operand's map is the folded 4-D form (encode_mn_major_4d): one load per stage instead of one per
+  // 128-byte-wide sub-tile.  The producer is one thread; with five or six loads per k-block it needed 700-750 cycles per
+  // k-block, more than the 512 cycles the tensor pipe takes to consume one, and the MLP step ran 8-12 % slower.
+  int32_t a_mn_4d, b_mn_4d;
   int32_t num_m_tiles, num_n_tiles;
   int64_t num_tiles;
   int32_t k_blocks;
@@ -210,11 +214,13 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
           const uint32_t sa = smem_base + stage * SM::STAGE_BYTES, sb = sa + SM::A_BYTES;
           const int k0 = kb * BK;
           if (!p.a_mn_major) tma_load_3d(sa, &tmA, full, k0, m0, b);
+          else if (p.a_mn_4d) tma_load_4d(sa, &tmA, full, 0, k0, m0 / CHUNK, b);
           else {
 #pragma unroll
             for (int c = 0; c < TC_BM / CHUNK; c++) tma_load_3d(sa + c * (BK * 128), &tmA, full, m0 + c * CHUNK, k0, b);
           }
           if (!p.b_mn_major) tma_load_3d(sb, &tmB, full, k0, n0, b);
+          else if (p.b_mn_4d) tma_load_4d(sb, &tmB, full, 0, k0, n0 / CHUNK, b);
           else {
 #pragma unroll
             for (int c = 0; c < BN / CHUNK; c++) tma_load_3d(sb + c * (BK * 128), &tmB, full, n0 + c * CHUNK, k0, b);

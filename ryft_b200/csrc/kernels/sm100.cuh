@@ -68,6 +68,13 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
       : "memory");
 }
 
+// The same with four coordinates.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"((uint64_t)m), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
 // 3-D tiled store of a box from this CTA's shared memory; part of the issuing thread's current bulk group.  Boxes are
 // clipped at the tensor's extents, so ragged edges need no predication.  c0 times the element size must be a multiple
 // of 16 bytes and no coordinate may be negative.
@@ -216,6 +223,27 @@ inline bool encode_3d(CUtensorMap* m, CUtensorMapDataType dt, int es, const void
   cuuint32_t box[3] = {box0, box1, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(m, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// 4-D map for an operand whose MN dimension is contiguous ("MN-major"): [batch][mn / chunk][k][chunk], i.e. the MN
+// extent folded into (chunk, mn / chunk), so that one load with box {chunk, box_k, box_mn / chunk, 1} fills all the
+// 128-byte-wide sub-tiles of a stage (they are box_k * 128 bytes apart in shared memory) where the 3-D map needs one load
+// per sub-tile.  The MN extent must be a multiple of `chunk`.
+inline bool encode_mn_major_4d(CUtensorMap* m, CUtensorMapDataType dt, int es, const void* base, uint64_t mn, uint64_t k, uint64_t batch,
+                               uint64_t ld_elems, uint64_t batch_stride_elems, uint32_t chunk, uint32_t box_k, uint32_t box_mn) {
+  PFN_encodeTiled fn = get_encode_tiled();
+  if (!fn || mn % chunk != 0) return false;
+  cuuint64_t dims[4] = {chunk, k, mn / chunk, batch ? batch : 1};
+  uint64_t s1 = ld_elems * es, s2 = (uint64_t)chunk * es, s3 = batch_stride_elems * es;
+  if (s1 % 16 != 0) return false;
+  if (dims[3] <= 1 || s3 == 0) s3 = s1 * k;
+  if (s3 % 16 != 0) return false;
+  cuuint64_t strides[3] = {s1, s2, s3};
+  cuuint32_t box[4] = {chunk, box_k, box_mn / chunk, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(m, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
