@@ -89,8 +89,9 @@ B2X_API int b2x_launch_gemm_tc(const B2xGemmArgs* host_args, const B2xVmProgram*
  * it to assert that a case runs the same kernel variant as another).  out[0] tile width BN, [1] id of the build-time
  * specialised epilogue (0 = interpreted), [2] epilogue groups (1 or 2), [3] 1 if the multi-store epilogue goes through
  * shared memory (transposed), [4] m-tiles per raster group, [5] m-tiles, [6] n-tiles, [7] k-blocks per tile, [8] stores of
- * the specialised program, [9] CTAs launched. */
-B2X_API int b2x_gemm_tc_route(const B2xGemmArgs* host_args, const B2xVmProgram* host_epilogue, int32_t out[10]);
+ * the specialised program, [9] CTAs launched, [10] rows of a tile (128, or 256 for the tall tiles of long-K problems),
+ * [11] reserved (0). */
+B2X_API int b2x_gemm_tc_route(const B2xGemmArgs* host_args, const B2xVmProgram* host_epilogue, int32_t out[12]);
 /* Splits f32 operands for the 3xTF32 scheme: writes A' = [hi | hi | lo] and B' = [hi | lo | hi] along K into scratch
  * (K-major rows of 3K elements), so that one TF32 GEMM over K' = 3K yields hi*hi + hi*lo + lo*hi. */
 B2X_API int b2x_launch_split_f32(const B2xGemmArgs* host_args, float* a_split, float* b_split, b2x_stream_t stream);

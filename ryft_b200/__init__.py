@@ -34,7 +34,8 @@ def plan_dump(mlir_text: str, num_replicas: int = 1) -> str:
 def plan_routes(mlir_text: str, num_replicas: int = 1) -> list:
     """For every tensor-core GEMM step of the program's launch plan, the kernel variant the launcher will pick (no GPU
     needed): a list of dicts with the problem size, tile width `bn`, the id of the build-time specialised epilogue
-    (`static_id`, 0 = interpreted), `epi_groups`, `transposed`, `group_m`, tile counts, `stores` and `ctas`."""
+    (`static_id`, 0 = interpreted), `epi_groups`, `transposed`, `group_m`, tile counts, `stores`, `ctas` and `tile_rows`
+    (128, or 256 for the tall tiles of long-K problems)."""
     import ctypes as C
     from .pjrt import PjrtError
     if not KERNELS_PATH.exists():
@@ -49,7 +50,7 @@ def plan_routes(mlir_text: str, num_replicas: int = 1) -> list:
     text = out.value.decode("utf-8", "replace")
     if code:
         raise PjrtError(code, text)
-    keys = ("M", "N", "K", "batch", "bn", "static_id", "epi_groups", "transposed", "group_m", "m_tiles", "n_tiles", "k_blocks", "stores", "ctas")
+    keys = ("M", "N", "K", "batch", "bn", "static_id", "epi_groups", "transposed", "group_m", "m_tiles", "n_tiles", "k_blocks", "stores", "ctas", "tile_rows")
     rows = []
     for line in text.splitlines():
         parts = line.split("|")

@@ -157,9 +157,29 @@ static int tc_route(const B2xGemmArgs* a, const B2xVmProgram* epilogue, TcRoute*
   p.k_blocks = (int)((a->K + BK - 1) / BK);
   p.transposed = a->K <= 8192 ? 1 : 0;
   p.epi_groups = p.k_blocks <= 8 ? 1 : 2;
+  // Tall (256 x 256) tiles: long-K 16-bit problems whose tall tiles still fill the last round of the 148 SMs.  Their
+  // epilogue is not overlapped, so K must be long enough to make it small; B2X_GEMM_TALL=0 / 1 switches them off / forces
+  // them wherever the kernel can run them.
+  p.tall = 0;
+  int64_t bm = TC_BM;
+  if (!r->tf32 && BN == 256 && a->M >= 2 * TC_BM) {
+    static const int mode = [] { const char* e = getenv("B2X_GEMM_TALL"); return e ? atoi(e) : -1; }();
+    // how full the rounds of the 148 SMs are with either tile height; tall tiles were measured 20-25 % faster per FLOP
+    // (MLP step, K = 4096 ... 16384), so they are taken unless their last round wastes more than that
+    const int64_t tall_tiles = ((a->M + 2 * TC_BM - 1) / (2 * TC_BM)) * p.num_n_tiles * a->batch;
+    auto fill = [](int64_t tiles) { const int64_t rounds = (tiles + kNumSms - 1) / kNumSms; return (double)tiles / (double)(rounds * kNumSms); };
+    const bool pays = fill(tall_tiles) * 1.2 > fill(p.num_tiles);
+    if (mode == 1 || (mode != 0 && p.k_blocks >= 32 && pays)) {
+      p.tall = 1;
+      p.epi_groups = 2;
+      bm = 2 * TC_BM;
+      p.num_m_tiles = (int)((a->M + bm - 1) / bm);
+      p.num_tiles = (int64_t)p.num_m_tiles * p.num_n_tiles * a->batch;
+    }
+  }
   {
     // A slab of a group ~ 32 MiB (a quarter of the 126 MB L2)
-    const int64_t slab_per_m_tile = (int64_t)TC_BM * a->K * es;
+    const int64_t slab_per_m_tile = bm * a->K * es;
     int64_t gm = (32ll << 20) / (slab_per_m_tile > 0 ? slab_per_m_tile : 1);
     if (gm < 4) gm = 4;
     if (gm > 64) gm = 64;
@@ -173,7 +193,7 @@ static int tc_route(const B2xGemmArgs* a, const B2xVmProgram* epilogue, TcRoute*
 }
 }  // namespace b2x
 
-extern "C" int b2x_gemm_tc_route(const B2xGemmArgs* a, const B2xVmProgram* epilogue, int32_t out[10]) {
+extern "C" int b2x_gemm_tc_route(const B2xGemmArgs* a, const B2xVmProgram* epilogue, int32_t out[12]) {
   using namespace b2x;
   TcRoute r;
   int rc = tc_route(a, epilogue, &r);
@@ -183,6 +203,8 @@ extern "C" int b2x_gemm_tc_route(const B2xGemmArgs* a, const B2xVmProgram* epilo
   out[4] = r.p.group_m; out[5] = r.p.num_m_tiles; out[6] = r.p.num_n_tiles; out[7] = r.p.k_blocks;
   out[8] = r.static_id ? tc_static_stores(r.static_id) : 0;
   out[9] = (int32_t)(r.p.num_tiles < kNumSms ? r.p.num_tiles : kNumSms);
+  out[10] = r.p.tall ? 2 * TC_BM : TC_BM;
+  out[11] = 0;
   return 0;
 }
 
@@ -203,9 +225,10 @@ extern "C" int b2x_launch_gemm_tc(const B2xGemmArgs* a, const B2xVmProgram* epil
   // B2X_GEMM_LOADS=3d keeps one load per 128-byte-wide sub-tile of an MN-major operand (for comparison)
   static const bool folded = [] { const char* e = getenv("B2X_GEMM_LOADS"); return !(e && e[0] == '3'); }();
   p.a_mn_4d = p.b_mn_4d = 0;
-  if (!a_mn) ok = encode_3d(&tmA, dt, es, a->a, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->batch, (uint64_t)a_ld, (uint64_t)a->a_batch_stride, BK, TC_BM);
+  const uint32_t bm = p.tall ? 2 * TC_BM : TC_BM;   // rows of A per stage
+  if (!a_mn) ok = encode_3d(&tmA, dt, es, a->a, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->batch, (uint64_t)a_ld, (uint64_t)a->a_batch_stride, BK, bm);
   else {
-    ok = folded && encode_mn_major_4d(&tmA, dt, es, a->a, (uint64_t)a->M, (uint64_t)a->K, (uint64_t)a->batch, (uint64_t)a_ld, (uint64_t)a->a_batch_stride, CHUNK, BK, TC_BM);
+    ok = folded && encode_mn_major_4d(&tmA, dt, es, a->a, (uint64_t)a->M, (uint64_t)a->K, (uint64_t)a->batch, (uint64_t)a_ld, (uint64_t)a->a_batch_stride, CHUNK, BK, bm);
     if (ok) p.a_mn_4d = 1;
     else ok = encode_3d(&tmA, dt, es, a->a, (uint64_t)a->M, (uint64_t)a->K, (uint64_t)a->batch, (uint64_t)a_ld, (uint64_t)a->a_batch_stride, CHUNK, BK);
   }

@@ -35,6 +35,12 @@ struct TcParams {
   // 128-byte-wide sub-tile.  The producer is one thread; with five or six loads per k-block it needed 700-750 cycles per
   // k-block, more than the 512 cycles the tensor pipe takes to consume one, and the MLP step ran 8-12 % slower.
   int32_t a_mn_4d, b_mn_4d;
+  // Tall tiles (256 x 256, only the <256, 4> kernels on long-K 16-bit problems): a stage is 256 rows of A and 256 of B
+  // (64 KB, three stages in the same 192 KB ring), every k-step issues two MMAs that share the B sub-tile, one into each
+  // 256-column accumulator, and epilogue group g drains accumulator g = rows [128 g, 128 g + 128) of the tile.  Operand
+  // bytes per FLOP drop by a third (62.5 instead of 94 bytes per clock and SM at full tensor rate) and a stage covers
+  // 1024 cycles of tensor work instead of 512; the price is that the epilogue no longer overlaps the next tile's MMAs.
+  int32_t tall;
   int32_t num_m_tiles, num_n_tiles;
   int64_t num_tiles;
   int32_t k_blocks;
@@ -74,7 +80,7 @@ __device__ __forceinline__ void tc_tile_coords(const TcParams& p, int64_t t, int
   const uint32_t gm = (uint32_t)min(p.group_m, p.num_m_tiles - (int)g * p.group_m);
   const uint32_t nn = in / gm;
   *b = (int)bb;
-  *m0 = (int)(g * (uint32_t)p.group_m + (in - nn * gm)) * TC_BM;
+  *m0 = (int)(g * (uint32_t)p.group_m + (in - nn * gm)) * (p.tall ? 2 * TC_BM : TC_BM);
   *n0 = (int)nn * BN;
 }
 
@@ -161,7 +167,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
     for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
     for (int a = 0; a < NACC; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, TC_EPI_WARPS / p.epi_groups); }
     mbar_init(bar_drain, 1);
-    for (int r = 0; r < RING; r++) { mbar_init(bar_sfull + 8 * r, 1); mbar_init(bar_sempty + 8 * r, TC_EPI_WARPS / p.epi_groups + 1); }
+    for (int r = 0; r < RING; r++) { mbar_init(bar_sfull + 8 * r, 1); mbar_init(bar_sempty + 8 * r, (p.tall ? TC_EPI_WARPS : TC_EPI_WARPS / p.epi_groups) + 1); }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -175,6 +181,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // stage geometry: the ring is STAGES * STAGE_BYTES either way (tall tiles are only routed to the <256, 4> kernels,
+  // whose 4 x 48 KB ring is 3 x 64 KB)
+  const int n_stages = p.tall ? 3 : STAGES;
+  const uint32_t a_bytes = p.tall ? 2u * SM::A_BYTES : (uint32_t)SM::A_BYTES;
+  const uint32_t stage_bytes = a_bytes + (uint32_t)SM::B_BYTES;
 
 
   if (warp == 0) {
@@ -196,7 +207,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         if (t >= 0) tc_tile_coords(p, t, BN, &b, &m0, &n0);
         tile_ring[slot * 4 + 0] = (int32_t)t; tile_ring[slot * 4 + 1] = b; tile_ring[slot * 4 + 2] = m0; tile_ring[slot * 4 + 3] = n0;
         if (!(p.withhold && local == 0 && blockIdx.x == 0)) mbar_arrive(bar_sfull + 8 * slot);
-        if (t < 0 && p.epi_groups == 1) break;
+        if (t < 0 && (p.epi_groups == 1 || p.tall)) break;
         if (t < 0) {
           // the other epilogue group reads the ring entry after this one: it gets its own end marker
           const int64_t nxt = local + 1;
@@ -210,14 +221,18 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         for (int kb = 0; kb < p.k_blocks; kb++) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, status, 1)) { ok = false; break; }
           const uint32_t full = bar_full + 8 * stage;
-          mbar_expect_tx(full, SM::STAGE_BYTES);
-          const uint32_t sa = smem_base + stage * SM::STAGE_BYTES, sb = sa + SM::A_BYTES;
+          mbar_expect_tx(full, stage_bytes);
+          const uint32_t sa = smem_base + stage * stage_bytes, sb = sa + a_bytes;
           const int k0 = kb * BK;
           if (!p.a_mn_major) tma_load_3d(sa, &tmA, full, k0, m0, b);
           else if (p.a_mn_4d) tma_load_4d(sa, &tmA, full, 0, k0, m0 / CHUNK, b);
           else {
 #pragma unroll
             for (int c = 0; c < TC_BM / CHUNK; c++) tma_load_3d(sa + c * (BK * 128), &tmA, full, m0 + c * CHUNK, k0, b);
+            if (p.tall) {
+#pragma unroll
+              for (int c = TC_BM / CHUNK; c < 2 * TC_BM / CHUNK; c++) tma_load_3d(sa + c * (BK * 128), &tmA, full, m0 + c * CHUNK, k0, b);
+            }
           }
           if (!p.b_mn_major) tma_load_3d(sb, &tmB, full, k0, n0, b);
           else if (p.b_mn_4d) tma_load_4d(sb, &tmB, full, 0, k0, n0 / CHUNK, b);
@@ -225,7 +240,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
 #pragma unroll
             for (int c = 0; c < BN / CHUNK; c++) tma_load_3d(sb + c * (BK * 128), &tmB, full, n0 + c * CHUNK, k0, b);
           }
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == n_stages) { stage = 0; phase ^= 1; }
         }
       }
       if (!ok) {
@@ -247,15 +262,16 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         const int32_t t = tile_ring[slot * 4];
         mbar_arrive(bar_sempty + 8 * slot);
         if (t < 0) break;
-        const int acc = (int)(local % NACC);
-        const uint32_t acc_phase = (uint32_t)((local / NACC) & 1);
+        const int acc = p.tall ? 0 : (int)(local % NACC);
+        const uint32_t acc_phase = p.tall ? (uint32_t)(local & 1) : (uint32_t)((local / NACC) & 1);
         if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, status, 2)) { ok = false; break; }
+        if (p.tall && !mbar_wait(bar_tempty + 8, acc_phase ^ 1, abort_flag, status, 2)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         for (int kb = 0; kb < p.k_blocks; kb++) {
           if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, status, 3)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sa = smem_base + stage * SM::STAGE_BYTES, sb = sa + SM::A_BYTES;
+          const uint32_t sa = smem_base + stage * stage_bytes, sb = sa + a_bytes;
           // K-major: 8-row groups 1024 B apart, k advances 32 B inside the swizzle atom.
           // MN-major: 64/32-element chunks BK*128 B apart, 8 k-lines per 1024 B group, k advances UMMA_K lines.
           const uint64_t a_desc0 = p.a_mn_major ? make_smem_desc(sa, BK * 128, 1024) : make_smem_desc(sa, 16, 1024);
@@ -265,11 +281,15 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; k++) {
             umma_ss<TF32>(d_tmem, a_desc0 + (uint64_t)(k * a_adv), b_desc0 + (uint64_t)(k * b_adv), p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            // tall tiles: rows 128..255 of the stage's A (16 KB further in either layout) against the same B sub-tile
+            if (p.tall) umma_ss<TF32>(d_tmem + (uint32_t)BN, a_desc0 + (uint64_t)(k * a_adv) + (uint64_t)(SM::A_BYTES >> 4), b_desc0 + (uint64_t)(k * b_adv), p.idesc,
+                                      (kb > 0 || k > 0) ? 1u : 0u);
           }
           tc_commit(bar_empty + 8 * stage);   // frees the stage once the MMAs above have read it
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == n_stages) { stage = 0; phase ^= 1; }
         }
         if (ok) tc_commit(bar_tfull + 8 * acc);  // accumulator complete
+        if (ok && p.tall) tc_commit(bar_tfull + 8);
       }
       // drain: everything issued must retire before TMEM is released
       tc_commit(bar_drain);
@@ -284,16 +304,16 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
     const int col_parts = group_warps / 4;
     bool ok = true;
     const VmRowPlan rplan = vm_row_plan(epi, (uint32_t)p.N);
-    for (int64_t local = group; ok; local += p.epi_groups) {
+    for (int64_t local = p.tall ? 0 : group; ok; local += p.tall ? 1 : p.epi_groups) {
       const int slot = (int)(local & (RING - 1));
       if (!mbar_wait(bar_sfull + 8 * slot, (uint32_t)((local / RING) & 1), abort_flag, status, 7)) { ok = false; break; }
       const int64_t t = tile_ring[slot * 4];
-      const int b = tile_ring[slot * 4 + 1], m0 = tile_ring[slot * 4 + 2], n0 = tile_ring[slot * 4 + 3];
+      const int b = tile_ring[slot * 4 + 1], m0 = tile_ring[slot * 4 + 2] + (p.tall ? group * TC_BM : 0), n0 = tile_ring[slot * 4 + 3];
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_sempty + 8 * slot);
       if (t < 0) break;
-      const int acc = (int)(local % NACC);
-      const uint32_t acc_phase = (uint32_t)((local / NACC) & 1);
+      const int acc = p.tall ? group : (int)(local % NACC);
+      const uint32_t acc_phase = p.tall ? (uint32_t)(local & 1) : (uint32_t)((local / NACC) & 1);
       if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, status, 4)) { ok = false; break; }
       tc_fence_after();
       const int64_t row = (int64_t)m0 + quad * 32 + lane;

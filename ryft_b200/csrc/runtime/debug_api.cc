@@ -132,10 +132,10 @@ extern "C" __attribute__((visibility("default"))) int b2x_plan_routes(const char
         ga.a_k_stride = 1; ga.a_row_stride = ga.K; ga.a_batch_stride = s.gM * ga.K;
         ga.b_k_stride = 1; ga.b_row_stride = ga.K; ga.b_batch_stride = s.gN * ga.K;
       }
-      int32_t r[10] = {};
+      int32_t r[12] = {};
       int rc = b2x_gemm_tc_route(&ga, &s.vm.prog, r);
       text += s.label + "|" + std::to_string(s.gM) + "|" + std::to_string(s.gN) + "|" + std::to_string(ga.K) + "|" + std::to_string(s.gB);
-      for (int i = 0; i < 10; i++) text += "|" + std::to_string(rc ? -1 : r[i]);
+      for (int i = 0; i < 11; i++) text += "|" + std::to_string(rc ? -1 : r[i]);
       text += "\n";
     }
   } catch (const b2x::CompileError& e) {

@@ -233,7 +233,10 @@ def test_benchmark_programs_take_specialised_gemm_variants():
     r4 = {r["label"].split("+")[0]: r for r in ryft_b200.plan_routes(configs.c4_program())}
     assert len(r4) == 5 and all(r["bn"] == 256 and r["static_id"] and r["ctas"] == 148 for r in r4.values())
     assert r4["dot_general:%0"]["transposed"] == 1 and r4["dot_general:%16"]["transposed"] == 0 and r4["dot_general:%16"]["stores"] == 2
+    # long K: 256-row tiles (two MMAs per k-step share the B sub-tile), also where their last round of SMs is less full
+    assert all(r["tile_rows"] == 256 and r["epi_groups"] == 2 for r in r4.values())
+    assert r4["dot_general:%0"]["m_tiles"] * r4["dot_general:%0"]["n_tiles"] == 32 * 64 and r4["dot_general:%16"]["m_tiles"] * r4["dot_general:%16"]["n_tiles"] == 32 * 16
     (r2,) = ryft_b200.plan_routes(configs.c2_program())
-    assert (r2["bn"], r2["epi_groups"], r2["k_blocks"], r2["stores"]) == (256, 1, 2, 1) and r2["static_id"]
+    assert (r2["bn"], r2["epi_groups"], r2["k_blocks"], r2["stores"], r2["tile_rows"]) == (256, 1, 2, 1, 128) and r2["static_id"]
     (r1,) = ryft_b200.plan_routes(configs.c1_program())
     assert r1["K"] == 3 * 768 and r1["static_id"]

@@ -475,16 +475,16 @@ def test_c4_mid_size_forces_the_benchmark_kernel_variants(client, T, D, F):
     """Smaller problems that still take the benchmark's kernel variants, so that a failure of the full-size test can be
     narrowed down in seconds.  (2048, 2048, 8448): the forward GEMMs run the same specialised two-store epilogues as the
     benchmark, one transposed through shared memory (K <= 8192) and one with row-strided stores (K > 8192), with two
-    epilogue groups, 256-wide tiles and more than three waves of tiles.  (4224, 512, 8448): a raster group smaller than
+    epilogue groups, 256 x 256 tiles and more than one wave of tiles.  (4224, 512, 8448): a raster group smaller than
     the number of m-tiles (dW2), one epilogue group on a short-K GEMM, and a 128-wide two-store epilogue."""
     text = configs.c4_program(T, D, F)
     full = _routes_by_label(configs.c4_program())
     here = _routes_by_label(text)
     if (T, D, F) == (2048, 2048, 8448):
         for label in ("dot_general:%0", "dot_general:%16", "dot_general:%26"):
-            for key in ("bn", "static_id", "epi_groups", "transposed", "stores"):
+            for key in ("bn", "static_id", "epi_groups", "transposed", "stores", "tile_rows"):
                 assert here[label][key] == full[label][key], (label, key, here[label], full[label])
-        assert here["dot_general:%0"]["m_tiles"] * here["dot_general:%0"]["n_tiles"] >= 3 * 148
+        assert here["dot_general:%0"]["tile_rows"] == 256 and here["dot_general:%0"]["m_tiles"] * here["dot_general:%0"]["n_tiles"] > 148
     else:
         assert here["dot_general:%25"]["group_m"] < here["dot_general:%25"]["m_tiles"]
         assert here["dot_general:%0"]["epi_groups"] == 1 and here["dot_general:%16"]["bn"] == 128
