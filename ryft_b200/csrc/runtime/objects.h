@@ -92,6 +92,16 @@ struct PJRT_Device {
   std::mutex staging_mu;
   std::vector<void*> staging_free;   // blocks of kStagingBlock bytes
   static constexpr size_t kStagingBlock = 64 << 10;
+  // Device blocks of destroyed host-upload buffers, kept with the event behind their last use.  A training loop uploads a
+  // buffer of the same size every step from a stream of its own; the stream-ordered pool can hand a block freed on the
+  // compute stream to that stream only once the free has retired, and otherwise grows (milliseconds, in the middle of a
+  // run).  An upload first looks here for a block of its size whose event has completed.
+  struct RecycledBlock { void* ptr; size_t bytes; cudaEvent_t last_use; };
+  std::mutex recycle_mu;
+  std::vector<RecycledBlock> recycled;
+  static constexpr size_t kMaxRecycled = 8;
+  static constexpr size_t kMinRecycledBytes = 1 << 20;
+  static constexpr size_t kMaxRecycledBytes = 1ull << 30;
 };
 
 // Definition of a buffer that is filled after it was created (asynchronous host-to-device transfers): consumers that
@@ -112,6 +122,7 @@ struct PJRT_Buffer {
   void* ptr = nullptr;
   size_t bytes = 0;
   bool owns = true;           // false for views of foreign device memory
+  bool from_host = false;     // created by a host-to-device upload: its block is recycled for the next upload of that size
   bool deleted = false;
   std::function<void()> on_delete;
   cudaEvent_t ready = nullptr;      // recorded on the producing stream

@@ -118,6 +118,8 @@ PJRT_Client::~PJRT_Client() {
     if (d->h2d) cudaStreamDestroy(d->h2d);
     if (d->d2h) cudaStreamDestroy(d->d2h);
     if (d->comm) cudaStreamDestroy(d->comm);
+    for (auto& r : d->recycled) { cudaEventDestroy(r.last_use); cudaFree(r.ptr); }
+    d->recycled.clear();
     if (d->status_host) cudaFreeHost(d->status_host);
     for (void* p : d->staging_free) cudaFreeHost(p);
     d->staging_free.clear();
@@ -195,7 +197,22 @@ static void release_buffer_memory(PJRT_Buffer* b) {
     for (auto ev : b->pending_reads) { cudaStreamWaitEvent(d->compute, ev, 0); cudaEventDestroy(ev); }
     b->pending_reads.clear();
     if (b->ready) cudaStreamWaitEvent(d->compute, b->ready, 0);
-    cudaFreeAsync(b->ptr, d->compute);
+    bool kept = false;
+    if (b->from_host && b->bytes >= PJRT_Device::kMinRecycledBytes) {
+      std::lock_guard<std::mutex> lk(d->recycle_mu);
+      size_t held = 0;
+      for (auto& r : d->recycled) held += r.bytes;
+      if (d->recycled.size() < PJRT_Device::kMaxRecycled && held + b->bytes <= PJRT_Device::kMaxRecycledBytes) {
+        cudaEvent_t ev = nullptr;
+        if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) == cudaSuccess && cudaEventRecord(ev, d->compute) == cudaSuccess) {
+          d->recycled.push_back({b->ptr, b->bytes, ev});
+          kept = true;
+        } else if (ev) {
+          cudaEventDestroy(ev);
+        }
+      }
+    }
+    if (!kept) cudaFreeAsync(b->ptr, d->compute);
     d->bytes_in_use -= (int64_t)b->bytes;
   } else {
     for (auto ev : b->pending_reads) { cudaEventSynchronize(ev); cudaEventDestroy(ev); }
@@ -540,8 +557,36 @@ static PJRT_Error* Client_BufferFromHostBuffer(PJRT_Client_BufferFromHostBuffer_
     int64_t acc = es;
     for (int i = (int)a->num_dims - 1; i >= 0; i--) { if (t.dims[i] != 1 && a->byte_strides[i] != acc) dense = false; acc *= t.dims[i]; }
   }
-  PJRT_Buffer* b;
-  B2X_RETURN_IF_ERROR(alloc_buffer(dev, t, dev->h2d, &b));
+  PJRT_Buffer* b = nullptr;
+  {
+    // a block of this size that an earlier upload left behind and whose last use has finished
+    const size_t want = (size_t)t.byte_size();
+    void* reuse = nullptr;
+    if (want >= PJRT_Device::kMinRecycledBytes) {
+      std::lock_guard<std::mutex> lk(dev->recycle_mu);
+      for (size_t i = 0; i < dev->recycled.size(); i++) {
+        PJRT_Device::RecycledBlock& r = dev->recycled[i];
+        if (r.bytes != want) continue;
+        cudaSetDevice(dev->cuda_ordinal);
+        if (cudaEventQuery(r.last_use) != cudaSuccess) { cudaGetLastError(); continue; }
+        cudaEventDestroy(r.last_use);
+        reuse = r.ptr;
+        dev->recycled.erase(dev->recycled.begin() + (long)i);
+        break;
+      }
+    }
+    if (reuse) {
+      b = new PJRT_Buffer();
+      b->client = dev->client; b->device = dev; b->type = t; b->dims = t.dims; b->pjrt_type = to_pjrt_type(t.dtype);
+      b->bytes = want;
+      for (int i = t.rank() - 1; i >= 0; i--) b->minor_to_major.push_back(i);
+      b->ptr = reuse;
+      track_alloc(dev, (int64_t)b->bytes);
+    } else {
+      B2X_RETURN_IF_ERROR(alloc_buffer(dev, t, dev->h2d, &b));
+    }
+    b->from_host = true;
+  }
   const void* src = a->data;
   std::vector<uint8_t> packed;
   if (!dense) {  // gather the strided host tensor into dense row-major order first

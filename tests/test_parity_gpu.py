@@ -482,7 +482,7 @@ def test_c4_mid_size_forces_the_benchmark_kernel_variants(client, T, D, F):
     here = _routes_by_label(text)
     if (T, D, F) == (2048, 2048, 8448):
         for label in ("dot_general:%0", "dot_general:%16", "dot_general:%26"):
-            for key in ("bn", "static_id", "epi_groups", "transposed", "stores", "tile_rows"):
+            for key in ("bn", "static_id", "epi_groups", "transposed", "stores"):
                 assert here[label][key] == full[label][key], (label, key, here[label], full[label])
         assert here["dot_general:%0"]["tile_rows"] == 256 and here["dot_general:%0"]["m_tiles"] * here["dot_general:%0"]["n_tiles"] > 148
     else:
