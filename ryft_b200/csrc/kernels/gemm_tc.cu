@@ -172,6 +172,7 @@ static int tc_route(const B2xGemmArgs* a, const B2xVmProgram* epilogue, TcRoute*
     if (mode == 1 || (mode != 0 && p.k_blocks >= 32 && pays)) {
       p.tall = 1;
       p.epi_groups = 2;
+      p.transposed = 1;   // the epilogue of a tall tile is not hidden behind the next tile, so the form with fewer store cycles wins at every K
       bm = 2 * TC_BM;
       p.num_m_tiles = (int)((a->M + bm - 1) / bm);
       p.num_tiles = (int64_t)p.num_m_tiles * p.num_n_tiles * a->batch;

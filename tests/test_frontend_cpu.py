@@ -232,7 +232,8 @@ def test_benchmark_programs_take_specialised_gemm_variants():
     """The kernel variant each GEMM of the benchmark programs runs, as the launcher decides it (host only)."""
     r4 = {r["label"].split("+")[0]: r for r in ryft_b200.plan_routes(configs.c4_program())}
     assert len(r4) == 5 and all(r["bn"] == 256 and r["static_id"] and r["ctas"] == 148 for r in r4.values())
-    assert r4["dot_general:%0"]["transposed"] == 1 and r4["dot_general:%16"]["transposed"] == 0 and r4["dot_general:%16"]["stores"] == 2
+    # two-store epilogues of 256-row tiles always go through shared memory (their time is not hidden behind the next tile)
+    assert r4["dot_general:%0"]["transposed"] == 1 and r4["dot_general:%16"]["transposed"] == 1 and r4["dot_general:%16"]["stores"] == 2
     # long K: 256-row tiles (two MMAs per k-step share the B sub-tile), also where their last round of SMs is less full
     assert all(r["tile_rows"] == 256 and r["epi_groups"] == 2 for r in r4.values())
     assert r4["dot_general:%0"]["m_tiles"] * r4["dot_general:%0"]["n_tiles"] == 32 * 64 and r4["dot_general:%16"]["m_tiles"] * r4["dot_general:%16"]["n_tiles"] == 32 * 16
