@@ -161,6 +161,9 @@ static int tc_route(const B2xGemmArgs* a, const B2xVmProgram* epilogue, TcRoute*
   // epilogue is not overlapped, so K must be long enough to make it small; B2X_GEMM_TALL=0 / 1 switches them off / forces
   // them wherever the kernel can run them.
   p.tall = 0;
+  // short K: three stages, the fourth holds the second set of staging tiles of the bulk-store epilogue (gemm_tc.cuh)
+  p.short_k = (BN == 256 && !r->tf32 && p.k_blocks <= 3) ? 1 : 0;
+  { static const int sk = [] { const char* e = getenv("B2X_GEMM_SHORT_K"); return e ? atoi(e) : -1; }(); if (sk == 0) p.short_k = 0; }
   int64_t bm = TC_BM;
   if (!r->tf32 && BN == 256 && a->M >= 2 * TC_BM) {
     static const int mode = [] { const char* e = getenv("B2X_GEMM_TALL"); return e ? atoi(e) : -1; }();

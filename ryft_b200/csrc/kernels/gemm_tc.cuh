@@ -41,6 +41,10 @@ struct TcParams {
   // bytes per FLOP drop by a third (62.5 instead of 94 bytes per clock and SM at full tensor rate) and a stage covers
   // 1024 cycles of tensor work instead of 512; the price is that the epilogue no longer overlaps the next tile's MMAs.
   int32_t tall;
+  // Short-K problems (a tile is at most three k-blocks, only the <256, 4> kernels): three stages instead of four, and the
+  // freed 48 KB double the bulk-store epilogue's staging tiles, so that a warp fills one while the TMA engine still reads the
+  // other (with one tile it waited 200-350 cycles per strip for the previous store to have read it).
+  int32_t short_k;
   int32_t num_m_tiles, num_n_tiles;
   int64_t num_tiles;
   int32_t k_blocks;
@@ -183,7 +187,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   const uint32_t tmem_base = *tmem_slot;
   // stage geometry: the ring is STAGES * STAGE_BYTES either way (tall tiles are only routed to the <256, 4> kernels,
   // whose 4 x 48 KB ring is 3 x 64 KB)
-  const int n_stages = p.tall ? 3 : STAGES;
+  const int n_stages = (p.tall || p.short_k) ? 3 : STAGES;
   const uint32_t a_bytes = p.tall ? 2u * SM::A_BYTES : (uint32_t)SM::A_BYTES;
   const uint32_t stage_bytes = a_bytes + (uint32_t)SM::B_BYTES;
 
@@ -303,6 +307,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
     const int part = ((warp - 2) % group_warps) >> 2;            // column chunks part, part + col_parts, ...
     const int col_parts = group_warps / 4;
     bool ok = true;
+    uint32_t stg_sel = 0;
     const VmRowPlan rplan = vm_row_plan(epi, (uint32_t)p.N);
     for (int64_t local = p.tall ? 0 : group; ok; local += p.tall ? 1 : p.epi_groups) {
       const int slot = (int)(local & (RING - 1));
@@ -370,8 +375,10 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
           // store per 64-byte-wide column strip.
           constexpr int OES = tc_store_elem_size<ID>();
           constexpr int STRIP = 64 / OES;                   // columns per strip: 32 (16-bit) or 16 (32-bit)
-          const uint32_t stg = smem_base + SM::STAGING_OFFSET + (uint32_t)(warp - 2) * 2048u;
-          const uint32_t my = stg + (uint32_t)lane * 64u;
+          // short_k: two staging tiles per warp in the ring's unused fourth stage, used alternately
+          const uint32_t stg0 = p.short_k ? smem_base + 3u * (uint32_t)SM::STAGE_BYTES + (uint32_t)(warp - 2) * 2048u
+                                          : smem_base + SM::STAGING_OFFSET + (uint32_t)(warp - 2) * 2048u;
+          const uint32_t stg1 = p.short_k ? smem_base + SM::STAGING_OFFSET + (uint32_t)(warp - 2) * 2048u : stg0;
           const uint32_t sw = (uint32_t)((lane >> 1) & 3);
           VmRow vrow;
           vm_row_begin(epi, rplan, (uint64_t)((int64_t)b * p.M + (row_ok ? row : 0)), (uint32_t)p.N, vrow);
@@ -384,8 +391,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
               tc_wait_ld();
 #pragma unroll
               for (int strip = 0; strip < 32 / STRIP; strip++) {
-                // the previous strip's store must have read the staging tile before it is overwritten
-                if (lane == 0) bulk_wait_read();
+                // the store that last read this staging tile must be done with it: the previous one, or with two tiles the
+                // one before that
+                const uint32_t stg = stg_sel ? stg1 : stg0;
+                const uint32_t my = stg + (uint32_t)lane * 64u;
+                if (lane == 0) { if (p.short_k) bulk_wait_read_1(); else bulk_wait_read(); }
                 __syncwarp();
 #pragma unroll
                 for (int v = strip * (STRIP / 8); v < (strip + 1) * (STRIP / 8); v++) {
@@ -401,10 +411,12 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                 }
                 fence_async_shared();
                 __syncwarp();
-                if (lane == 0 && n0 + c * 32 + strip * STRIP < p.N && m0 + quad * 32 < p.M) {
+                const bool do_store = n0 + c * 32 + strip * STRIP < p.N && m0 + quad * 32 < p.M;   // the same for the whole warp
+                if (lane == 0 && do_store) {
                   tma_store_3d(&tmOut, stg, n0 + c * 32 + strip * STRIP, m0 + quad * 32, b);
                   bulk_commit();
                 }
+                if (do_store && p.short_k) stg_sel ^= 1u;   // issued stores alternate between the two tiles
               }
             }
             // the last strip's store is still reading the staging tile: the next tile waits for it before its first
